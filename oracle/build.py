@@ -1,0 +1,107 @@
+"""Build the CPU oracle (and, when the reference checkout is present, the
+reference's own CPU extensions) with plain gcc/g++ commands.
+
+TEST INFRASTRUCTURE: the outputs are loaded only by tests, the smoke test and
+the benchmark's CPU-baseline legs.
+
+  python oracle/build.py            # oracle + (if the reference tree exists) oracle/_ref
+  python oracle/build.py --no-ref   # oracle only
+
+Outputs
+  oracle/liblffn_oracle.so   C restatement (oracle/lffn_oracle.c)
+  oracle/_ref/ccs_cpu*.so          reference compute_code_score extension, unmodified source
+  oracle/_ref/gather_add_cpu*.so   reference CPU gather extension, unmodified source
+The reference sources are compiled where they lie; nothing is copied.
+"""
+import argparse
+import os
+import subprocess
+import sys
+import sysconfig
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "liblffn_oracle.so")
+REF_OUT = os.path.join(HERE, "_ref")
+REF_ROOT = os.environ.get("LFFN_REFERENCE_ROOT", "/root/reference")
+REF_LOOKUP = os.path.join(REF_ROOT, "src", "roberta", "models", "prenorm_lookup")
+
+# AVX2+FMA rather than -march=native: the library is built on one machine and
+# run on another.  -ffp-contract=off keeps every rounding where the source puts it.
+CFLAGS = ["-O3", "-mavx2", "-mfma", "-ffp-contract=off", "-fno-fast-math", "-fopenmp", "-fPIC", "-shared"]
+
+REF_EXTENSIONS = {
+    # module name -> source relative to prenorm_lookup/
+    "ccs_cpu": os.path.join("compute_code_score", "torch_extension.cc"),
+    "gather_add_cpu": os.path.join("gather", "cpu", "torch_extension.cpp"),
+}
+
+
+def _newer(target, sources):
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources)
+
+
+def build_oracle(force=False, verbose=True):
+    src = os.path.join(HERE, "lffn_oracle.c")
+    if not force and _newer(ORACLE_SO, [src]):
+        return ORACLE_SO
+    cmd = ["gcc", "-std=gnu11"] + CFLAGS + [src, "-o", ORACLE_SO, "-lm"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.check_call(cmd)
+    return ORACLE_SO
+
+
+def ref_module_path(name):
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    return os.path.join(REF_OUT, name + suffix)
+
+
+def build_ref(force=False, verbose=True):
+    """Compile the reference's two CPU extensions (pybind11 + ATen modules) with one
+    g++ command each.  Returns the list built, or [] when the reference tree is absent."""
+    if not os.path.isdir(REF_LOOKUP):
+        return []
+    import torch
+    from torch.utils import cpp_extension
+
+    os.makedirs(REF_OUT, exist_ok=True)
+    inc = []
+    for p in cpp_extension.include_paths():
+        inc += ["-isystem", p]
+    inc += ["-isystem", sysconfig.get_paths()["include"]]
+    libdir = os.path.join(os.path.dirname(torch.__file__), "lib")
+    built = []
+    for name, rel in REF_EXTENSIONS.items():
+        src = os.path.join(REF_LOOKUP, rel)
+        out = ref_module_path(name)
+        if not force and _newer(out, [src]):
+            built.append(out)
+            continue
+        cmd = (["g++", "-std=c++17", "-O3", "-mavx2", "-mfma", "-fopenmp", "-fPIC", "-shared", "-w",
+                f"-DTORCH_EXTENSION_NAME={name}", "-DTORCH_API_INCLUDE_EXTENSION_H",
+                f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+               + inc + [src, "-o", out, f"-L{libdir}", f"-Wl,-rpath,{libdir}",
+                        "-ltorch_python", "-ltorch", "-ltorch_cpu", "-lc10", "-lgomp"])
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
+        built.append(out)
+    return built
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--no-ref", action="store_true")
+    ap.add_argument("--force", action="store_true")
+    a = ap.parse_args()
+    build_oracle(force=a.force)
+    if not a.no_ref:
+        got = build_ref(force=a.force)
+        print("reference CPU extensions:", got if got else "reference tree not present, skipped")
+
+
+if __name__ == "__main__":
+    sys.exit(main())

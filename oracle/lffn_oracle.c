@@ -1,0 +1,402 @@
+/*
+ * CPU restatement of the LookupFFN layer (mlpen/LookupFFN,
+ * src/roberta/models/prenorm_lookup/).  TEST INFRASTRUCTURE ONLY: this file is
+ * the checker the CUDA kernels are compared with (tests, the smoke test and
+ * the CPU-baseline leg of the benchmark).  Nothing in the product path calls
+ * it, and the product must fail when the CUDA library is missing rather than
+ * fall back to this code.
+ *
+ * Every function states the reference lines it follows.  All arithmetic is
+ * fp32 with the rounding points spelled out (compile with -ffp-contract=off;
+ * fused multiply-adds are written as fmaf where the CUDA kernels fuse), so
+ * that sign bits -- and therefore hash codes -- can be compared bit for bit.
+ *
+ * Parity is pinned: tests/golden/ holds vectors produced by running the
+ * reference's own Python/C++ code (see tests/golden/make_golden.py) and
+ * tests/test_oracle_golden.py checks this file against them.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define LFFN_BIT_MSB_FIRST 0
+#define LFFN_BIT_LSB_FIRST 1
+#define LFFN_WEIGHT_SCORE 0
+#define LFFN_WEIGHT_ONES 1
+#define LFFN_WEIGHT_SOFT_FLIP 2
+
+static inline float bf16_to_f32(uint16_t h) {
+    uint32_t u = ((uint32_t)h) << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* round-to-nearest-even, NaN kept quiet: what __float2bfloat16_rn does */
+static inline uint16_t f32_to_bf16(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+int lffn_oracle_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+void lffn_oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+/*
+ * Unnormalised Walsh-Hadamard transform of one row, Sylvester ordering
+ * (H as scipy.linalg.hadamard, bh4/fast_hadamard_transform/kernel.py:31-37).
+ * Butterfly order = stride D/2, D/4, ..., 1, the order of the reference's
+ * generic fp32 kernel (bh4/fast_hadamard_transform/extension/cuda_kernel.cu:
+ * 234-252): the lower element of a pair becomes a+b, the upper a-b, one
+ * rounding each.  `scale` (1 = none, as the reference, whose 1/sqrt(D) is
+ * commented out at cuda_kernel.cu:255) is applied with one more rounding.
+ */
+static void fwht_row(float *v, int D, float scale) {
+    for (int stride = D / 2; stride >= 1; stride >>= 1) {
+        for (int base = 0; base < D; base += 2 * stride) {
+            for (int i = base; i < base + stride; i++) {
+                float a = v[i], b = v[i + stride];
+                v[i] = a + b;
+                v[i + stride] = a - b;
+            }
+        }
+    }
+    if (scale != 1.0f)
+        for (int i = 0; i < D; i++) v[i] = v[i] * scale;
+}
+
+/* hadamard(), bh4/fast_hadamard_transform/kernel.py:78-89 : [N, D] -> [N, D] */
+void lffn_oracle_fwht(const float *x, float *out, long N, int D, float scale) {
+#pragma omp parallel for schedule(static)
+    for (long n = 0; n < N; n++) {
+        float *o = out + n * (long)D;
+        if (o != x + n * (long)D) memcpy(o, x + n * (long)D, sizeof(float) * D);
+        fwht_row(o, D, scale);
+    }
+}
+
+/*
+ * LayerNorm over the last dimension (lookup.py:84,99 -> torch.nn.LayerNorm):
+ * biased variance, eps inside the square root.  Accumulated in double, so the
+ * result is the correctly rounded one up to the final fp32 operations; GPU
+ * results are compared with a tolerance, not bit for bit.
+ */
+void lffn_oracle_layernorm(const float *x, const float *gamma, const float *beta, float eps,
+                           float *out, long N, int d) {
+#pragma omp parallel for schedule(static)
+    for (long n = 0; n < N; n++) {
+        const float *r = x + n * (long)d;
+        double s = 0;
+        for (int i = 0; i < d; i++) s += r[i];
+        double mean = s / d, v = 0;
+        for (int i = 0; i < d; i++) v += (r[i] - mean) * (r[i] - mean);
+        double rstd = 1.0 / sqrt(v / d + (double)eps);
+        for (int i = 0; i < d; i++) {
+            float y = (float)((r[i] - mean) * rstd);
+            if (gamma) y = y * gamma[i];
+            if (beta) y = y + beta[i];
+            out[n * (long)d + i] = y;
+        }
+    }
+}
+
+/*
+ * The hashing projection, BH4.forward with the CUDA/training semantics:
+ *   lookup.py:29-39   zero-pad to D, mix, slice to out_dim, add bias
+ *   bh4/kernel.py:23-36   R repeats of S x (block-diagonal multiply, Hadamard)
+ *
+ * x        [N, d_in] fp32 (already layer-normed when the module calls it)
+ * w        [R, S, D/BS, BS, BS] fp32.  BS = 1 is a diagonal (random +-1 signs
+ *          give v = H diag(s2) H diag(s1) x); BS = 64 is the reference BH4.
+ *          transpose_w = 0: y[o] = sum_i y[i] * w[nb][o][i]   ("bni,noi->bno",
+ *          bh4/kernel.py:32); 1: w[nb][i][o] (the CPU extension's convention,
+ *          bh4/cpu/kernel.py:91).
+ * Each dot product is one fmaf chain over i ascending from 0.
+ * z[n, c]  = fl(fl(mix_a * P[n, c]) + fl(mix_b * u_pad[n, c mod D])) + bias[c]
+ *          for c < out_dim, P the concatenation over repeats (lookup.py:36-37;
+ *          reference: mix_a = 0.7, mix_b = 1 - 0.7).
+ */
+void lffn_oracle_project(const float *x, long N, int d_in, int D, const float *w, int BS, int S,
+                         int R, int transpose_w, float had_scale, float mix_a, float mix_b,
+                         const float *bias, int out_dim, float *z) {
+    const int NB = D / BS;
+#pragma omp parallel
+    {
+        float *u = (float *)malloc(sizeof(float) * D);
+        float *y = (float *)malloc(sizeof(float) * D);
+        float *t = (float *)malloc(sizeof(float) * D);
+#pragma omp for schedule(static)
+        for (long n = 0; n < N; n++) {
+            for (int i = 0; i < D; i++) u[i] = i < d_in ? x[n * (long)d_in + i] : 0.0f;
+            for (int r = 0; r < R; r++) {
+                if ((long)r * D >= out_dim) break;
+                memcpy(y, u, sizeof(float) * D);
+                for (int j = 0; j < S; j++) {
+                    const float *wj = w + ((long)(r * S + j)) * NB * BS * BS;
+                    if (BS == 1) {
+                        for (int i = 0; i < D; i++) y[i] = y[i] * wj[i];
+                    } else {
+                        for (int nb = 0; nb < NB; nb++) {
+                            const float *wb = wj + (long)nb * BS * BS;
+                            const float *yb = y + nb * BS;
+                            for (int o = 0; o < BS; o++) {
+                                float acc = 0.0f;
+                                if (!transpose_w)
+                                    for (int i = 0; i < BS; i++) acc = fmaf(yb[i], wb[o * BS + i], acc);
+                                else
+                                    for (int i = 0; i < BS; i++) acc = fmaf(yb[i], wb[i * BS + o], acc);
+                                t[nb * BS + o] = acc;
+                            }
+                        }
+                        memcpy(y, t, sizeof(float) * D);
+                    }
+                    fwht_row(y, D, had_scale);
+                }
+                for (int i = 0; i < D; i++) {
+                    long c = (long)r * D + i;
+                    if (c >= out_dim) break;
+                    float a = mix_a * y[i];
+                    float b = mix_b * u[i];
+                    float v = a + b;
+                    if (bias) v = v + bias[c];
+                    z[n * (long)out_dim + c] = v;
+                }
+            }
+        }
+        free(u);
+        free(y);
+        free(t);
+    }
+}
+
+/* nn.Linear projection (lookup.py:59-60): z = x W^T + b, W [out_dim, d_in]; fmaf chain. */
+void lffn_oracle_project_dense(const float *x, long N, int d_in, const float *w, const float *bias,
+                               int out_dim, float *z) {
+#pragma omp parallel for schedule(static)
+    for (long n = 0; n < N; n++)
+        for (int c = 0; c < out_dim; c++) {
+            float acc = 0.0f;
+            for (int i = 0; i < d_in; i++) acc = fmaf(x[n * (long)d_in + i], w[(long)c * d_in + i], acc);
+            if (bias) acc = acc + bias[c];
+            z[n * (long)out_dim + c] = acc;
+        }
+}
+
+static inline int code_bit(int j, int k, int bit_order) {
+    return bit_order == LFFN_BIT_MSB_FIRST ? (k - 1 - j) : j;
+}
+
+/*
+ * Codes and gather weights from z viewed as [N, T, k].
+ *
+ * code  = sum_j [z_j > 0] << bit(j); strict ">" so 0, -0 and NaN give bit 0.
+ *         MSB-first (bit(j) = k-1-j) is the reference
+ *         (compute_code_score/kernel.py:32-34,47-48, torch_extension.cc:35);
+ *         LSB-first (bit(j) = j) is the other convention in the same repo
+ *         (prenorm_yoso/yoso_kernel/fast_hash/cuda_kernel.cu:76).
+ * weight modes (m = candidates per table):
+ *   SCORE (m=1): sum_j |z_j| / prod_j (1 + exp(-2 |z_j|)), both accumulated
+ *         serially over j (torch_extension.cc:30-40, kernel.py:51-53).
+ *   ONES  (m=1): 1.
+ *   SOFT_FLIP (m=k+1): candidate 0 is the hard code with weight
+ *         prod_j s_j, s_j = 1/(1+exp(-|z_j|/tau)); candidate 1+j flips the bit
+ *         of coordinate j and replaces factor j by (1 - s_j).  No reference
+ *         code exists for this mode; it follows the benchmark specification.
+ * idx_out[n, t*m + c] = code_c + t * 2^k when add_offsets (lookup.py:126),
+ * otherwise the bare code.
+ */
+void lffn_oracle_code_weights(const float *z, long N, int T, int k, int bit_order, int weight_mode,
+                              float tau, int add_offsets, int32_t *idx_out, float *w_out) {
+    const int m = weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
+#pragma omp parallel for schedule(static)
+    for (long n = 0; n < N; n++) {
+        for (int t = 0; t < T; t++) {
+            const float *v = z + (n * (long)T + t) * k;
+            int32_t code = 0;
+            for (int j = 0; j < k; j++)
+                if (v[j] > 0.0f) code |= 1 << code_bit(j, k, bit_order);
+            const int32_t off = add_offsets ? t * (1 << k) : 0;
+            int32_t *io = idx_out + (n * (long)T + t) * m;
+            float *wo = w_out + (n * (long)T + t) * m;
+            if (weight_mode == LFFN_WEIGHT_SCORE) {
+                float num = 0.0f, den = 1.0f;
+                for (int j = 0; j < k; j++) {
+                    float a = fabsf(v[j]);
+                    num = num + a;
+                    den = den * (1.0f + expf(-2.0f * a));
+                }
+                io[0] = code + off;
+                wo[0] = num / den;
+            } else if (weight_mode == LFFN_WEIGHT_ONES) {
+                io[0] = code + off;
+                wo[0] = 1.0f;
+            } else {
+                float s[32];
+                for (int j = 0; j < k; j++) s[j] = 1.0f / (1.0f + expf(-fabsf(v[j]) / tau));
+                for (int c = 0; c <= k; c++) {
+                    float p = 1.0f;
+                    for (int j = 0; j < k; j++) p = p * ((c == j + 1) ? (1.0f - s[j]) : s[j]);
+                    int32_t cc = c == 0 ? code : (code ^ (1 << code_bit(c - 1, k, bit_order)));
+                    io[c] = cc + off;
+                    wo[c] = p;
+                }
+            }
+        }
+    }
+}
+
+/*
+ * Weighted gather-add: out[n, :] = sum_i w[n, i] * tables[idx[n, i], :] (+ bias)
+ * (gather/cuda/kernel.py:45-56; gather/cuda/extension/gather_kernel_fp32.cu:
+ * 37-45; gather/cpu/torch_extension.cpp:34-42; bias: lookup.py:108).
+ * Per output column one fmaf chain over i ascending from 0, then one rounded
+ * add of the bias, then (bf16 output) one rounding to bf16.
+ * table_bf16 / out_bf16 select 16-bit storage (raw uint16 bit patterns).
+ * Returns the number of indices outside [0, S); those rows are skipped.
+ */
+long lffn_oracle_gather(const int32_t *idx, const float *w, const void *tables, int table_bf16,
+                        void *out, int out_bf16, long N, int I, long S, int d, const float *bias) {
+    long bad = 0;
+#pragma omp parallel reduction(+ : bad)
+    {
+        float *acc = (float *)malloc(sizeof(float) * d);
+#pragma omp for schedule(static)
+        for (long n = 0; n < N; n++) {
+            for (int c = 0; c < d; c++) acc[c] = 0.0f;
+            for (int i = 0; i < I; i++) {
+                long r = idx[n * (long)I + i];
+                if (r < 0 || r >= S) {
+                    bad++;
+                    continue;
+                }
+                float ww = w[n * (long)I + i];
+                if (table_bf16) {
+                    const uint16_t *row = (const uint16_t *)tables + r * d;
+                    for (int c = 0; c < d; c++) acc[c] = fmaf(ww, bf16_to_f32(row[c]), acc[c]);
+                } else {
+                    const float *row = (const float *)tables + r * d;
+                    for (int c = 0; c < d; c++) acc[c] = fmaf(ww, row[c], acc[c]);
+                }
+            }
+            for (int c = 0; c < d; c++) {
+                float v = acc[c];
+                if (bias) v = v + bias[c];
+                if (out_bf16)
+                    ((uint16_t *)out)[n * (long)d + c] = f32_to_bf16(v);
+                else
+                    ((float *)out)[n * (long)d + c] = v;
+            }
+        }
+        free(acc);
+    }
+    return bad;
+}
+
+/*
+ * Gradient of the gather with respect to the weights:
+ * dw[n, i] = <dy[n, :], tables[idx[n, i], :]>  (gather/cuda/kernel.py:95-107,
+ * gather_kernel_fp32.cu:94-157).  Accumulated in double; GPU results are
+ * compared with a tolerance.
+ */
+void lffn_oracle_gather_bwd_weights(const int32_t *idx, const float *dy, const void *tables,
+                                    int table_bf16, float *dw, long N, int I, long S, int d) {
+#pragma omp parallel for schedule(static)
+    for (long n = 0; n < N; n++) {
+        const float *g = dy + n * (long)d;
+        for (int i = 0; i < I; i++) {
+            long r = idx[n * (long)I + i];
+            double s = 0;
+            if (r >= 0 && r < S) {
+                if (table_bf16) {
+                    const uint16_t *row = (const uint16_t *)tables + r * d;
+                    for (int c = 0; c < d; c++) s += (double)g[c] * bf16_to_f32(row[c]);
+                } else {
+                    const float *row = (const float *)tables + r * d;
+                    for (int c = 0; c < d; c++) s += (double)g[c] * row[c];
+                }
+            }
+            dw[n * (long)I + i] = (float)s;
+        }
+    }
+}
+
+/*
+ * Gradient with respect to the tables (scatter-add):
+ * dtables[idx[n, i], :] += w[n, i] * dy[n, :]  (gather/cuda/kernel.py:149-156,
+ * gather_kernel_fp32.cu:84-90), dtables zero-initialised here.  Per element one
+ * fmaf chain over (n, i) in ascending order, the order the sorted CUDA kernel
+ * also uses, so fp32 results compare bit for bit with it.
+ */
+void lffn_oracle_gather_bwd_tables(const int32_t *idx, const float *w, const float *dy,
+                                   float *dtables, long N, int I, long S, int d) {
+    memset(dtables, 0, sizeof(float) * (size_t)S * d);
+    const int CH = 64;
+#pragma omp parallel for schedule(static)
+    for (int c0 = 0; c0 < d; c0 += CH) {
+        int c1 = c0 + CH < d ? c0 + CH : d;
+        for (long n = 0; n < N; n++) {
+            const float *g = dy + n * (long)d;
+            for (int i = 0; i < I; i++) {
+                long r = idx[n * (long)I + i];
+                if (r < 0 || r >= S) continue;
+                float ww = w[n * (long)I + i];
+                float *row = dtables + r * d;
+                for (int c = c0; c < c1; c++) row[c] = fmaf(ww, g[c], row[c]);
+            }
+        }
+    }
+}
+
+/*
+ * The whole layer, eval forward (lookup.py:98-129): optional LayerNorm ->
+ * projection -> codes/weights -> gather -> + bias.  Scratch is allocated here.
+ * Used by the CPU-baseline timing and the end-to-end parity tests.
+ */
+long lffn_oracle_layer_fwd(const float *x, long N, int d_in, const float *ln_w, const float *ln_b,
+                           float ln_eps, int use_ln, int D, const float *proj_w, int BS, int S,
+                           int R, int transpose_w, float had_scale, float mix_a, float mix_b,
+                           const float *proj_bias, int T, int k, int bit_order, int weight_mode,
+                           float tau, const void *tables, int table_bf16, int d_out,
+                           const float *bias, void *out, int out_bf16) {
+    const int m = weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
+    const int out_dim = T * k;
+    float *u = NULL;
+    if (use_ln) {
+        u = (float *)malloc(sizeof(float) * (size_t)N * d_in);
+        lffn_oracle_layernorm(x, ln_w, ln_b, ln_eps, u, N, d_in);
+    }
+    float *z = (float *)malloc(sizeof(float) * (size_t)N * out_dim);
+    int32_t *idx = (int32_t *)malloc(sizeof(int32_t) * (size_t)N * T * m);
+    float *w = (float *)malloc(sizeof(float) * (size_t)N * T * m);
+    lffn_oracle_project(use_ln ? u : x, N, d_in, D, proj_w, BS, S, R, transpose_w, had_scale, mix_a,
+                        mix_b, proj_bias, out_dim, z);
+    lffn_oracle_code_weights(z, N, T, k, bit_order, weight_mode, tau, 1, idx, w);
+    long bad = lffn_oracle_gather(idx, w, tables, table_bf16, out, out_bf16, N, T * m,
+                                  (long)T << k, d_out, bias);
+    free(u);
+    free(z);
+    free(idx);
+    free(w);
+    return bad;
+}
