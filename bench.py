@@ -1,0 +1,392 @@
+#!/usr/bin/env python
+"""Benchmark of the LookupFFN layer forward (hash -> gather-add) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c1|c2|c5k8] [--impl ours|reference]
+
+One "step" = one pass of the layer forward over one batch of synthetic tokens.  Default workload
+"c3": N = 65536 tokens per GPU, d = 768 (zero-padded to D = 1024), T = 512 tables of 2^8 rows,
+bf16 x / tables / y, fp32 accumulation, projection v = H diag(s2) H diag(s1) x with seeded +-1
+diagonals (4 rotations), reference score weights, MSB-first codes.  For N GPUs the tokens are
+partitioned (each rank its own N tokens, tables replicated, no collective): weak scaling.
+
+Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM; `e2e` = the same
+through the host-buffer C-ABI call (pinned host x in, pinned host y out, copies inside the timed
+region); `roofline` = the gather kernel's algorithmic bytes per launch over its CUDA-event time;
+`cpu_baseline` = the reference's CPU path timed on this box's host cores on a bounded sample.
+`--impl reference` times only that CPU path.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+WORKLOADS = {
+    # name: N per GPU, d_in, d_out, T, k, storage dtype, projection, weight_mode, bit_order
+    "c1": dict(N=4096, d_in=512, d_out=512, T=128, k=8, dtype="f32", weight_mode="ones", bit_order="lsb"),
+    "c2": dict(N=16384, d_in=512, d_out=512, T=256, k=8, dtype="f32", weight_mode="score", bit_order="msb"),
+    "c3": dict(N=65536, d_in=768, d_out=768, T=512, k=8, dtype="bf16", weight_mode="score", bit_order="msb"),
+    "c5k8": dict(N=262144, d_in=1024, d_out=1024, T=256, k=8, dtype="bf16", weight_mode="score", bit_order="msb"),
+}
+# DRAM bytes per gather launch of workload c3 from one ncu capture (dram__bytes_read.sum +
+# dram__bytes_write.sum; see profiles/).  None until captured.
+NCU_TRAFFIC_BYTES = {"c3": None}
+
+
+def padded_dim(d):
+    return 1 << int(np.ceil(np.log2(d)))
+
+
+def algorithmic_bytes_per_token(w):
+    eb = 2 if w["dtype"] == "bf16" else 4
+    # every gathered row once per use + x in + y out; codes/weights not counted
+    return w["T"] * w["d_out"] * eb + w["d_in"] * eb + w["d_out"] * eb
+
+
+def load_peaks():
+    p = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---- clocks ------------------------------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every 100 ms."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                r = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.1)
+
+    def result(self):
+        self.stop_flag.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+# ---- synthetic workload ----------------------------------------------------------------------------
+def make_inputs(w, device, seed):
+    """Seeded synthetic stand-ins for the pre-training activations and trained tables: x ~ N(0,1),
+    tables ~ N(0, 0.02), +-1 diagonals; the same on every rank except x (rank-specific tokens)."""
+    dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
+    D = padded_dim(w["d_in"])
+    R = max(1, -(-w["T"] * w["k"] // D))
+    g = torch.Generator(device=device).manual_seed(1234)
+    tables = (0.02 * torch.randn(w["T"] << w["k"], w["d_out"], generator=g, device=device)).to(dt)
+    signs = (2 * torch.randint(0, 2, (R, 2, D, 1, 1), generator=g, device=device) - 1).float()
+    bias = torch.zeros(w["d_out"], device=device)
+    gx = torch.Generator(device=device).manual_seed(1000 + seed)
+    x = torch.randn(w["N"], w["d_in"], generator=gx, device=device).to(dt)
+    return x, tables, signs, bias, D, R
+
+
+def run_ours(args, rank, world, local):
+    from lookupffn_b200 import _lib as L
+    from lookupffn_b200 import ops
+
+    w = WORKLOADS[args.workload]
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    lib = L.lib()
+    x, tables, signs, bias, D, R = make_inputs(w, device, rank)
+    N, T, k = w["N"], w["T"], w["k"]
+    dt = x.dtype
+    dcode = L.dtype_code(dt)
+    wm = {"score": L.WEIGHT_SCORE, "ones": L.WEIGHT_ONES}[w["weight_mode"]]
+    bo = {"msb": L.MSB_FIRST, "lsb": L.LSB_FIRST}[w["bit_order"]]
+    desc = ops.make_hash_desc(w["d_in"], signs, None, T, k, had_scale=float(1.0 / np.sqrt(D)), mix_a=1.0, mix_b=0.0,
+                              bit_order=bo, weight_mode=wm)
+    idx = torch.empty((N, T), dtype=torch.int32, device=device)
+    wgt = torch.empty((N, T), dtype=torch.float32, device=device)
+    y = torch.empty((N, w["d_out"]), dtype=dt, device=device)
+    stream = torch.cuda.current_stream(device)
+    sp = C.c_void_p(stream.cuda_stream)
+
+    def step(ev=None):
+        if ev is not None:
+            ev[0].record(stream)
+        L.check(lib.lffn_hash_fwd(C.byref(desc), L.ptr(x), dcode, N, 0, T, L.ptr(idx), L.ptr(wgt), None, sp))
+        if ev is not None:
+            ev[1].record(stream)
+        L.check(lib.lffn_gather_fwd(L.ptr(idx), L.ptr(wgt), L.ptr(tables), dcode, L.ptr(y), dcode, N, T, T << k,
+                                    w["d_out"], L.ptr(bias), sp))
+        if ev is not None:
+            ev[2].record(stream)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(physical_gpu_index(local))
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record(stream)
+    for s in range(args.steps):
+        step(events[s])
+    t_end.record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    elapsed_ms = t_start.elapsed_time(t_end)
+    clocks = sampler.result()
+    hash_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in events)
+    gather_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in events)
+    status = L.device_status(device)
+
+    # ---- end to end through the host-buffer entry point -------------------------------------------
+    chunk = args.e2e_chunk
+    ws_bytes = lib.lffn_layer_fwd_host_ws_bytes(C.byref(desc), dcode, dcode, w["d_out"], chunk)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+    x_host = torch.empty(x.shape, dtype=dt).pin_memory()
+    x_host.copy_(x)
+    y_host = torch.empty(y.shape, dtype=dt).pin_memory()
+
+    def e2e_step():
+        L.check(lib.lffn_layer_fwd_host(C.byref(desc), L.ptr(x_host), dcode, N, L.ptr(tables), dcode, w["d_out"],
+                                        L.ptr(bias), L.ptr(y_host), dcode, L.ptr(ws), ws_bytes, chunk, sp))
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ok = bool(torch.equal(y_host.view(torch.int16) if dt == torch.bfloat16 else y_host,
+                              y.cpu().view(torch.int16) if dt == torch.bfloat16 else y.cpu()))
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()  # synchronous: returns when y_host is complete
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+
+    if world > 1:
+        t = torch.tensor([elapsed_ms, e2e_s, gather_ms, hash_ms], dtype=torch.float64, device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        elapsed_ms, e2e_s, gather_ms, hash_ms = (float(v) for v in t.tolist())
+
+    if rank != 0:
+        return None
+    eb = 2 if w["dtype"] == "bf16" else 4
+    alg = algorithmic_bytes_per_token(w)
+    peak, peak_kind = load_peaks()
+    achieved = alg * N / (gather_ms * 1e-3) / 1e9
+    chunks = -(-N // chunk)
+    out = {
+        "metric": "lookupffn_layer_forward_throughput", "value": world * N * args.steps / (elapsed_ms * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": f"{args.workload}: LookupFFN layer forward, N={N} tokens per GPU, d={w['d_in']}->D={D}, "
+                               f"T={T}, k={k}, d_out={w['d_out']}, {w['dtype']} x/tables/y, fp32 accumulate",
+                   "projection": f"sign-diagonal Hadamard, R={R} rotations x 2 stages, normalised",
+                   "weights": w["weight_mode"], "bit_order": w["bit_order"], "sharding": f"tokens x{world}, tables replicated",
+                   "l2": "inputs larger than L2: tables %.0f MB + idx/w %.0f MB + x/y %.0f MB per step" % (
+                       tables.numel() * eb / 1e6, N * T * 8 / 1e6, 2 * N * w["d_in"] * eb / 1e6)},
+        "kernels_ms": {"hash_fwd": hash_ms, "gather_fwd": gather_ms},
+        "roofline": {"bound": "hbm", "kernel": "gather_fwd_kernel", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
+                     "algorithmic_bytes_per_token": alg, "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
+        "e2e": {"value": world * N * args.steps / e2e_s, "unit": "tokens/s",
+                "h2d_bytes_per_step": N * w["d_in"] * eb, "d2h_bytes_per_step": N * w["d_out"] * eb,
+                "api": "lffn_layer_fwd_host (pinned host x -> pinned host y)", "chunk_tokens": chunk,
+                "matches_device_path": e2e_ok},
+        "gpu_launches": 2 * args.steps + 2 * chunks * args.steps,
+        "clocks": clocks, "device_status": status,
+    }
+    return out
+
+
+# ---- the reference's CPU path, on this box's host cores ---------------------------------------------------
+def load_ref_modules():
+    """The reference's own CPU extensions compiled (unmodified) into oracle/_ref, or None."""
+    import importlib.util
+
+    from oracle import build as obuild
+
+    mods = {}
+    for name in ("ccs_cpu", "gather_add_cpu"):
+        path = obuild.ref_module_path(name)
+        if not os.path.exists(path):
+            return None
+        spec = importlib.util.spec_from_file_location(name, path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mods[name] = mod
+    return mods
+
+
+def cpu_path(args, budget_s):
+    """Times the layer forward on the host: projection = CPU restatement (the reference's CPU BH4 needs
+    libxsmm, which is not available), code+score and gather = the reference's own C++ extensions when
+    oracle/_ref holds them, else the oracle port.  Sample: `cpu_tokens` tokens of the same workload,
+    fp32 copies of the tables (the reference's CPU kernels are fp32 only)."""
+    from oracle import oracle as O
+
+    w = WORKLOADS[args.workload]
+    Ns = args.cpu_tokens
+    T, k, D = w["T"], w["k"], padded_dim(w["d_in"])
+    R = max(1, -(-T * k // D))
+    rng = np.random.RandomState(7)
+    x = rng.randn(Ns, w["d_in"]).astype(np.float32)
+    tables = (0.02 * rng.randn(T << k, w["d_out"])).astype(np.float32)
+    signs = (2.0 * rng.randint(0, 2, size=(R, 2, D, 1, 1)) - 1.0).astype(np.float32)
+    cores = os.cpu_count()
+    torch.set_num_threads(cores)
+    O.set_threads(cores)
+    ref = load_ref_modules()
+    kind = "reference" if ref is not None else "port"
+    hs = float(1.0 / np.sqrt(D))
+    offsets = (torch.arange(T, dtype=torch.int32) << k)[None]
+    tt = torch.from_numpy(tables)
+
+    def one():
+        z = O.project(x, signs, T * k, had_scale=hs, mix_a=1.0, mix_b=0.0)
+        if ref is not None:
+            zt = torch.from_numpy(z).reshape(Ns, T, k)
+            codes = torch.empty(Ns, T, dtype=torch.int32)
+            scores = torch.empty(Ns, T, dtype=torch.float32)
+            ref["ccs_cpu"].compute_code_score(zt, codes, scores)
+            return ref["gather_add_cpu"].weighted_vector_gather_add_avx2_par(codes + offsets, tt, scores)
+        idx, wg = O.code_weights(z, T, k)
+        return O.gather(idx, wg, tables)
+
+    one()
+    times = []
+    t_all = time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - t_all < budget_s and len(times) < 50):
+        t0 = time.perf_counter()
+        one()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return {"value": Ns / med, "unit": "tokens/s", "cores": cores, "kind": kind,
+            "sample": f"{Ns} tokens of workload {args.workload} (fp32 tables), median of {len(times)} passes; "
+                      f"projection = C restatement, code+score and gather = "
+                      f"{'reference C++ extensions (oracle/_ref)' if ref is not None else 'oracle port'}",
+            "ms_per_pass": med * 1e3}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return None
+    w = WORKLOADS[args.workload]
+    D = padded_dim(w["d_in"])
+    per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    base = None
+    vals = []
+    for i in range(args.warmup + args.steps):
+        base = cpu_path(args, per_step)
+        if i >= args.warmup:
+            vals.append(base["value"])
+    v = statistics.median(vals)
+    base = dict(base, value=v)
+    return {
+        "impl": "reference", "metric": "lookupffn_layer_forward_throughput", "value": v, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": args.cpu_tokens / v * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: LookupFFN layer forward, CPU path on host cores, bounded sample of "
+                               f"{args.cpu_tokens} tokens per step, d={w['d_in']}->D={D}, T={w['T']}, k={w['k']}"},
+        "cpu_baseline": base,
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-chunk", type=int, default=8192)
+    ap.add_argument("--cpu-tokens", type=int, default=4096)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        out = run_reference(args, rank, world)
+        if out is not None:
+            print(json.dumps(out), flush=True)
+        return 0
+
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+    out = run_ours(args, rank, world, local)
+    if out is not None:
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_path(args, 15.0)
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

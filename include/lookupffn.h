@@ -1,0 +1,197 @@
+/*
+ * lookupffn.h -- C ABI of liblookupffn.so, the sm_100a implementation of the
+ * LookupFFN layer's hot path (hash projection -> codes/weights -> weighted
+ * gather-add, and the gather's backward).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller unless the name ends
+ *     in _host; nothing is allocated behind the caller's back unless a function
+ *     says so; buffers are dense row-major.
+ *   - every function returns LFFN_OK (0) or a negative LFFN_ERR_* code and never
+ *     aborts; lffn_last_error_string() gives the message for the calling thread.
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the
+ *     legacy default stream) and is asynchronous unless stated otherwise.
+ *   - paths below are relative to src/roberta/models/prenorm_lookup/ of
+ *     mlpen/LookupFFN; each entry point names the reference interface it replaces.
+ */
+#ifndef LOOKUPFFN_H_
+#define LOOKUPFFN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LFFN_VERSION 100
+
+#define LFFN_OK 0
+#define LFFN_ERR_INVALID_ARG (-1) /* null pointer, non-positive size, bad enum            */
+#define LFFN_ERR_UNSUPPORTED (-2) /* a shape the kernels do not cover (message says which) */
+#define LFFN_ERR_CUDA (-3)        /* a CUDA runtime call or launch failed                  */
+#define LFFN_ERR_INDEX_RANGE (-4) /* device status word reports an index outside [0, S)   */
+#define LFFN_ERR_SCRATCH (-5)     /* scratch buffer missing or too small                   */
+
+/* storage types */
+#define LFFN_F32 0
+#define LFFN_BF16 1
+
+/* bit order of a code: MSB first is the reference (compute_code_score/kernel.py:32-34,
+ * torch_extension.cc:35); LSB first is code = sum_j [v_j > 0] << j. */
+#define LFFN_BIT_MSB_FIRST 0
+#define LFFN_BIT_LSB_FIRST 1
+
+/* how gather weights are derived from the projection z[t, 0..k) */
+#define LFFN_WEIGHT_SCORE 0     /* sum|z| / prod(1 + exp(-2|z|))  (compute_code_score/kernel.py:51-53) */
+#define LFFN_WEIGHT_ONES 1      /* 1                                                                   */
+#define LFFN_WEIGHT_SOFT_FLIP 2 /* k+1 candidates per table: hard code and its k single-bit flips,
+                                   weights prod_j sigma(|z_j|/tau) with factor j replaced by
+                                   1 - sigma(|z_j|/tau) for flip j                                    */
+
+/* bits of the device status word (lffn_device_status) */
+#define LFFN_STATUS_INDEX_RANGE 1u /* a gather/scatter index was outside [0, S); the row was skipped */
+#define LFFN_STATUS_STRUCTURE 2u   /* an index left its table's row range in the sorted backward     */
+
+typedef void *lffn_stream_t;
+
+/*
+ * Description of the hashing stage = modules BH4 + Hashing (lookup.py:10-77) with the
+ * CUDA/training semantics of bh4_cuda (bh4/kernel.py:23-36):
+ *   u      = x zero-padded from d_in to D columns (D a power of two, 64 <= D <= 2048)
+ *   y_r    = u; repeat S times { y_r <- blockdiag(w[r, j]) y_r ; y_r <- H_D y_r * had_scale }
+ *   z      = fl(fl(mix_a * concat_r y_r) + fl(mix_b * tile(u, R)))[:, :T*k] + proj_bias
+ *   codes and weights from z viewed as [T, k]
+ * proj_w is [R, S, D/BS, BS, BS] fp32.  BS = 1 is a diagonal (random +-1 entries give
+ * H diag(s2) H diag(s1) x for S = 2); BS = 64, S = 4, mix 0.7/0.3, had_scale 1 is the reference.
+ * transpose_w = 0 multiplies by w[nb][o][i] ("bni,noi->bno", bh4/kernel.py:32), 1 by w[nb][i][o]
+ * (the convention of the reference's CPU extension, bh4/cpu/kernel.py:91).
+ * H is the unnormalised Sylvester matrix; butterflies run from stride D/2 down to 1, the order
+ * of bh4/fast_hadamard_transform/extension/cuda_kernel.cu:234-252, so sign bits reproduce.
+ */
+typedef struct lffn_hash_desc {
+    int32_t d_in;
+    int32_t D;
+    int32_t BS;
+    int32_t S;
+    int32_t R;
+    int32_t transpose_w;
+    float had_scale;
+    float mix_a;
+    float mix_b;
+    int32_t T; /* number of tables of the whole layer */
+    int32_t k; /* code length, table has 2^k rows, 1 <= k <= 16 */
+    int32_t bit_order;
+    int32_t weight_mode;
+    float tau;
+    const float *proj_w;
+    const float *proj_bias; /* [T*k] or NULL */
+} lffn_hash_desc;
+
+int lffn_version(void);
+const char *lffn_last_error_string(void);
+
+/* Reads and clears the status word of the current device (synchronises `stream`). */
+int lffn_device_status(uint32_t *status_out, lffn_stream_t stream);
+
+/*
+ * Walsh-Hadamard transform of each row, out = x H_D * scale.  Replaces
+ * fast_hadamard_transform_kernel.fast_hadamard_transform(inp)
+ * (bh4/fast_hadamard_transform/extension/torch_extension.cpp:5-32, kernel.py:39-44,78-89).
+ * x, out: [N, D] of `dtype` (LFFN_F32 or LFFN_BF16, arithmetic in fp32); in place allowed.
+ */
+int lffn_fwht(const void *x, void *out, int64_t N, int32_t D, int32_t dtype, float scale, lffn_stream_t stream);
+
+/*
+ * Hashing stage for tables [t_begin, t_begin + t_count): replaces
+ * Hashing.forward = BH4.forward + compute_code_score (lookup.py:64-77, bh4/kernel.py:10-36,
+ * compute_code_score/kernel.py:22-55) plus the table offsets of LookupFFN.gather (lookup.py:126).
+ *   x        [N, d_in] of x_dtype
+ *   idx_out  int32 [N, t_count*m]  row index = code + (t - t_begin) * 2^k  (m = 1, or k+1 for SOFT_FLIP)
+ *   w_out    fp32  [N, t_count*m]
+ *   z_out    fp32  [N, t_count*k] or NULL: the projected coordinates, for diagnostics and backward
+ * idx_out and w_out may both be NULL when only z_out is wanted (the projection alone = bh4(x, w),
+ * bh4/kernel.py:10-21, with mix_a = 1, mix_b = 0, no bias, k = 1, T = R*D).
+ */
+int lffn_hash_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, int32_t t_begin,
+                  int32_t t_count, int32_t *idx_out, float *w_out, float *z_out, lffn_stream_t stream);
+
+/*
+ * Codes and weights from already projected coordinates z [N, T, k] fp32: replaces
+ * compute_code_score(hash_scores, training) (compute_code_score/kernel.py:22-30) and
+ * ccs_cpu.compute_code_score (torch_extension.cc:14-42).  add_offsets adds t * 2^k (lookup.py:126).
+ */
+int lffn_code_weights(const float *z, int64_t N, int32_t T, int32_t k, int32_t bit_order, int32_t weight_mode,
+                      float tau, int32_t add_offsets, int32_t *idx_out, float *w_out, lffn_stream_t stream);
+
+/*
+ * out[n, :] = sum_i w[n, i] * tables[idx[n, i], :] (+ bias): replaces
+ * gather_add.weighted_vector_gather_add_fp32/_fp16 (gather/cuda/extension/torch_extension.cpp:6-33,
+ * gather/cuda/kernel.py:22-70) and gather_add_cpu.weighted_vector_gather_add_* (gather/cpu/
+ * torch_extension.cpp:17-96), with `+ bias` of lookup.py:108 folded in.
+ *   idx int32 [N, I], w fp32 [N, I], tables [S, d] of table_dtype, out [N, d] of out_dtype.
+ * d must be a multiple of 4 (fp32 tables) or 8 (bf16 tables).  out need not be zeroed.
+ * Accumulation is fp32, one fused multiply-add per row in index order.  Indices outside [0, S)
+ * are skipped and flagged in the device status word.
+ */
+int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype, void *out,
+                    int32_t out_dtype, int64_t N, int32_t I, int64_t S, int32_t d, const float *bias,
+                    lffn_stream_t stream);
+
+/*
+ * dw[n, i] = <dy[n, :], tables[idx[n, i], :]>: replaces gather_add.indexed_inner_product_fp32/_fp16
+ * (gather/cuda/extension/torch_extension.cpp:35-62, gather/cuda/kernel.py:72-122).
+ * dy fp32 [N, d]; dw fp32 [N, I].
+ */
+int lffn_gather_bwd_weights(const int32_t *idx, const float *dy, const void *tables, int32_t table_dtype, float *dw,
+                            int64_t N, int32_t I, int64_t S, int32_t d, lffn_stream_t stream);
+
+/*
+ * dtables[idx[n, i], :] += w[n, i] * dy[n, :] with dtables [S, d] fp32 zeroed first by this call:
+ * replaces gather_add.weighted_vector_scatter_add_fp32/_fp16 (gather/cuda/extension/
+ * torch_extension.cpp:64-91, gather/cuda/kernel.py:124-173).  Any index list; uses vector
+ * reductions in L2, so the summation order (not the set of terms) varies between runs.
+ */
+int lffn_gather_bwd_tables(const int32_t *idx, const float *w, const float *dy, float *dtables, int64_t N, int32_t I,
+                           int64_t S, int32_t d, lffn_stream_t stream);
+
+/*
+ * Same result, deterministic and without atomics on the output, for index lists with the layer's
+ * structure: I = T * m entries per token and idx[n, t*m + c] in [t * rows, (t+1) * rows).
+ * Entries are counting-sorted per table into `scratch`, then every output row is summed in
+ * ascending (n, c) order and written once.  lffn_gather_bwd_tables_sorted_scratch_bytes gives
+ * the scratch size.  An entry outside its table's range is dropped and flagged (LFFN_STATUS_STRUCTURE).
+ */
+size_t lffn_gather_bwd_tables_sorted_scratch_bytes(int64_t N, int32_t T, int32_t m, int32_t rows);
+int lffn_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const float *dy, float *dtables, int64_t N,
+                                  int32_t T, int32_t m, int32_t rows, int32_t d, void *scratch,
+                                  size_t scratch_bytes, lffn_stream_t stream);
+
+/*
+ * Whole layer forward on device buffers = LookupFFN._forward without LayerNorm (lookup.py:101-110):
+ * hash -> gather -> + bias for tables [t_begin, t_begin + t_count) (`tables` points at the first
+ * of those, [t_count * 2^k, d_out]).  idx_ws/w_ws are caller-provided workspaces of
+ * N * t_count * m int32 / fp32.
+ */
+int lffn_layer_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, int32_t t_begin,
+                   int32_t t_count, const void *tables, int32_t table_dtype, int32_t d_out, const float *bias,
+                   void *out, int32_t out_dtype, int32_t *idx_ws, float *w_ws, lffn_stream_t stream);
+
+/*
+ * The same forward for callers that hold HOST buffers (the shape of the reference's CPU
+ * inference path, compare.py:23-37): x_host [N, d_in] and out_host [N, d_out] are host pointers
+ * (pinned memory makes the copies asynchronous).  Tokens are cut into chunks; the copy-in of
+ * chunk c+1 and the copy-out of chunk c-1 overlap the kernels of chunk c.  Parameters
+ * (desc->proj_w, proj_bias, tables, bias) stay on the device.  `ws` is a device workspace of
+ * lffn_layer_fwd_host_ws_bytes(...) bytes.  Synchronous: returns when out_host is complete.
+ */
+size_t lffn_layer_fwd_host_ws_bytes(const lffn_hash_desc *desc, int32_t x_dtype, int32_t out_dtype, int32_t d_out,
+                                    int64_t chunk_tokens);
+int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t x_dtype, int64_t N,
+                        const void *tables, int32_t table_dtype, int32_t d_out, const float *bias, void *out_host,
+                        int32_t out_dtype, void *ws, size_t ws_bytes, int64_t chunk_tokens, lffn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOOKUPFFN_H_ */

@@ -1,0 +1,296 @@
+// extern "C" entry points of liblookupffn.so (declared in include/lookupffn.h): argument checks,
+// error strings, the device status word, and the two whole-layer drivers.
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace lffn {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+    set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return LFFN_ERR_CUDA;
+}
+
+constexpr int MAX_DEV = 64;
+
+int num_sms() {
+    static int cache[MAX_DEV] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return 148;
+    if (cache[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cache[dev] = n;
+    }
+    return cache[dev];
+}
+
+// The status word is a __device__ variable (one per device that loads the library), not an
+// allocation: kernels OR flags into it, lffn_device_status reads and clears it.
+__device__ uint32_t g_status_word = 0;
+
+uint32_t *status_word() {
+    static uint32_t *cache[MAX_DEV] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return nullptr;
+    if (cache[dev] == nullptr) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+        cache[dev] = static_cast<uint32_t *>(p);
+    }
+    return cache[dev];
+}
+
+static int check_hash_desc(const lffn_hash_desc *h, int t_begin, int t_count) {
+    LFFN_REQUIRE(h != nullptr, LFFN_ERR_INVALID_ARG, "hash descriptor is NULL");
+    LFFN_REQUIRE(h->proj_w != nullptr, LFFN_ERR_INVALID_ARG, "hash descriptor: proj_w is NULL");
+    LFFN_REQUIRE(h->d_in >= 1 && h->D >= h->d_in && (h->D & (h->D - 1)) == 0, LFFN_ERR_INVALID_ARG,
+                 "hash descriptor: need 1 <= d_in (%d) <= D (%d), D a power of two", h->d_in, h->D);
+    LFFN_REQUIRE(h->D >= 64 && h->D <= 2048, LFFN_ERR_UNSUPPORTED, "hash: D = %d outside [64, 2048]", h->D);
+    LFFN_REQUIRE(h->k >= 1 && h->k <= 16, LFFN_ERR_UNSUPPORTED, "hash: code length k = %d outside [1, 16]", h->k);
+    LFFN_REQUIRE(h->T >= 1 && h->S >= 1 && h->R >= 1, LFFN_ERR_INVALID_ARG, "hash descriptor: T, S, R must be >= 1");
+    LFFN_REQUIRE((long long)h->R * h->D >= (long long)h->T * h->k, LFFN_ERR_INVALID_ARG,
+                 "hash descriptor: R*D = %lld < T*k = %lld", (long long)h->R * h->D, (long long)h->T * h->k);
+    LFFN_REQUIRE(h->BS >= 1 && h->D % h->BS == 0, LFFN_ERR_INVALID_ARG, "hash descriptor: BS = %d does not divide D",
+                 h->BS);
+    LFFN_REQUIRE(h->bit_order == LFFN_BIT_MSB_FIRST || h->bit_order == LFFN_BIT_LSB_FIRST, LFFN_ERR_INVALID_ARG,
+                 "hash descriptor: bit_order %d", h->bit_order);
+    LFFN_REQUIRE(h->weight_mode >= LFFN_WEIGHT_SCORE && h->weight_mode <= LFFN_WEIGHT_SOFT_FLIP, LFFN_ERR_INVALID_ARG,
+                 "hash descriptor: weight_mode %d", h->weight_mode);
+    LFFN_REQUIRE(h->weight_mode != LFFN_WEIGHT_SOFT_FLIP || h->tau > 0.f, LFFN_ERR_INVALID_ARG,
+                 "hash descriptor: tau must be > 0 for soft-flip weights");
+    LFFN_REQUIRE(t_begin >= 0 && t_count >= 1 && t_begin + t_count <= h->T, LFFN_ERR_INVALID_ARG,
+                 "table range [%d, %d) outside [0, %d)", t_begin, t_begin + t_count, h->T);
+    return LFFN_OK;
+}
+
+static int check_gather(int64_t N, int I, int64_t S, int d, int table_dtype) {
+    LFFN_REQUIRE(N >= 0 && I >= 0 && S >= 1 && d >= 1, LFFN_ERR_INVALID_ARG, "gather: bad sizes N=%lld I=%d S=%lld d=%d",
+                 (long long)N, I, (long long)S, d);
+    LFFN_REQUIRE(table_dtype == LFFN_F32 || table_dtype == LFFN_BF16, LFFN_ERR_INVALID_ARG, "gather: table dtype %d",
+                 table_dtype);
+    const int per = table_dtype == LFFN_F32 ? 4 : 8;
+    LFFN_REQUIRE(d % per == 0, LFFN_ERR_UNSUPPORTED, "gather: d = %d must be a multiple of %d for this table dtype", d,
+                 per);
+    LFFN_REQUIRE(S < (1ll << 31), LFFN_ERR_UNSUPPORTED, "gather: S = %lld rows do not fit int32 indices", (long long)S);
+    return LFFN_OK;
+}
+
+static int aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace lffn
+
+using namespace lffn;
+
+extern "C" {
+
+int lffn_version(void) { return LFFN_VERSION; }
+
+const char *lffn_last_error_string(void) { return g_err; }
+
+int lffn_device_status(uint32_t *status_out, lffn_stream_t stream) {
+    LFFN_REQUIRE(status_out != nullptr, LFFN_ERR_INVALID_ARG, "status_out is NULL");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint32_t *dev = status_word();
+    LFFN_REQUIRE(dev != nullptr, LFFN_ERR_CUDA, "no CUDA device");
+    LFFN_CHECK_CUDA(cudaMemcpyAsync(status_out, dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    LFFN_CHECK_CUDA(cudaMemsetAsync(dev, 0, sizeof(uint32_t), st));
+    LFFN_CHECK_CUDA(cudaStreamSynchronize(st));
+    return LFFN_OK;
+}
+
+int lffn_fwht(const void *x, void *out, int64_t N, int32_t D, int32_t dtype, float scale, lffn_stream_t stream) {
+    LFFN_REQUIRE(x != nullptr && out != nullptr, LFFN_ERR_INVALID_ARG, "fwht: NULL buffer");
+    LFFN_REQUIRE(N >= 0, LFFN_ERR_INVALID_ARG, "fwht: N = %lld", (long long)N);
+    if (N == 0) return LFFN_OK;
+    return launch_fwht(x, out, N, D, dtype, scale, static_cast<cudaStream_t>(stream));
+}
+
+int lffn_hash_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, int32_t t_begin,
+                  int32_t t_count, int32_t *idx_out, float *w_out, float *z_out, lffn_stream_t stream) {
+    int rc = check_hash_desc(desc, t_begin, t_count);
+    if (rc != LFFN_OK) return rc;
+    LFFN_REQUIRE(x != nullptr, LFFN_ERR_INVALID_ARG, "hash_fwd: x is NULL");
+    LFFN_REQUIRE((idx_out != nullptr) == (w_out != nullptr) && (idx_out != nullptr || z_out != nullptr),
+                 LFFN_ERR_INVALID_ARG, "hash_fwd: give idx_out and w_out together, or z_out alone");
+    LFFN_REQUIRE(N >= 0, LFFN_ERR_INVALID_ARG, "hash_fwd: N = %lld", (long long)N);
+    if (N == 0) return LFFN_OK;
+    return launch_hash_fwd(*desc, x, x_dtype, N, t_begin, t_count, idx_out, w_out, z_out,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int lffn_code_weights(const float *z, int64_t N, int32_t T, int32_t k, int32_t bit_order, int32_t weight_mode,
+                      float tau, int32_t add_offsets, int32_t *idx_out, float *w_out, lffn_stream_t stream) {
+    LFFN_REQUIRE(z != nullptr && idx_out != nullptr && w_out != nullptr, LFFN_ERR_INVALID_ARG,
+                 "code_weights: NULL buffer");
+    LFFN_REQUIRE(N >= 0 && T >= 1, LFFN_ERR_INVALID_ARG, "code_weights: bad sizes");
+    LFFN_REQUIRE(k >= 1 && k <= 16, LFFN_ERR_UNSUPPORTED, "code_weights: k = %d outside [1, 16]", k);
+    LFFN_REQUIRE(bit_order == LFFN_BIT_MSB_FIRST || bit_order == LFFN_BIT_LSB_FIRST, LFFN_ERR_INVALID_ARG,
+                 "code_weights: bit_order %d", bit_order);
+    LFFN_REQUIRE(weight_mode >= LFFN_WEIGHT_SCORE && weight_mode <= LFFN_WEIGHT_SOFT_FLIP, LFFN_ERR_INVALID_ARG,
+                 "code_weights: weight_mode %d", weight_mode);
+    LFFN_REQUIRE(weight_mode != LFFN_WEIGHT_SOFT_FLIP || tau > 0.f, LFFN_ERR_INVALID_ARG, "code_weights: tau <= 0");
+    if (N == 0) return LFFN_OK;
+    return launch_code_weights(z, N, T, k, bit_order, weight_mode, tau, add_offsets, idx_out, w_out,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype, void *out,
+                    int32_t out_dtype, int64_t N, int32_t I, int64_t S, int32_t d, const float *bias,
+                    lffn_stream_t stream) {
+    int rc = check_gather(N, I, S, d, table_dtype);
+    if (rc != LFFN_OK) return rc;
+    LFFN_REQUIRE(tables != nullptr && out != nullptr && (I == 0 || (idx != nullptr && w != nullptr)),
+                 LFFN_ERR_INVALID_ARG, "gather_fwd: NULL buffer");
+    LFFN_REQUIRE(out_dtype == LFFN_F32 || out_dtype == LFFN_BF16, LFFN_ERR_INVALID_ARG, "gather_fwd: out dtype %d",
+                 out_dtype);
+    LFFN_REQUIRE(aligned16(tables) && aligned16(out), LFFN_ERR_INVALID_ARG,
+                 "gather_fwd: tables and out must be 16-byte aligned");
+    if (N == 0) return LFFN_OK;
+    return launch_gather_fwd(idx, w, tables, table_dtype, out, out_dtype, N, I, S, d, bias,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int lffn_gather_bwd_weights(const int32_t *idx, const float *dy, const void *tables, int32_t table_dtype, float *dw,
+                            int64_t N, int32_t I, int64_t S, int32_t d, lffn_stream_t stream) {
+    int rc = check_gather(N, I, S, d, table_dtype);
+    if (rc != LFFN_OK) return rc;
+    LFFN_REQUIRE(idx != nullptr && dy != nullptr && tables != nullptr && dw != nullptr, LFFN_ERR_INVALID_ARG,
+                 "gather_bwd_weights: NULL buffer");
+    LFFN_REQUIRE(aligned16(tables) && aligned16(dy), LFFN_ERR_INVALID_ARG,
+                 "gather_bwd_weights: tables and dy must be 16-byte aligned");
+    if (N == 0 || I == 0) return LFFN_OK;
+    return launch_gather_bwd_weights(idx, dy, tables, table_dtype, dw, N, I, S, d, static_cast<cudaStream_t>(stream));
+}
+
+int lffn_gather_bwd_tables(const int32_t *idx, const float *w, const float *dy, float *dtables, int64_t N, int32_t I,
+                           int64_t S, int32_t d, lffn_stream_t stream) {
+    int rc = check_gather(N, I, S, d, LFFN_F32);
+    if (rc != LFFN_OK) return rc;
+    LFFN_REQUIRE(dtables != nullptr && (N == 0 || I == 0 || (idx != nullptr && w != nullptr && dy != nullptr)),
+                 LFFN_ERR_INVALID_ARG, "gather_bwd_tables: NULL buffer");
+    LFFN_REQUIRE(aligned16(dtables) && aligned16(dy), LFFN_ERR_INVALID_ARG,
+                 "gather_bwd_tables: dtables and dy must be 16-byte aligned");
+    return launch_gather_bwd_tables(idx, w, dy, dtables, N, I, S, d, static_cast<cudaStream_t>(stream));
+}
+
+size_t lffn_gather_bwd_tables_sorted_scratch_bytes(int64_t N, int32_t T, int32_t m, int32_t rows) {
+    if (N < 0 || T < 1 || m < 1 || rows < 1) return 0;
+    return sorted_scratch_bytes(N, T, m, rows);
+}
+
+int lffn_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const float *dy, float *dtables, int64_t N,
+                                  int32_t T, int32_t m, int32_t rows, int32_t d, void *scratch, size_t scratch_bytes,
+                                  lffn_stream_t stream) {
+    LFFN_REQUIRE(T >= 1 && m >= 1 && rows >= 1, LFFN_ERR_INVALID_ARG, "gather_bwd_tables_sorted: bad T/m/rows");
+    int rc = check_gather(N, T * m, (int64_t)T * rows, d, LFFN_F32);
+    if (rc != LFFN_OK) return rc;
+    LFFN_REQUIRE(dtables != nullptr && (N == 0 || (idx != nullptr && w != nullptr && dy != nullptr)),
+                 LFFN_ERR_INVALID_ARG, "gather_bwd_tables_sorted: NULL buffer");
+    LFFN_REQUIRE(aligned16(dtables) && aligned16(dy), LFFN_ERR_INVALID_ARG,
+                 "gather_bwd_tables_sorted: dtables and dy must be 16-byte aligned");
+    return launch_gather_bwd_tables_sorted(idx, w, dy, dtables, N, T, m, rows, d, scratch, scratch_bytes,
+                                           static_cast<cudaStream_t>(stream));
+}
+
+int lffn_layer_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, int32_t t_begin,
+                   int32_t t_count, const void *tables, int32_t table_dtype, int32_t d_out, const float *bias,
+                   void *out, int32_t out_dtype, int32_t *idx_ws, float *w_ws, lffn_stream_t stream) {
+    int rc = lffn_hash_fwd(desc, x, x_dtype, N, t_begin, t_count, idx_ws, w_ws, nullptr, stream);
+    if (rc != LFFN_OK) return rc;
+    const int m = desc->weight_mode == LFFN_WEIGHT_SOFT_FLIP ? desc->k + 1 : 1;
+    return lffn_gather_fwd(idx_ws, w_ws, tables, table_dtype, out, out_dtype, N, t_count * m,
+                           (int64_t)t_count << desc->k, d_out, bias, stream);
+}
+
+static size_t esize(int dtype) { return dtype == LFFN_BF16 ? 2 : 4; }
+static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+size_t lffn_layer_fwd_host_ws_bytes(const lffn_hash_desc *desc, int32_t x_dtype, int32_t out_dtype, int32_t d_out,
+                                    int64_t chunk_tokens) {
+    if (desc == nullptr || chunk_tokens < 1) return 0;
+    const int m = desc->weight_mode == LFFN_WEIGHT_SOFT_FLIP ? desc->k + 1 : 1;
+    const size_t per_lane = up256((size_t)chunk_tokens * desc->d_in * esize(x_dtype)) +
+                            up256((size_t)chunk_tokens * d_out * esize(out_dtype)) +
+                            2 * up256((size_t)chunk_tokens * desc->T * m * 4);
+    return 2 * per_lane;
+}
+
+// Two lanes (streams) alternate over token chunks; within a lane copy-in, the two kernels and
+// copy-out are stream-ordered, and the lanes overlap each other's copies with kernels.
+int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t x_dtype, int64_t N,
+                        const void *tables, int32_t table_dtype, int32_t d_out, const float *bias, void *out_host,
+                        int32_t out_dtype, void *ws, size_t ws_bytes, int64_t chunk_tokens, lffn_stream_t stream) {
+    int rc = check_hash_desc(desc, 0, desc ? desc->T : 0);
+    if (rc != LFFN_OK) return rc;
+    LFFN_REQUIRE(x_host != nullptr && out_host != nullptr && tables != nullptr && ws != nullptr, LFFN_ERR_INVALID_ARG,
+                 "layer_fwd_host: NULL buffer");
+    LFFN_REQUIRE(chunk_tokens >= 1, LFFN_ERR_INVALID_ARG, "layer_fwd_host: chunk_tokens = %lld", (long long)chunk_tokens);
+    LFFN_REQUIRE(ws_bytes >= lffn_layer_fwd_host_ws_bytes(desc, x_dtype, out_dtype, d_out, chunk_tokens),
+                 LFFN_ERR_SCRATCH, "layer_fwd_host: workspace of %zu bytes needed, %zu given",
+                 lffn_layer_fwd_host_ws_bytes(desc, x_dtype, out_dtype, d_out, chunk_tokens), ws_bytes);
+    if (N == 0) return LFFN_OK;
+
+    struct Lanes {
+        cudaStream_t s[2] = {nullptr, nullptr};
+        cudaEvent_t done[2] = {nullptr, nullptr};
+        cudaEvent_t start = nullptr;
+    };
+    static Lanes lanes[MAX_DEV];
+    static std::mutex mu;
+    int dev = 0;
+    LFFN_CHECK_CUDA(cudaGetDevice(&dev));
+    LFFN_REQUIRE(dev >= 0 && dev < MAX_DEV, LFFN_ERR_UNSUPPORTED, "device ordinal %d", dev);
+    std::lock_guard<std::mutex> lock(mu);  // one host-buffer call at a time per process: the lanes are shared
+    Lanes &L = lanes[dev];
+    if (L.s[0] == nullptr) {
+        for (int i = 0; i < 2; i++) {
+            LFFN_CHECK_CUDA(cudaStreamCreateWithFlags(&L.s[i], cudaStreamNonBlocking));
+            LFFN_CHECK_CUDA(cudaEventCreateWithFlags(&L.done[i], cudaEventDisableTiming));
+        }
+        LFFN_CHECK_CUDA(cudaEventCreateWithFlags(&L.start, cudaEventDisableTiming));
+    }
+    cudaStream_t user = static_cast<cudaStream_t>(stream);
+    LFFN_CHECK_CUDA(cudaEventRecord(L.start, user));
+    const int m = desc->weight_mode == LFFN_WEIGHT_SOFT_FLIP ? desc->k + 1 : 1;
+    const size_t xb = up256((size_t)chunk_tokens * desc->d_in * esize(x_dtype));
+    const size_t ob = up256((size_t)chunk_tokens * d_out * esize(out_dtype));
+    const size_t ib = up256((size_t)chunk_tokens * desc->T * m * 4);
+    const size_t per_lane = xb + ob + 2 * ib;
+    for (int i = 0; i < 2; i++) LFFN_CHECK_CUDA(cudaStreamWaitEvent(L.s[i], L.start, 0));
+    int64_t c = 0;
+    for (int64_t n0 = 0; n0 < N; n0 += chunk_tokens, c++) {
+        const int lane = (int)(c & 1);
+        const int64_t nt = (N - n0 < chunk_tokens) ? (N - n0) : chunk_tokens;
+        char *base = static_cast<char *>(ws) + lane * per_lane;
+        void *xd = base;
+        void *od = base + xb;
+        int32_t *iw = reinterpret_cast<int32_t *>(base + xb + ob);
+        float *ww = reinterpret_cast<float *>(base + xb + ob + ib);
+        const char *xs = static_cast<const char *>(x_host) + (size_t)n0 * desc->d_in * esize(x_dtype);
+        char *os = static_cast<char *>(out_host) + (size_t)n0 * d_out * esize(out_dtype);
+        LFFN_CHECK_CUDA(cudaMemcpyAsync(xd, xs, (size_t)nt * desc->d_in * esize(x_dtype), cudaMemcpyHostToDevice, L.s[lane]));
+        rc = lffn_layer_fwd(desc, xd, x_dtype, nt, 0, desc->T, tables, table_dtype, d_out, bias, od, out_dtype, iw, ww,
+                            L.s[lane]);
+        if (rc != LFFN_OK) return rc;
+        LFFN_CHECK_CUDA(cudaMemcpyAsync(os, od, (size_t)nt * d_out * esize(out_dtype), cudaMemcpyDeviceToHost, L.s[lane]));
+    }
+    for (int i = 0; i < 2; i++) {
+        LFFN_CHECK_CUDA(cudaEventRecord(L.done[i], L.s[i]));
+        LFFN_CHECK_CUDA(cudaStreamWaitEvent(user, L.done[i], 0));
+    }
+    LFFN_CHECK_CUDA(cudaStreamSynchronize(user));
+    return LFFN_OK;
+}
+
+}  // extern "C"

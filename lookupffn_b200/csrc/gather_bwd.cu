@@ -1,0 +1,403 @@
+// Backward of the weighted gather-add.
+//
+//   dw[n, i]            = <dy[n, :], tables[idx[n, i], :]>      (reference: indexed_inner_product,
+//                          gather/cuda/extension/gather_kernel_fp32.cu:94-157)
+//   dtables[idx[n, i]] += w[n, i] * dy[n, :]                     (reference: weighted_vector_scatter_add,
+//                          gather_kernel_fp32.cu:49-92, one scalar atomicAdd per element)
+//
+// dw: one warp per token, dy[n] held in registers in the same 16-byte-vector layout as the rows;
+// each lane keeps its partial dot product of 32 consecutive rows in 32 registers, then one
+// 31-shuffle transpose-reduce hands lane j the full sum of row j: one coalesced 128-byte store
+// per 32 rows instead of a 5-shuffle reduction and a shared-memory atomic per row.
+//
+// dtables, any index list: one warp per token, dy[n] in registers, one 16-byte vector reduction
+// (red.global.add.v4.f32) per lane per row -- a quarter of the reference's atomic count, resolved
+// in L2.
+//
+// dtables, layer-structured index list (I = T*m, entry (n, t*m+c) lands in table t): entries are
+// counting-sorted per table into scratch by a stable in-CTA sort, then the segmented form of the
+// forward gather kernel sums each output row's terms in ascending (n, c) order from dy and
+// writes the row once: no atomics on the output, no memset, bit-reproducible, and equal to the
+// CPU oracle's fmaf chain.
+#include "common.cuh"
+
+namespace lffn {
+
+int launch_gather_segmented(const int32_t *idx, const float *w, const float *src, float *out, int64_t n_out,
+                            const int2 *seg, int64_t n_src, int d, cudaStream_t st);  // gather_fwd.cu
+
+// ---- dw ----------------------------------------------------------------------------------------
+template <typename TableT, int VPL, int U>
+__global__ void __launch_bounds__(256) gather_bwd_weights_kernel(const int32_t *__restrict__ idx,
+                                                                 const float *__restrict__ dy,
+                                                                 const TableT *__restrict__ tables,
+                                                                 float *__restrict__ dw, long long N, int I,
+                                                                 long long S, int d, int col0, int accumulate,
+                                                                 uint32_t *status) {
+    constexpr int EPV = Elem<TableT>::PER_VEC;
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    const long long warp0 = (long long)blockIdx.x * wpb + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * wpb;
+    const int row_vecs = d / EPV;
+    const int nvec = min(row_vecs - col0, VPL * 32);
+    const uint4 *tv = reinterpret_cast<const uint4 *>(tables) + col0;
+    bool bad = false;
+
+    for (long long n = warp0; n < N; n += nwarps) {
+        float g[VPL][EPV];
+        const float *dyr = dy + n * d + (long long)col0 * EPV;
+#pragma unroll
+        for (int v = 0; v < VPL; v++) {
+            const int c = lane + 32 * v;
+#pragma unroll
+            for (int q = 0; q < EPV / 4; q++) {
+                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (c < nvec) t = __ldg(reinterpret_cast<const float4 *>(dyr + c * EPV + 4 * q));
+                g[v][4 * q] = t.x;
+                g[v][4 * q + 1] = t.y;
+                g[v][4 * q + 2] = t.z;
+                g[v][4 * q + 3] = t.w;
+            }
+        }
+        const int32_t *ip = idx + n * I;
+        for (int g0 = 0; g0 < I; g0 += 32) {
+            const int cnt = min(32, I - g0);
+            const int my_i = lane < cnt ? __ldg(ip + g0 + lane) : 0;
+            float p[32];
+#pragma unroll
+            for (int j0 = 0; j0 < 32; j0 += U) {
+                uint4 buf[U][VPL];
+                bool ok[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int j = j0 + u;
+                    const int r = __shfl_sync(FULL, my_i, j);
+                    ok[u] = j < cnt && (unsigned long long)(long long)r < (unsigned long long)S;
+                    if (j < cnt && !ok[u]) bad = true;
+                    const uint4 *row = tv + (long long)(ok[u] ? r : 0) * row_vecs;
+#pragma unroll
+                    for (int v = 0; v < VPL; v++) {
+                        const int c = lane + 32 * v;
+                        buf[u][v] = make_uint4(0u, 0u, 0u, 0u);
+                        if (ok[u] && c < nvec) buf[u][v] = ld_row16(row + c);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int v = 0; v < VPL; v++) {
+                        float f[EPV];
+                        Elem<TableT>::unpack(buf[u][v], f);
+#pragma unroll
+                        for (int e = 0; e < EPV; e++) s = fmaf(g[v][e], f[e], s);
+                    }
+                    p[j0 + u] = s;
+                }
+            }
+            // transpose-reduce: after the 5 rounds lane j holds sum over lanes of p[j]
+#pragma unroll
+            for (int s = 16; s >= 1; s >>= 1) {
+                const bool up = (lane & s) != 0;
+#pragma unroll
+                for (int j = 0; j < s; j++) {
+                    const float send = up ? p[j] : p[j + s];
+                    const float keep = up ? p[j + s] : p[j];
+                    p[j] = keep + __shfl_xor_sync(FULL, send, s);
+                }
+            }
+            if (lane < cnt) {
+                float *o = dw + n * I + g0 + lane;
+                *o = accumulate ? (*o + p[0]) : p[0];
+            }
+        }
+    }
+    if (bad) atomicOr(status, LFFN_STATUS_INDEX_RANGE);
+}
+
+template <typename TableT, int VPL>
+static int launch_bww_vpl(const int32_t *idx, const float *dy, const void *tables, float *dw, int64_t N, int I,
+                          int64_t S, int d, int col0, cudaStream_t st) {
+    constexpr int U = (VPL <= 3) ? 4 : 2;
+    constexpr int THREADS = 256;
+    auto kern = gather_bwd_weights_kernel<TableT, VPL, U>;
+    int per_sm = 0;
+    LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, 0));
+    if (per_sm < 1) per_sm = 1;
+    const long long want = (N + THREADS / 32 - 1) / (THREADS / 32);
+    long long grid = (long long)num_sms() * per_sm;
+    if (grid > want) grid = want;
+    if (grid < 1) grid = 1;
+    kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, dy, static_cast<const TableT *>(tables), dw, N, I, S, d, col0,
+                                             col0 > 0 ? 1 : 0, status_word());
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return LFFN_OK;
+}
+
+template <typename TableT>
+static int launch_bww_typed(const int32_t *idx, const float *dy, const void *tables, float *dw, int64_t N, int I,
+                            int64_t S, int d, cudaStream_t st) {
+    constexpr int EPV = Elem<TableT>::PER_VEC;
+    const int row_vecs = d / EPV;
+    constexpr int MAXV = 6;
+    for (int col0 = 0; col0 < row_vecs; col0 += MAXV * 32) {
+        const int nvec = min(row_vecs - col0, MAXV * 32);
+        const int vpl = (nvec + 31) / 32;
+        int rc;
+        switch (vpl) {
+            case 1: rc = launch_bww_vpl<TableT, 1>(idx, dy, tables, dw, N, I, S, d, col0, st); break;
+            case 2: rc = launch_bww_vpl<TableT, 2>(idx, dy, tables, dw, N, I, S, d, col0, st); break;
+            case 3: rc = launch_bww_vpl<TableT, 3>(idx, dy, tables, dw, N, I, S, d, col0, st); break;
+            case 4: rc = launch_bww_vpl<TableT, 4>(idx, dy, tables, dw, N, I, S, d, col0, st); break;
+            default: rc = launch_bww_vpl<TableT, 6>(idx, dy, tables, dw, N, I, S, d, col0, st); break;
+        }
+        if (rc != LFFN_OK) return rc;
+    }
+    return LFFN_OK;
+}
+
+int launch_gather_bwd_weights(const int32_t *idx, const float *dy, const void *tables, int table_dtype, float *dw,
+                              int64_t N, int I, int64_t S, int d, cudaStream_t st) {
+    if (table_dtype == LFFN_F32) return launch_bww_typed<float>(idx, dy, tables, dw, N, I, S, d, st);
+    if (table_dtype == LFFN_BF16) return launch_bww_typed<__nv_bfloat16>(idx, dy, tables, dw, N, I, S, d, st);
+    set_error("gather_bwd_weights: unknown table dtype %d", table_dtype);
+    return LFFN_ERR_INVALID_ARG;
+}
+
+// ---- dtables, any index list: vector reductions in L2 ---------------------------------------------
+__device__ __forceinline__ void red_add_v4(float *p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256) gather_bwd_tables_red_kernel(const int32_t *__restrict__ idx,
+                                                                    const float *__restrict__ w,
+                                                                    const float *__restrict__ dy,
+                                                                    float *__restrict__ dtables, long long N, int I,
+                                                                    long long S, int d, int col0, uint32_t *status) {
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    const long long warp0 = (long long)blockIdx.x * wpb + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * wpb;
+    const int row_vecs = d / 4;
+    const int nvec = min(row_vecs - col0, VPL * 32);
+    bool bad = false;
+    for (long long n = warp0; n < N; n += nwarps) {
+        float4 g[VPL];
+        const float *dyr = dy + n * d + (long long)col0 * 4;
+#pragma unroll
+        for (int v = 0; v < VPL; v++) {
+            const int c = lane + 32 * v;
+            g[v] = c < nvec ? __ldg(reinterpret_cast<const float4 *>(dyr) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int g0 = 0; g0 < I; g0 += 32) {
+            const int cnt = min(32, I - g0);
+            const int my_i = lane < cnt ? __ldg(idx + n * I + g0 + lane) : 0;
+            const float my_w = lane < cnt ? __ldg(w + n * I + g0 + lane) : 0.f;
+            for (int j = 0; j < cnt; j++) {
+                const int r = __shfl_sync(FULL, my_i, j);
+                const float ww = __shfl_sync(FULL, my_w, j);
+                if ((unsigned long long)(long long)r >= (unsigned long long)S) {
+                    bad = true;
+                    continue;
+                }
+                float *row = dtables + (long long)r * d + (long long)col0 * 4;
+#pragma unroll
+                for (int v = 0; v < VPL; v++) {
+                    const int c = lane + 32 * v;
+                    if (c < nvec) red_add_v4(row + c * 4, ww * g[v].x, ww * g[v].y, ww * g[v].z, ww * g[v].w);
+                }
+            }
+        }
+    }
+    if (bad) atomicOr(status, LFFN_STATUS_INDEX_RANGE);
+}
+
+template <int VPL>
+static int launch_red_vpl(const int32_t *idx, const float *w, const float *dy, float *dtables, int64_t N, int I,
+                          int64_t S, int d, int col0, cudaStream_t st) {
+    constexpr int THREADS = 256;
+    auto kern = gather_bwd_tables_red_kernel<VPL>;
+    int per_sm = 0;
+    LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, 0));
+    if (per_sm < 1) per_sm = 1;
+    const long long want = (N + THREADS / 32 - 1) / (THREADS / 32);
+    long long grid = (long long)num_sms() * per_sm;
+    if (grid > want) grid = want;
+    if (grid < 1) grid = 1;
+    kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, w, dy, dtables, N, I, S, d, col0, status_word());
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return LFFN_OK;
+}
+
+int launch_gather_bwd_tables(const int32_t *idx, const float *w, const float *dy, float *dtables, int64_t N, int I,
+                             int64_t S, int d, cudaStream_t st) {
+    LFFN_CHECK_CUDA(cudaMemsetAsync(dtables, 0, (size_t)S * d * sizeof(float), st));
+    const int row_vecs = d / 4;
+    constexpr int MAXV = 8;
+    for (int col0 = 0; col0 < row_vecs; col0 += MAXV * 32) {
+        const int nvec = min(row_vecs - col0, MAXV * 32);
+        const int vpl = (nvec + 31) / 32;
+        int rc;
+        if (vpl <= 1) rc = launch_red_vpl<1>(idx, w, dy, dtables, N, I, S, d, col0, st);
+        else if (vpl <= 2) rc = launch_red_vpl<2>(idx, w, dy, dtables, N, I, S, d, col0, st);
+        else if (vpl <= 4) rc = launch_red_vpl<4>(idx, w, dy, dtables, N, I, S, d, col0, st);
+        else if (vpl <= 6) rc = launch_red_vpl<6>(idx, w, dy, dtables, N, I, S, d, col0, st);
+        else rc = launch_red_vpl<8>(idx, w, dy, dtables, N, I, S, d, col0, st);
+        if (rc != LFFN_OK) return rc;
+    }
+    return LFFN_OK;
+}
+
+// ---- dtables, layer-structured index list: stable per-table counting sort + segmented reduction ----
+constexpr int SORT_THREADS = 512;
+constexpr int SORT_MAX_ROWS = 16384;
+
+// scratch layout: seg int2[T*rows] | ent_n int32[T*Ne] | ent_w float[T*Ne],  Ne = N*m
+struct SortedScratch {
+    int2 *seg;
+    int32_t *ent_n;
+    float *ent_w;
+};
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+size_t sorted_scratch_bytes(int64_t N, int T, int m, int rows) {
+    const size_t ne = (size_t)N * m * T;
+    return align256((size_t)T * rows * sizeof(int2)) + align256(ne * 4) + align256(ne * 4);
+}
+static SortedScratch carve(void *scratch, int64_t N, int T, int m, int rows) {
+    char *p = static_cast<char *>(scratch);
+    const size_t ne = (size_t)N * m * T;
+    SortedScratch s;
+    s.seg = reinterpret_cast<int2 *>(p);
+    p += align256((size_t)T * rows * sizeof(int2));
+    s.ent_n = reinterpret_cast<int32_t *>(p);
+    p += align256(ne * 4);
+    s.ent_w = reinterpret_cast<float *>(p);
+    return s;
+}
+
+// One CTA sorts the N*m entries of one table by row, keeping ascending (n, c) order inside a row.
+__global__ void __launch_bounds__(SORT_THREADS) sort_table_entries_kernel(const int32_t *__restrict__ idx,
+                                                                          const float *__restrict__ w, long long N,
+                                                                          int T, int m, int rows, int2 *seg,
+                                                                          int32_t *ent_n, float *ent_w,
+                                                                          uint32_t *status) {
+    extern __shared__ int cursor[];  // [rows] counts, then running write offsets
+    __shared__ int warp_sums[SORT_THREADS / 32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long Ne = N * m;
+    const int I = T * m;
+    bool bad = false;
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        for (int i = tid; i < rows; i += SORT_THREADS) cursor[i] = 0;
+        __syncthreads();
+        const int32_t *col = idx + (long long)t * m;
+        for (long long e = tid; e < Ne; e += SORT_THREADS) {
+            const long long n = e / m;
+            const int c = (int)(e - n * m);
+            const int key = __ldg(col + n * I + c) - t * rows;
+            if ((unsigned)key < (unsigned)rows) atomicAdd(&cursor[key], 1);
+            else bad = true;
+        }
+        __syncthreads();
+        // exclusive scan of cursor[0..rows): each thread owns a contiguous chunk
+        const int chunk = (rows + SORT_THREADS - 1) / SORT_THREADS;
+        const int b = min(tid * chunk, rows), e2 = min(b + chunk, rows);
+        int local = 0;
+        for (int i = b; i < e2; i++) local += cursor[i];
+        int incl = local;
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+            const int v = __shfl_up_sync(FULL, incl, s);
+            if (lane >= s) incl += v;
+        }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int v = lane < SORT_THREADS / 32 ? warp_sums[lane] : 0;
+#pragma unroll
+            for (int s = 1; s < 32; s <<= 1) {
+                const int u = __shfl_up_sync(FULL, v, s);
+                if (lane >= s) v += u;
+            }
+            if (lane < SORT_THREADS / 32) warp_sums[lane] = v;  // inclusive sums of warps
+        }
+        __syncthreads();
+        int run = incl - local + (warp > 0 ? warp_sums[warp - 1] : 0);
+        const long long tbase = (long long)t * Ne;
+        for (int i = b; i < e2; i++) {
+            const int cnt = cursor[i];
+            seg[(long long)t * rows + i] = make_int2((int)(tbase + run), cnt);
+            cursor[i] = run;
+            run += cnt;
+        }
+        __syncthreads();
+        // stable placement, SORT_THREADS entries per step in entry order
+        for (long long base = 0; base < Ne; base += SORT_THREADS) {
+            const long long e = base + tid;
+            long long n = 0;
+            int key = -1 - lane;  // unique per lane: matches nobody
+            float ww = 0.f;
+            if (e < Ne) {
+                n = e / m;
+                const int c = (int)(e - n * m);
+                const int kk = __ldg(col + n * I + c) - t * rows;
+                if ((unsigned)kk < (unsigned)rows) {
+                    key = kk;
+                    ww = __ldg(w + n * I + (long long)t * m + c);
+                }
+            }
+            const unsigned peers = __match_any_sync(FULL, key);
+            const int rank = __popc(peers & ((1u << lane) - 1u));
+            const int leader = __ffs(peers) - 1;
+            int basepos = 0;
+            for (int ws = 0; ws < SORT_THREADS / 32; ws++) {  // warps take their turn in entry order
+                if (warp == ws && key >= 0 && rank == 0) {
+                    basepos = cursor[key];
+                    cursor[key] = basepos + __popc(peers);
+                }
+                __syncthreads();
+            }
+            basepos = __shfl_sync(FULL, basepos, leader);
+            if (key >= 0) {
+                const long long pos = tbase + basepos + rank;
+                ent_n[pos] = (int32_t)n;
+                ent_w[pos] = ww;
+            }
+        }
+        __syncthreads();
+    }
+    if (bad) atomicOr(status, LFFN_STATUS_STRUCTURE);
+}
+
+int launch_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const float *dy, float *dtables, int64_t N,
+                                    int T, int m, int rows, int d, void *scratch, size_t scratch_bytes,
+                                    cudaStream_t st) {
+    if (rows > SORT_MAX_ROWS) {
+        set_error("gather_bwd_tables_sorted: %d rows per table exceeds %d; use lffn_gather_bwd_tables", rows,
+                  SORT_MAX_ROWS);
+        return LFFN_ERR_UNSUPPORTED;
+    }
+    if ((long long)N * m * T >= (1ll << 31)) {
+        set_error("gather_bwd_tables_sorted: N*T*m = %lld entries exceed 2^31", (long long)N * m * T);
+        return LFFN_ERR_UNSUPPORTED;
+    }
+    if (scratch == nullptr || scratch_bytes < sorted_scratch_bytes(N, T, m, rows)) {
+        set_error("gather_bwd_tables_sorted: scratch of %zu bytes needed, %zu given", sorted_scratch_bytes(N, T, m, rows),
+                  scratch_bytes);
+        return LFFN_ERR_SCRATCH;
+    }
+    SortedScratch s = carve(scratch, N, T, m, rows);
+    const size_t smem = (size_t)rows * sizeof(int);
+    if (smem > 48 * 1024)
+        LFFN_CHECK_CUDA(cudaFuncSetAttribute(sort_table_entries_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem));
+    int grid = T < 4 * num_sms() ? T : 4 * num_sms();
+    sort_table_entries_kernel<<<grid, SORT_THREADS, smem, st>>>(idx, w, N, T, m, rows, s.seg, s.ent_n, s.ent_w,
+                                                                status_word());
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return launch_gather_segmented(s.ent_n, s.ent_w, dy, dtables, (int64_t)T * rows, s.seg, N, d, st);
+}
+
+}  // namespace lffn

@@ -1,0 +1,228 @@
+// Hashing stage with block-diagonal projection weights (BS >= 4): the reference's BH4
+// (lookup.py:10-47, bh4/kernel.py:23-36): R x S x (block-diagonal multiply, Hadamard), mix,
+// bias, then codes and weights (compute_code_score/kernel.py:43-55).
+//
+// Mapping: one CTA of 256 threads owns a tile of M = 32 tokens for all rotations and stages; the
+// tile lives in shared memory TRANSPOSED, Y[e][m] (coordinate-major, tokens contiguous, row
+// padded to 36 floats), so that
+//   - the block multiply reads 8 tokens of one input coordinate as two 16-byte broadcasts and 4
+//     output columns of the staged weights as one 16-byte load, for an 8 x 4 register tile
+//     per thread (32 fused multiply-adds per 3 shared loads).  Each output is one fmaf chain
+//     over i ascending from zero -- the CPU oracle's order.
+//   - the Hadamard transform needs no shuffles: a thread owns one token (lane) and 16/8/4/2
+//     coordinates of one radix group; strides run from D/2 down to 1 in passes of up to 4 bits.
+// Weights of 256 output columns (PC/BS blocks) are staged per pass into shared memory as
+// Ws[g][i][o] with a 16-byte XOR swizzle, from either global layout ([o][i] or [i][o]).
+// No tensor cores: sign bits must reproduce the fp32 fmaf chain.
+#include "common.cuh"
+#include "hash_common.cuh"
+
+namespace lffn {
+
+constexpr int HB_M = 32;        // tokens per tile
+constexpr int HB_MP = 36;       // padded tokens per coordinate row
+constexpr int HB_THREADS = 256;
+constexpr int HB_CARRY = 16;
+constexpr int HB_WFLOATS = 16384;  // staged weights per pass: PC * BS floats
+
+template <int RADIX>
+__device__ __forceinline__ void radix_butterflies(float (&v)[RADIX]) {
+#pragma unroll
+    for (int s = RADIX / 2; s >= 1; s >>= 1) {
+#pragma unroll
+        for (int q = 0; q < RADIX; q++) {
+            if ((q & s) == 0) {
+                const float a = v[q], b = v[q + s];
+                v[q] = __fadd_rn(a, b);
+                v[q + s] = __fsub_rn(a, b);
+            }
+        }
+    }
+}
+
+// One pass of the transform over bits [lo, lo+nb) of the coordinate index, RADIX = 2^nb.
+template <int RADIX>
+__device__ __forceinline__ void fwht_pass(float *Y, int D, int lo, float scale, int warp, int lane) {
+    const int ngroups = D / RADIX;
+    const int lo_mask = (1 << lo) - 1;
+    for (int gi = warp; gi < ngroups; gi += HB_THREADS / 32) {
+        const int base = ((gi >> lo) * RADIX << lo) | (gi & lo_mask);
+        float v[RADIX];
+#pragma unroll
+        for (int q = 0; q < RADIX; q++) v[q] = Y[(base + (q << lo)) * HB_MP + lane];
+        radix_butterflies<RADIX>(v);
+#pragma unroll
+        for (int q = 0; q < RADIX; q++) {
+            float o = v[q];
+            if (scale != 1.f) o = __fmul_rn(o, scale);
+            Y[(base + (q << lo)) * HB_MP + lane] = o;
+        }
+    }
+}
+
+__device__ __forceinline__ void fwht_tile(float *Y, int D, float scale, int warp, int lane) {
+    int bits = 31 - __clz(D);
+    while (bits > 0) {
+        const int nb = bits >= 4 ? 4 : bits;
+        const int lo = bits - nb;
+        const float sc = lo == 0 ? scale : 1.f;
+        if (nb == 4) fwht_pass<16>(Y, D, lo, sc, warp, lane);
+        else if (nb == 3) fwht_pass<8>(Y, D, lo, sc, warp, lane);
+        else if (nb == 2) fwht_pass<4>(Y, D, lo, sc, warp, lane);
+        else fwht_pass<2>(Y, D, lo, sc, warp, lane);
+        bits = lo;
+        __syncthreads();
+    }
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, int BS, int transpose_w) {
+    extern __shared__ __align__(16) float smem[];
+    const int D = a.D;
+    float *Y = smem;                         // [D][HB_MP]
+    float *Ws = Y + (size_t)D * HB_MP;       // [PC/BS][BS][BS] swizzled
+    float *carry = Ws + HB_WFLOATS;          // [HB_CARRY][HB_MP]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int k = a.k;
+    const int m = a.weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
+    const long long g_lo = (long long)a.t_begin * k, g_hi = (long long)(a.t_begin + a.t_count) * k;
+    const long long out_pitch = (long long)a.t_count * m;
+    const int PC = min(D, BS <= 64 ? 256 : HB_WFLOATS / BS);  // columns per pass
+    const int bs4mask = BS / 4 - 1;
+    const long long ntiles = (a.N + HB_M - 1) / HB_M;
+
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const long long n0 = tile * HB_M;
+        const int mt = (int)min((long long)HB_M, a.N - n0);  // valid tokens in the tile
+        for (int r = a.r_lo; r <= a.r_hi; r++) {
+            __syncthreads();
+            // keep the last coordinates of the previous rotation for a straddling table
+            for (int i = tid; i < HB_CARRY * HB_M; i += HB_THREADS) {
+                const int e = i / HB_M, mm = i % HB_M;
+                carry[e * HB_MP + mm] = Y[(D - HB_CARRY + e) * HB_MP + mm];
+            }
+            __syncthreads();
+            // load the tile, transposed and zero-padded
+            for (int mm = warp; mm < HB_M; mm += HB_THREADS / 32) {
+                const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
+                for (int e = lane; e < D; e += 32)
+                    Y[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+            }
+            __syncthreads();
+            for (int s = 0; s < a.S; s++) {
+                const float *wstage = a.w + ((long long)r * a.S + s) * D * BS;
+                for (int col0 = 0; col0 < D; col0 += PC) {
+                    // stage PC/BS weight blocks as Ws[g][i][o], 16-byte XOR swizzle on o
+                    const float *wsrc = wstage + (long long)col0 * BS;
+                    for (int L = tid; L < PC * BS; L += HB_THREADS) {
+                        const int g = L / (BS * BS), rem = L % (BS * BS);
+                        const int p = rem / BS, q = rem % BS;
+                        const int i = transpose_w ? p : q, o = transpose_w ? q : p;
+                        Ws[g * BS * BS + i * BS + ((((o >> 2) ^ (i & bs4mask)) << 2) | (o & 3))] = __ldg(wsrc + L);
+                    }
+                    __syncthreads();
+                    // PC output columns x 32 tokens = PC items of 8 tokens x 4 columns: at most one per thread
+                    const bool active = tid < PC;
+                    const int cq = tid % (PC / 4), tq = tid / (PC / 4);
+                    const int c = cq * 4, g = c / BS, o4 = (c % BS) >> 2;
+                    float acc[8][4];
+#pragma unroll
+                    for (int p = 0; p < 8; p++)
+#pragma unroll
+                        for (int q = 0; q < 4; q++) acc[p][q] = 0.f;
+                    if (active) {
+                        const float *yb = Y + (size_t)(col0 + g * BS) * HB_MP + tq * 8;
+                        const float *wb = Ws + g * BS * BS;
+#pragma unroll 4
+                        for (int i = 0; i < BS; i++) {
+                            const float4 x0 = *reinterpret_cast<const float4 *>(yb + i * HB_MP);
+                            const float4 x1 = *reinterpret_cast<const float4 *>(yb + i * HB_MP + 4);
+                            const float4 w4 = *reinterpret_cast<const float4 *>(wb + i * BS + ((o4 ^ (i & bs4mask)) << 2));
+                            const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                            const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                            for (int p = 0; p < 8; p++)
+#pragma unroll
+                                for (int q = 0; q < 4; q++) acc[p][q] = fmaf(xs[p], wv[q], acc[p][q]);
+                        }
+                    }
+                    __syncthreads();  // all reads of this pass's input columns are done before they are overwritten
+                    if (active) {
+                        float *yo = Y + (size_t)(col0 + c) * HB_MP + tq * 8;
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            *reinterpret_cast<float4 *>(yo + q * HB_MP) = make_float4(acc[0][q], acc[1][q], acc[2][q], acc[3][q]);
+                            *reinterpret_cast<float4 *>(yo + q * HB_MP + 4) = make_float4(acc[4][q], acc[5][q], acc[6][q], acc[7][q]);
+                        }
+                    }
+                    __syncthreads();
+                }
+                fwht_tile(Y, D, a.had_scale, warp, lane);
+            }
+            // mix + bias:  z = fl(fl(mix_a * y) + fl(mix_b * u)) + bias
+            const long long c_lo = (long long)r * D, c_hi = c_lo + D;
+            for (int mm = warp; mm < HB_M; mm += HB_THREADS / 32) {
+                const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
+                for (int e = lane; e < D; e += 32) {
+                    const float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+                    const long long g = c_lo + e;
+                    float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + mm]), __fmul_rn(a.mix_b, u));
+                    if (a.bias != nullptr && g < (long long)a.T * k) z = __fadd_rn(z, __ldg(a.bias + g));
+                    Y[e * HB_MP + mm] = z;
+                    if (a.z_out != nullptr && mm < mt && g >= g_lo && g < g_hi)
+                        a.z_out[(n0 + mm) * (g_hi - g_lo) + (g - g_lo)] = z;
+                }
+            }
+            __syncthreads();
+            // tables that end inside this rotation; lane = token, warps stride over tables
+            long long t_first = c_lo / k;
+            if (t_first < a.t_begin) t_first = a.t_begin;
+            long long t_end = c_hi / k;
+            if (t_end > a.t_begin + a.t_count) t_end = a.t_begin + a.t_count;
+            if (lane < mt && a.idx_out != nullptr) {
+                for (long long t = t_first + warp; t < t_end; t += HB_THREADS / 32) {
+                    const int local0 = (int)(t * k - c_lo);
+                    auto get = [&](int j) -> float {
+                        const int e = local0 + j;
+                        return e >= 0 ? Y[e * HB_MP + lane] : carry[(HB_CARRY + e) * HB_MP + lane];
+                    };
+                    const long long o = (n0 + lane) * out_pitch + (t - a.t_begin) * m;
+                    emit_table(get, k, a.bit_order, a.weight_mode, a.tau, (int32_t)((t - a.t_begin) << k), false, 0,
+                               a.idx_out + o, a.w_out + o);
+                }
+            }
+        }
+    }
+}
+
+int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, cudaStream_t st) {
+    if (BS < 4 || BS > 128 || (BS & (BS - 1)) != 0 || a.D % BS != 0) {
+        set_error("hash_fwd: block size %d unsupported (1, or a power of two in [4, 128] dividing D)", BS);
+        return LFFN_ERR_UNSUPPORTED;
+    }
+    if (a.D < 64 || a.D > 1024 || (a.D & (a.D - 1)) != 0) {
+        set_error("hash_fwd: block-diagonal projection supports D a power of two in [64, 1024], got %d", a.D);
+        return LFFN_ERR_UNSUPPORTED;
+    }
+    const size_t smem = ((size_t)a.D * HB_MP + HB_WFLOATS + HB_CARRY * HB_MP) * sizeof(float);
+    const long long ntiles = (a.N + HB_M - 1) / HB_M;
+    long long grid = num_sms();
+    if (grid > ntiles) grid = ntiles;
+    if (grid < 1) grid = 1;
+    if (x_dtype == LFFN_F32) {
+        auto kern = hash_block_kernel<float>;
+        LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<(unsigned)grid, HB_THREADS, smem, st>>>(a, BS, transpose_w);
+    } else if (x_dtype == LFFN_BF16) {
+        auto kern = hash_block_kernel<__nv_bfloat16>;
+        LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<(unsigned)grid, HB_THREADS, smem, st>>>(a, BS, transpose_w);
+    } else {
+        set_error("hash_fwd: unknown x dtype %d", x_dtype);
+        return LFFN_ERR_INVALID_ARG;
+    }
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return LFFN_OK;
+}
+
+}  // namespace lffn

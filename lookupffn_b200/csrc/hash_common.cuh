@@ -1,0 +1,78 @@
+// Pieces shared by the two hashing kernels (hash_fwd.cu: diagonal projection, one warp per token;
+// hash_block.cu: block-diagonal projection, one CTA per 32-token tile).
+#pragma once
+
+#include "common.cuh"
+
+namespace lffn {
+
+struct HashArgs {
+    const void *x;
+    long long N;
+    int d_in, D, S, R;
+    int r_lo, r_hi;  // rotations needed for the requested tables, inclusive
+    float had_scale, mix_a, mix_b;
+    const float *w;     // [R, S, D]
+    const float *bias;  // [T*k] or null
+    int T, k, bit_order, weight_mode;
+    float tau;
+    int t_begin, t_count;
+    int32_t *idx_out;  // may be null together with w_out: only z_out is produced
+    float *w_out;
+    float *z_out;
+};
+
+// ---- codes and weights of one table from its k coordinates ------------------------------------
+// `get(j)` returns coordinate j of the table.  Writes m = 1 or k+1 (idx, w) pairs.
+template <typename Get>
+__device__ __forceinline__ void emit_table(Get get, int k, int bit_order, int weight_mode, float tau, int32_t offset,
+                                           bool have_code, int32_t code_lsb, int32_t *io, float *wo) {
+    int32_t code = 0;
+    if (weight_mode == LFFN_WEIGHT_SCORE) {
+        float num = 0.f, den = 1.f;
+        for (int j = 0; j < k; j++) {
+            const float z = get(j);
+            if (!have_code && z > 0.f) code |= 1 << j;
+            const float a = fabsf(z);
+            num = __fadd_rn(num, a);
+            den = __fmul_rn(den, __fadd_rn(1.f, expf(__fmul_rn(-2.f, a))));
+        }
+        if (have_code) code = code_lsb;
+        if (bit_order == LFFN_BIT_MSB_FIRST) code = (int32_t)(__brev((unsigned)code) >> (32 - k));
+        io[0] = code + offset;
+        wo[0] = __fdiv_rn(num, den);
+    } else if (weight_mode == LFFN_WEIGHT_ONES) {
+        if (have_code) {
+            code = code_lsb;
+        } else {
+            for (int j = 0; j < k; j++)
+                if (get(j) > 0.f) code |= 1 << j;
+        }
+        if (bit_order == LFFN_BIT_MSB_FIRST) code = (int32_t)(__brev((unsigned)code) >> (32 - k));
+        io[0] = code + offset;
+        wo[0] = 1.f;
+    } else {  // soft flip: k+1 candidates
+        float s[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            if (j < k) {
+                const float z = get(j);
+                if (!have_code && z > 0.f) code |= 1 << j;
+                s[j] = __fdiv_rn(1.f, __fadd_rn(1.f, expf(__fdiv_rn(-fabsf(z), tau))));
+            }
+        }
+        if (have_code) code = code_lsb;
+        for (int c = 0; c <= k; c++) {
+            float p = 1.f;
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (j < k) p = __fmul_rn(p, (c == j + 1) ? __fsub_rn(1.f, s[j]) : s[j]);
+            int32_t cc = c == 0 ? code : (code ^ (1 << (c - 1)));
+            if (bit_order == LFFN_BIT_MSB_FIRST) cc = (int32_t)(__brev((unsigned)cc) >> (32 - k));
+            io[c] = cc + offset;
+            wo[c] = p;
+        }
+    }
+}
+
+}  // namespace lffn

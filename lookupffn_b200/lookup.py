@@ -1,0 +1,170 @@
+"""LookupFFN: the hashed-lookup-table replacement of a transformer feed-forward block.
+
+Drop-in for the reference's module (src/roberta/models/prenorm_lookup/lookup.py:10-129): same
+constructor `LookupFFN(config, output_size)`, same `forward(hidden_states)`, same parameter names
+and shapes (`LayerNorm.weight/bias`, `hash.projection.weight/bias`, `tables`, `bias`), so a
+reference checkpoint loads with strict=True.  The work is done by the sm_100a kernels of
+liblookupffn.so; tensors must live on a CUDA device (there is no CPU path).
+
+Config attributes read (reference names): hidden_size, ffn_num_table, ffn_table_size,
+layer_norm_eps, projection_type ("bh4" | "dense" | "sign_hadamard"), block_size.
+Optional attributes (defaults = reference behaviour):
+  lookup_bit_order    "msb" (reference) | "lsb"
+  lookup_weight_mode  "score" (reference) | "ones" | "soft_flip"
+  lookup_tau          temperature of soft_flip (0.5)
+  lookup_table_dtype  torch.float32 (reference) | torch.bfloat16
+"""
+import math
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import ops
+from ._lib import MSB_FIRST, LSB_FIRST, WEIGHT_ONES, WEIGHT_SCORE, WEIGHT_SOFT_FLIP
+
+_BIT_ORDER = {"msb": MSB_FIRST, "lsb": LSB_FIRST}
+_WEIGHT_MODE = {"score": WEIGHT_SCORE, "ones": WEIGHT_ONES, "soft_flip": WEIGHT_SOFT_FLIP}
+
+
+class BH4(nn.Module):
+    """Block-diagonal x Hadamard projection (reference lookup.py:10-47).  Holds the parameters and
+    the description of the projection; the arithmetic runs fused inside the hash kernel."""
+
+    num_stages = 4
+
+    def __init__(self, in_dim, out_dim, block_size, decay_coeff=0.7):
+        super().__init__()
+        self.in_dim = in_dim
+        self.out_dim = out_dim
+        self.block_size = block_size
+        self.decay_coeff = decay_coeff
+        self.padded_in_dim = int(2 ** math.ceil(math.log2(in_dim)))
+        self.num_repeat = max(1, int(math.ceil(self.out_dim / self.padded_in_dim)))
+        self.num_block = self.padded_in_dim // self.block_size
+        coeff = math.sqrt(self.block_size * self.padded_in_dim)
+        self.weight = nn.Parameter(
+            torch.randn(self.num_repeat, self.num_stages, self.num_block, self.block_size, self.block_size) / coeff)
+        self.bias = nn.Parameter(torch.zeros(self.out_dim))
+        self.had_scale = 1.0
+
+    def extra_repr(self):
+        return (f"in_dim={self.in_dim}, out_dim={self.out_dim}, block_size={self.block_size}, "
+                f"decay_coeff={self.decay_coeff}")
+
+    @property
+    def mix(self):
+        return self.decay_coeff, 1 - self.decay_coeff
+
+    def forward(self, xs):
+        """The projection alone, z [..., out_dim] (reference BH4.forward)."""
+        shape = xs.shape[:-1]
+        x = xs.reshape(-1, xs.shape[-1])
+        desc = ops.make_hash_desc(self.in_dim, self.weight.detach().contiguous(), self.bias.detach().contiguous(),
+                                  self.out_dim, 1, had_scale=self.had_scale, mix_a=self.mix[0], mix_b=self.mix[1],
+                                  weight_mode=WEIGHT_ONES)
+        _, _, z = ops.hash_fwd(x, desc, want_z=True, want_codes=False)
+        return z.reshape(*shape, self.out_dim)
+
+
+class SignHadamard(BH4):
+    """v = H diag(s2) H diag(s1) x per rotation with fixed random +-1 diagonals and the Hadamard
+    matrix normalised by 1/sqrt(D): the BS = 1, two-stage, no-mix case of the same kernel."""
+
+    num_stages = 2
+
+    def __init__(self, in_dim, out_dim, seed=0):
+        super().__init__(in_dim, out_dim, block_size=1, decay_coeff=1.0)
+        g = torch.Generator().manual_seed(seed)
+        signs = (2 * torch.randint(0, 2, self.weight.shape, generator=g) - 1).float()
+        self.weight = nn.Parameter(signs, requires_grad=False)
+        self.had_scale = 1.0 / math.sqrt(self.padded_in_dim)
+
+
+class Hashing(nn.Module):
+    """Projection to T*k coordinates, then codes and weights (reference lookup.py:49-77)."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        self.num_table = config.ffn_num_table
+        self.table_size = config.ffn_table_size
+        self.code_length = int(math.log2(self.table_size))
+        self.total_dim = self.num_table * self.code_length
+        self.bit_order = _BIT_ORDER[getattr(config, "lookup_bit_order", "msb")]
+        self.weight_mode = _WEIGHT_MODE[getattr(config, "lookup_weight_mode", "score")]
+        self.tau = float(getattr(config, "lookup_tau", 0.5))
+        if config.projection_type == "bh4":
+            self.projection = BH4(self.hidden_size, self.total_dim, block_size=config.block_size)
+        elif config.projection_type == "sign_hadamard":
+            self.projection = SignHadamard(self.hidden_size, self.total_dim, seed=getattr(config, "lookup_seed", 0))
+        elif config.projection_type == "dense":
+            self.projection = nn.Linear(self.hidden_size, self.total_dim)
+        else:
+            raise NotImplementedError
+
+    @property
+    def candidates(self):
+        return self.code_length + 1 if self.weight_mode == WEIGHT_SOFT_FLIP else 1
+
+    def forward(self, x, t_begin=0, t_count=None):
+        """x [N, hidden] -> (row indices int32 [N, T*m] with table offsets added, weights fp32 [N, T*m])."""
+        t_count = self.num_table - t_begin if t_count is None else t_count
+        if isinstance(self.projection, nn.Linear):
+            z = self.projection(x).float().reshape(x.shape[0], self.num_table, self.code_length)
+            z = z[:, t_begin:t_begin + t_count].contiguous()
+            return ops.compute_code_score(z, bit_order=self.bit_order, weight_mode=self.weight_mode, tau=self.tau,
+                                          add_offsets=True)
+        p = self.projection
+        desc = ops.make_hash_desc(self.hidden_size, p.weight.detach().contiguous(), p.bias.detach().contiguous(),
+                                  self.num_table, self.code_length, had_scale=p.had_scale, mix_a=p.mix[0],
+                                  mix_b=p.mix[1], bit_order=self.bit_order, weight_mode=self.weight_mode, tau=self.tau)
+        idx, w, _ = ops.hash_fwd(x, desc, t_begin=t_begin, t_count=t_count)
+        return idx, w
+
+
+class LookupFFN(nn.Module):
+    def __init__(self, config, output_size):
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        self.output_size = output_size
+        self.LayerNorm = nn.LayerNorm(self.hidden_size, eps=config.layer_norm_eps)
+        self.num_table = config.ffn_num_table
+        self.table_size = config.ffn_table_size
+        assert (2 ** int(math.log2(self.table_size))) == self.table_size
+        self.hash = Hashing(config)
+        table_dtype = getattr(config, "lookup_table_dtype", torch.float32)
+        self.tables = nn.Parameter(
+            (0.02 * torch.randn(self.num_table, self.table_size, self.output_size)).to(table_dtype))
+        self.bias = nn.Parameter(0.001 * torch.randn(self.output_size))
+
+    def extra_repr(self):
+        return (f"hidden_size={self.hidden_size}, num_table={self.num_table}, table_size={self.table_size}, "
+                f"output_size={self.output_size}")
+
+    def _forward(self, hidden_states):
+        if not hidden_states.is_cuda:
+            raise RuntimeError("lookupffn_b200.LookupFFN runs on CUDA tensors only (no CPU fallback)")
+        hidden_states = self.LayerNorm(hidden_states)
+        code, score = self.hash(hidden_states)
+        outputs = self.gather(code, score, self.tables)
+        return outputs
+
+    def forward(self, hidden_states):
+        shape = hidden_states.shape[:-1]
+        dim = hidden_states.shape[-1]
+        hidden_states = hidden_states.reshape(int(np.prod(shape)), dim)
+        outputs = self._forward(hidden_states)
+        return outputs.reshape(*shape, self.output_size)
+
+    def gather(self, indexes, weights, tables):
+        """indexes already hold code + t * table_size (the kernel adds the offsets of reference
+        lookup.py:126).  The bias add of lookup.py:108 is fused into the kernel when no gradient is
+        needed."""
+        num_table, table_size, vector_dim = tables.shape
+        flat = tables.reshape(num_table * table_size, vector_dim)
+        m = self.hash.candidates
+        if torch.is_grad_enabled() and (flat.requires_grad or weights.requires_grad):
+            out = ops.gather(indexes, weights, flat, training=self.training, structure=(num_table, m, table_size))
+            return out + self.bias.to(out.dtype)
+        return ops.weighted_vector_gather_add(indexes, flat, weights, bias=self.bias)

@@ -1,0 +1,228 @@
+"""Operator functions of the LookupFFN path, with the reference's names and argument meaning
+(src/roberta/models/prenorm_lookup/{bh4,compute_code_score,gather}/kernel.py), each calling the
+sm_100a kernels of liblookupffn.so through its C ABI.  CUDA tensors only; a missing library or
+a CPU tensor raises.
+"""
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib as L
+from ._lib import (BF16, F32, LSB_FIRST, MSB_FIRST, WEIGHT_ONES, WEIGHT_SCORE, WEIGHT_SOFT_FLIP,  # noqa: F401
+                   LookupFFNError)
+
+
+def _contig(t):
+    return t if t.is_contiguous() else t.contiguous()
+
+
+# ---- Hadamard ---------------------------------------------------------------------------------
+def hadamard(inp, scale=1.0):
+    """inp [N, D] (fp32 or bf16) -> inp @ H_D * scale, H the unnormalised Sylvester matrix.
+    Reference: hadamard(inp) (bh4/fast_hadamard_transform/kernel.py:78-89)."""
+    L.require_cuda(inp)
+    assert inp.dim() == 2
+    inp = _contig(inp)
+    N, D = inp.shape
+    out = torch.empty_like(inp)
+    with torch.cuda.device(inp.device):
+        L.check(L.lib().lffn_fwht(L.ptr(inp), L.ptr(out), N, D, L.dtype_code(inp.dtype), float(scale),
+                                  L.stream_ptr(inp.device)))
+    return out
+
+
+class _Hadamard(torch.autograd.Function):
+    """The transform is its own transpose: backward = the same transform
+    (bh4/fast_hadamard_transform/kernel.py:47-54)."""
+
+    @staticmethod
+    def forward(ctx, inp, scale):
+        ctx.scale = scale
+        return hadamard(inp, scale)
+
+    @staticmethod
+    def backward(ctx, g):
+        return hadamard(g.contiguous(), ctx.scale), None
+
+
+def fast_hadamard_transform(X, scale=1.0):
+    return _Hadamard.apply(X, scale)
+
+
+# ---- hashing ------------------------------------------------------------------------------------
+def make_hash_desc(d_in, proj_w, proj_bias, T, k, transpose_w=False, had_scale=1.0, mix_a=0.7, mix_b=1 - 0.7,
+                   bit_order=MSB_FIRST, weight_mode=WEIGHT_SCORE, tau=0.5):
+    """proj_w [R, S, D/BS, BS, BS] fp32 CUDA tensor.  The descriptor holds raw pointers: keep the
+    tensors alive while it is used."""
+    L.require_cuda(proj_w, proj_bias)
+    assert proj_w.dtype == torch.float32 and proj_w.is_contiguous() and proj_w.dim() == 5
+    R, S, NB, BS, BS2 = proj_w.shape
+    assert BS == BS2
+    if proj_bias is not None:
+        assert proj_bias.dtype == torch.float32 and proj_bias.is_contiguous() and proj_bias.numel() == T * k
+    return L.HashDesc(d_in=d_in, D=NB * BS, BS=BS, S=S, R=R, transpose_w=int(transpose_w), had_scale=had_scale,
+                      mix_a=mix_a, mix_b=mix_b, T=T, k=k, bit_order=bit_order, weight_mode=weight_mode, tau=tau,
+                      proj_w=proj_w.data_ptr(), proj_bias=0 if proj_bias is None else proj_bias.data_ptr())
+
+
+def hash_fwd(x, desc, t_begin=0, t_count=None, want_z=False, want_codes=True):
+    """x [N, d_in] -> (idx int32 [N, t_count*m] with table offsets, w fp32 [N, t_count*m], z or None).
+    Reference: Hashing.forward (lookup.py:64-77) + the offsets of LookupFFN.gather (lookup.py:126)."""
+    L.require_cuda(x)
+    x = _contig(x)
+    N = x.shape[0]
+    t_count = desc.T - t_begin if t_count is None else t_count
+    m = desc.k + 1 if desc.weight_mode == WEIGHT_SOFT_FLIP else 1
+    idx = w = z = None
+    if want_codes:
+        idx = torch.empty((N, t_count * m), dtype=torch.int32, device=x.device)
+        w = torch.empty((N, t_count * m), dtype=torch.float32, device=x.device)
+    if want_z:
+        z = torch.empty((N, t_count * desc.k), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(L.lib().lffn_hash_fwd(C.byref(desc), L.ptr(x), L.dtype_code(x.dtype), N, t_begin, t_count, L.ptr(idx),
+                                      L.ptr(w), L.ptr(z), L.stream_ptr(x.device)))
+    return idx, w, z
+
+
+def bh4(x, w, training=False, transpose_w=False, had_scale=1.0):
+    """x [N, D] (D a power of two), w [R, S, D/BS, BS, BS] -> [N, R*D]: R repeats of S x (block-diagonal
+    multiply, Hadamard).  Reference: bh4(x, w, training) (bh4/kernel.py:10-36), CUDA semantics."""
+    L.require_cuda(x, w)
+    R, S, NB, BS, _ = w.shape
+    D = NB * BS
+    assert x.shape[1] == D
+    desc = make_hash_desc(D, _contig(w.float()), None, R * D, 1, transpose_w=transpose_w, had_scale=had_scale,
+                          mix_a=1.0, mix_b=0.0, weight_mode=WEIGHT_ONES)
+    _, _, z = hash_fwd(x, desc, want_z=True, want_codes=False)
+    return z
+
+
+def compute_code_score(hash_scores, training=False, bit_order=MSB_FIRST, weight_mode=WEIGHT_SCORE, tau=0.5,
+                       add_offsets=False):
+    """hash_scores [N, T, k] fp32 -> (code int32 [N, T*m], score fp32 [N, T*m]).
+    Reference: compute_code_score(hash_scores, training) (compute_code_score/kernel.py:22-55)."""
+    L.require_cuda(hash_scores)
+    assert hash_scores.dim() == 3 and hash_scores.dtype == torch.float32
+    z = _contig(hash_scores)
+    N, T, k = z.shape
+    m = k + 1 if weight_mode == WEIGHT_SOFT_FLIP else 1
+    code = torch.empty((N, T * m), dtype=torch.int32, device=z.device)
+    score = torch.empty((N, T * m), dtype=torch.float32, device=z.device)
+    with torch.cuda.device(z.device):
+        L.check(L.lib().lffn_code_weights(L.ptr(z), N, T, k, bit_order, weight_mode, float(tau), int(add_offsets),
+                                          L.ptr(code), L.ptr(score), L.stream_ptr(z.device)))
+    return code, score
+
+
+# ---- gather and its backward ------------------------------------------------------------------------
+def _check_gather_args(indexes, source, weights):
+    # the reference's asserts (gather/cuda/kernel.py:28-43) minus its `index_size % 2` and
+    # `vector_dim % 64` limits, which these kernels do not have
+    L.require_cuda(indexes, source, weights)
+    assert indexes.dtype == torch.int32, indexes.dtype
+    assert source.dtype in (torch.float32, torch.bfloat16), source.dtype
+    assert weights.dtype == torch.float32, weights.dtype
+    assert indexes.dim() == 2 and source.dim() == 2 and weights.dim() == 2
+    assert weights.shape == indexes.shape
+
+
+def weighted_vector_gather_add(indexes, source, weights, bias=None, out_dtype=None):
+    """outputs[b] = sum_i weights[b, i] * source[indexes[b, i]] (+ bias).
+    Reference: weighted_vector_gather_add(indexes, source, weights) (gather/cuda/kernel.py:22-70)."""
+    _check_gather_args(indexes, source, weights)
+    indexes, source, weights = _contig(indexes), _contig(source), _contig(weights)
+    N, I = indexes.shape
+    S, d = source.shape
+    out_dtype = source.dtype if out_dtype is None else out_dtype
+    out = torch.empty((N, d), dtype=out_dtype, device=source.device)
+    if bias is not None:
+        bias = _contig(bias.float())
+    with torch.cuda.device(source.device):
+        L.check(L.lib().lffn_gather_fwd(L.ptr(indexes), L.ptr(weights), L.ptr(source), L.dtype_code(source.dtype),
+                                        L.ptr(out), L.dtype_code(out_dtype), N, I, S, d, L.ptr(bias),
+                                        L.stream_ptr(source.device)))
+    return out
+
+
+def indexed_inner_product(indexes, source_1, source_2):
+    """outputs[b, i] = <source_1[b], source_2[indexes[b, i]]>, source_1 fp32 [N, d].
+    Reference: indexed_inner_product (gather/cuda/kernel.py:72-122)."""
+    L.require_cuda(indexes, source_1, source_2)
+    assert indexes.dtype == torch.int32 and source_1.dtype == torch.float32
+    indexes, source_1, source_2 = _contig(indexes), _contig(source_1), _contig(source_2)
+    N, I = indexes.shape
+    S, d = source_2.shape
+    assert source_1.shape == (N, d)
+    out = torch.empty((N, I), dtype=torch.float32, device=source_2.device)
+    with torch.cuda.device(source_2.device):
+        L.check(L.lib().lffn_gather_bwd_weights(L.ptr(indexes), L.ptr(source_1), L.ptr(source_2),
+                                                L.dtype_code(source_2.dtype), L.ptr(out), N, I, S, d,
+                                                L.stream_ptr(source_2.device)))
+    return out
+
+
+def weighted_vector_scatter_add(indexes, source, weights, output_size, structure=None):
+    """outputs[indexes[b, i]] += weights[b, i] * source[b]; outputs fp32 [output_size, d].
+    Reference: weighted_vector_scatter_add (gather/cuda/kernel.py:124-173).
+    structure=(T, m, rows) declares the layer's index structure (entry (b, t*m+c) lies in table t of
+    `rows` rows) and selects the deterministic sorted kernel; None accepts any index list."""
+    L.require_cuda(indexes, source, weights)
+    assert indexes.dtype == torch.int32 and source.dtype == torch.float32 and weights.dtype == torch.float32
+    indexes, source, weights = _contig(indexes), _contig(source), _contig(weights)
+    N, I = indexes.shape
+    d = source.shape[1]
+    out = torch.empty((output_size, d), dtype=torch.float32, device=source.device)
+    lib = L.lib()
+    with torch.cuda.device(source.device):
+        if structure is None:
+            L.check(lib.lffn_gather_bwd_tables(L.ptr(indexes), L.ptr(weights), L.ptr(source), L.ptr(out), N, I,
+                                               output_size, d, L.stream_ptr(source.device)))
+        else:
+            T, m, rows = structure
+            assert T * m == I and T * rows == output_size
+            nbytes = lib.lffn_gather_bwd_tables_sorted_scratch_bytes(N, T, m, rows)
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device=source.device)
+            L.check(lib.lffn_gather_bwd_tables_sorted(L.ptr(indexes), L.ptr(weights), L.ptr(source), L.ptr(out), N, T,
+                                                      m, rows, d, L.ptr(scratch), nbytes,
+                                                      L.stream_ptr(source.device)))
+    return out
+
+
+class WeightedVectorGatherAdd(torch.autograd.Function):
+    """Reference: WeightedVectorGatherAdd (gather/cuda/kernel.py:175-202): saves (indexes, source,
+    weights); backward returns (None, grad_source, grad_weights)."""
+
+    @staticmethod
+    def forward(ctx, indexes, source, weights, structure=None):
+        indexes, source, weights = _contig(indexes), _contig(source), _contig(weights)
+        ctx.save_for_backward(indexes, source, weights)
+        ctx.structure = structure
+        return weighted_vector_gather_add(indexes, source, weights)
+
+    @staticmethod
+    def backward(ctx, grad_outputs):
+        indexes, source, weights = ctx.saved_tensors
+        g = _contig(grad_outputs.float())
+        grad_source = grad_weights = None
+        if ctx.needs_input_grad[2]:
+            grad_weights = indexed_inner_product(indexes, g, source)
+        if ctx.needs_input_grad[1]:
+            grad_source = weighted_vector_scatter_add(indexes, g, weights, source.shape[0], ctx.structure)
+            grad_source = grad_source.to(source.dtype)
+        return None, grad_source, grad_weights, None
+
+
+def weighted_gather_add(indexes, source, weights, structure=None):
+    return WeightedVectorGatherAdd.apply(indexes, source, weights, structure)
+
+
+def gather(indices, weights, tables, training=False, structure=None):
+    """Reference: gather(indices, weights, tables, training) (gather/kernel.py:11-25).  `indices`
+    already carry the table offsets; tables is [S, d]."""
+    return weighted_gather_add(indices, tables, weights, structure)
+
+
+def padded_dim(d_in):
+    return int(2 ** math.ceil(math.log2(d_in)))

@@ -1,0 +1,415 @@
+"""Parity of the CUDA kernels (called through the C ABI of liblookupffn.so) with the CPU oracle
+and the reference-generated golden vectors.  Bars: hash codes / row indices bit-exact; projected
+coordinates z bit-exact (same butterfly order and fmaf chains); gather outputs bit-exact for fp32
+and bf16 storage (one fmaf chain per column); weights (expf) within 1e-5 relative; gradient of the
+weights within 1e-4 relative (different reduction order); sorted table gradient bit-exact, vector-
+reduction table gradient within 1e-5 relative."""
+from argparse import Namespace
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from lookupffn_b200 import _lib
+
+    _lib.lib()  # fail here, loudly, if the CUDA library was not built
+    return torch.device("cuda:0")
+
+
+def rel_err(a, b):
+    a = np.asarray(a, dtype=np.float64)
+    b = np.asarray(b, dtype=np.float64)
+    return np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)
+
+
+def t2n(t):
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+def bf16_tensor(bits, dev):
+    return torch.from_numpy(bits.view(np.int16)).to(dev).view(torch.bfloat16)
+
+
+# ---- Hadamard ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("D", [32, 64, 128, 256, 512, 1024, 2048])
+def test_fwht_bit_exact(dev, D):
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(D)
+    for N in (1, 13, 300):
+        x = rng.randn(N, D).astype(np.float32)
+        y = ops.hadamard(torch.from_numpy(x).to(dev))
+        np.testing.assert_array_equal(t2n(y), O.fwht(x))
+    x = rng.randn(9, D).astype(np.float32)
+    y = ops.hadamard(torch.from_numpy(x).to(dev), scale=0.125)
+    np.testing.assert_array_equal(t2n(y), O.fwht(x, 0.125))
+    # bf16 storage: widen exactly, transform in fp32, round once
+    xb = O.f32_to_bf16_bits(x)
+    yb = ops.hadamard(bf16_tensor(xb, dev))
+    np.testing.assert_array_equal(t2n(yb), O.f32_to_bf16_bits(O.fwht(O.bf16_bits_to_f32(xb))))
+
+
+def test_fwht_matches_reference_golden(dev, golden):
+    from lookupffn_b200 import ops
+
+    for D in (64, 256, 1024):
+        y = ops.hadamard(torch.from_numpy(golden[f"had_{D}_x"]).to(dev))
+        assert rel_err(t2n(y), golden[f"had_{D}_y"]) < 1e-5  # reference = fp32 matmul with H
+
+
+# ---- hashing ---------------------------------------------------------------------------------------
+def make_proj(rng, D, BS, S, R, signs):
+    NB = D // BS
+    if signs:
+        return (2.0 * rng.randint(0, 2, size=(R, S, NB, BS, BS)) - 1.0).astype(np.float32)
+    return (rng.randn(R, S, NB, BS, BS) / np.sqrt(BS * D)).astype(np.float32)
+
+
+HASH_CASES = [
+    # N, d_in, D, BS, S, T, k, weight_mode, bit_order, had_scale, mix
+    (37, 100, 128, 1, 2, 50, 6, O.WEIGHT_SCORE, O.MSB_FIRST, 1.0, (0.7, 0.3)),      # tables straddle rotations
+    (64, 128, 128, 1, 2, 64, 8, O.WEIGHT_ONES, O.LSB_FIRST, 2.0 ** -7, (1.0, 0.0)),  # sign-diagonal, LSB, ones
+    (33, 512, 512, 1, 2, 128, 8, O.WEIGHT_ONES, O.LSB_FIRST, 1.0 / np.sqrt(512), (1.0, 0.0)),  # benchmark config 1
+    (20, 768, 1024, 1, 2, 512, 8, O.WEIGHT_SCORE, O.MSB_FIRST, 1.0 / 32, (1.0, 0.0)),  # benchmark config 3
+    (9, 768, 1024, 1, 2, 100, 10, O.WEIGHT_SCORE, O.MSB_FIRST, 1.0, (0.7, 0.3)),
+    (9, 300, 512, 1, 4, 90, 12, O.WEIGHT_SCORE, O.LSB_FIRST, 1.0, (0.7, 0.3)),
+    (5, 64, 64, 1, 2, 40, 1, O.WEIGHT_SCORE, O.MSB_FIRST, 1.0, (0.7, 0.3)),
+    (5, 200, 256, 1, 2, 30, 16, O.WEIGHT_ONES, O.MSB_FIRST, 1.0, (0.7, 0.3)),
+    (7, 1500, 2048, 1, 2, 300, 8, O.WEIGHT_SCORE, O.MSB_FIRST, 1.0, (0.7, 0.3)),
+    (40, 100, 128, 1, 2, 30, 8, O.WEIGHT_SOFT_FLIP, O.MSB_FIRST, 1.0 / 8, (1.0, 0.0)),  # benchmark config 4 weights
+    (11, 100, 128, 1, 2, 21, 6, O.WEIGHT_SOFT_FLIP, O.LSB_FIRST, 1.0 / 8, (1.0, 0.0)),
+    # block-diagonal projection (the reference's BH4)
+    (70, 512, 512, 64, 4, 128, 8, O.WEIGHT_SCORE, O.MSB_FIRST, 1.0, (0.7, 0.3)),    # reference config t128
+    (33, 768, 1024, 64, 4, 160, 8, O.WEIGHT_SCORE, O.MSB_FIRST, 1.0, (0.7, 0.3)),
+    (40, 100, 128, 64, 4, 50, 6, O.WEIGHT_SCORE, O.MSB_FIRST, 1.0, (0.7, 0.3)),
+    (10, 60, 64, 16, 4, 20, 8, O.WEIGHT_ONES, O.LSB_FIRST, 1.0, (0.7, 0.3)),
+    (10, 250, 256, 128, 2, 40, 10, O.WEIGHT_SCORE, O.MSB_FIRST, 1.0, (0.7, 0.3)),
+    (6, 256, 256, 4, 4, 64, 8, O.WEIGHT_SOFT_FLIP, O.MSB_FIRST, 1.0, (0.7, 0.3)),
+]
+
+
+@pytest.mark.parametrize("case", HASH_CASES, ids=[f"c{i}" for i in range(len(HASH_CASES))])
+@pytest.mark.parametrize("transpose_w", [False, True])
+def test_hash_fwd_matches_oracle(dev, case, transpose_w):
+    from lookupffn_b200 import ops
+
+    N, d_in, D, BS, S, T, k, wm, bo, hs, mix = case
+    if BS == 1 and transpose_w:
+        pytest.skip("a diagonal has no transpose")
+    rng = np.random.RandomState(N * 1000 + T)
+    R = max(1, -(-T * k // D))
+    w = make_proj(rng, D, BS, S, R, signs=(BS == 1))
+    bias = (0.05 * rng.randn(T * k)).astype(np.float32)
+    x = rng.randn(N, d_in).astype(np.float32)
+    z_ref = O.project(x, w, T * k, transpose_w=transpose_w, had_scale=hs, mix_a=mix[0], mix_b=mix[1], bias=bias)
+    idx_ref, w_ref = O.code_weights(z_ref, T, k, bit_order=bo, weight_mode=wm, tau=0.5)
+
+    wt, bt = torch.from_numpy(w).to(dev), torch.from_numpy(bias).to(dev)
+    desc = ops.make_hash_desc(d_in, wt, bt, T, k, transpose_w=transpose_w, had_scale=float(np.float32(hs)),
+                              mix_a=mix[0], mix_b=mix[1], bit_order=bo, weight_mode=wm, tau=0.5)
+    idx, wgt, z = ops.hash_fwd(torch.from_numpy(x).to(dev), desc, want_z=True)
+    np.testing.assert_array_equal(t2n(z), z_ref)           # projected coordinates: bit-exact
+    np.testing.assert_array_equal(t2n(idx), idx_ref)       # codes + offsets: bit-exact
+    assert rel_err(t2n(wgt), w_ref) < 1e-5                 # weights: expf accuracy
+    # a sub-range of tables (what a table-sharded rank computes) equals the slice of the whole
+    m = k + 1 if wm == O.WEIGHT_SOFT_FLIP else 1
+    tb, tc = T // 3, T - T // 3 - 1
+    idx_s, w_s, z_s = ops.hash_fwd(torch.from_numpy(x).to(dev), desc, t_begin=tb, t_count=tc, want_z=True)
+    np.testing.assert_array_equal(t2n(z_s), z_ref[:, tb * k:(tb + tc) * k])
+    np.testing.assert_array_equal(t2n(idx_s), idx_ref[:, tb * m:(tb + tc) * m] - tb * (1 << k))
+    np.testing.assert_array_equal(t2n(w_s), t2n(wgt)[:, tb * m:(tb + tc) * m])
+
+
+def test_hash_bf16_input(dev):
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(5)
+    N, d_in, D, T, k = 50, 768, 1024, 512, 8
+    w = make_proj(rng, D, 1, 2, 4, signs=True)
+    xb = O.f32_to_bf16_bits(rng.randn(N, d_in).astype(np.float32))
+    z_ref = O.project(O.bf16_bits_to_f32(xb), w, T * k, had_scale=1 / 32, mix_a=1.0, mix_b=0.0)
+    idx_ref, w_ref = O.code_weights(z_ref, T, k)
+    desc = ops.make_hash_desc(d_in, torch.from_numpy(w).to(dev), None, T, k, had_scale=1 / 32, mix_a=1.0, mix_b=0.0)
+    idx, wgt, z = ops.hash_fwd(bf16_tensor(xb, dev), desc, want_z=True)
+    np.testing.assert_array_equal(t2n(z), z_ref)
+    np.testing.assert_array_equal(t2n(idx), idx_ref)
+    assert rel_err(t2n(wgt), w_ref) < 1e-5
+
+
+@pytest.mark.parametrize("tag,T,k", [("k8", 12, 8), ("k6", 10, 6), ("k10", 5, 10), ("k1", 4, 1)])
+def test_code_weights_matches_reference_golden(dev, golden, tag, T, k):
+    from lookupffn_b200 import ops
+
+    z = torch.from_numpy(golden[f"ccs_{tag}_z"]).to(dev)
+    code, score = ops.compute_code_score(z)
+    np.testing.assert_array_equal(t2n(code), golden[f"ccs_{tag}_code_torch"])
+    np.testing.assert_array_equal(t2n(code), golden[f"ccs_{tag}_code_cpp"])
+    assert rel_err(t2n(score), golden[f"ccs_{tag}_score_cpp"]) < 1e-5
+
+
+def test_code_edge_values(dev):
+    from lookupffn_b200 import ops
+
+    z = torch.tensor([[[0.0, -0.0, float("nan"), 1e-45, -1e-45, float("inf"), -float("inf"), 3.0]]], device=dev)
+    code, _ = ops.compute_code_score(z, weight_mode=O.WEIGHT_ONES)
+    assert int(code[0, 0]) == 0b00010101
+    code, _ = ops.compute_code_score(z, weight_mode=O.WEIGHT_ONES, bit_order=O.LSB_FIRST)
+    assert int(code[0, 0]) == 0b10101000
+
+
+def test_bh4_matches_reference_golden(dev, golden):
+    from lookupffn_b200 import ops
+    from lookupffn_b200.lookup import BH4
+
+    for tag in ("a", "b", "c", "d"):
+        in_dim, out_dim, BS, D, R = [int(v) for v in golden[f"bh4_{tag}_meta"]]
+        x = golden[f"bh4_{tag}_x"]
+        w = torch.from_numpy(golden[f"bh4_{tag}_w"]).to(dev)
+        xp = np.zeros((x.shape[0], D), dtype=np.float32)
+        xp[:, :in_dim] = x
+        P = ops.bh4(torch.from_numpy(xp).to(dev), w)
+        assert rel_err(t2n(P), golden[f"bh4_{tag}_P"]) < 2e-5   # reference = torch einsum + matmul with H
+        mod = BH4(in_dim, out_dim, BS).to(dev)
+        with torch.no_grad():
+            mod.weight.copy_(w)
+            mod.bias.copy_(torch.from_numpy(golden[f"bh4_{tag}_bias"]))
+        z = t2n(mod(torch.from_numpy(x).to(dev)))
+        zr = golden[f"bh4_{tag}_z"]
+        assert rel_err(z, zr) < 2e-5
+        diff = (z > 0) != (zr > 0)
+        assert np.abs(zr[diff]).max(initial=0.0) < 1e-5
+
+
+# ---- gather forward ----------------------------------------------------------------------------------
+GATHER_CASES = [
+    # N, I, S, d
+    (1, 1, 5, 4), (7, 3, 50, 16), (33, 18, 333, 64), (64, 128, 32768, 512), (20, 512, 4096, 768),
+    (5, 37, 1000, 1024), (3, 64, 500, 1536), (4, 10, 100, 2052), (6, 70, 900, 4096), (17, 0, 9, 64),
+    (40, 4608, 2000, 768),
+]
+
+
+@pytest.mark.parametrize("N,I,S,d", GATHER_CASES)
+def test_gather_fwd_fp32_bit_exact(dev, N, I, S, d):
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(N + I + d)
+    idx = rng.randint(0, S, size=(N, I)).astype(np.int32)
+    w = rng.randn(N, I).astype(np.float32)
+    tab = (0.02 * rng.randn(S, d)).astype(np.float32)
+    bias = rng.randn(d).astype(np.float32)
+    ti, tw, tt, tb = (torch.from_numpy(a).to(dev) for a in (idx, w, tab, bias))
+    np.testing.assert_array_equal(t2n(ops.weighted_vector_gather_add(ti, tt, tw)), O.gather(idx, w, tab))
+    np.testing.assert_array_equal(t2n(ops.weighted_vector_gather_add(ti, tt, tw, bias=tb)),
+                                  O.gather(idx, w, tab, bias=bias))
+    out_b = ops.weighted_vector_gather_add(ti, tt, tw, bias=tb, out_dtype=torch.bfloat16)
+    np.testing.assert_array_equal(t2n(out_b), O.gather(idx, w, tab, bias=bias, out_bf16=True))
+
+
+@pytest.mark.parametrize("N,I,S,d", [c for c in GATHER_CASES if c[3] % 8 == 0])
+def test_gather_fwd_bf16_bit_exact(dev, N, I, S, d):
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(N + I + d + 1)
+    idx = rng.randint(0, S, size=(N, I)).astype(np.int32)
+    w = rng.randn(N, I).astype(np.float32)
+    tab = O.f32_to_bf16_bits((0.02 * rng.randn(S, d)).astype(np.float32))
+    bias = rng.randn(d).astype(np.float32)
+    ti, tw, tb = (torch.from_numpy(a).to(dev) for a in (idx, w, bias))
+    tt = bf16_tensor(tab, dev)
+    out = ops.weighted_vector_gather_add(ti, tt, tw, bias=tb)
+    assert out.dtype == torch.bfloat16
+    np.testing.assert_array_equal(t2n(out), O.gather(idx, w, tab, bias=bias, out_bf16=True))
+    out32 = ops.weighted_vector_gather_add(ti, tt, tw, out_dtype=torch.float32)
+    np.testing.assert_array_equal(t2n(out32), O.gather(idx, w, tab))
+
+
+def test_gather_matches_reference_golden(dev, golden):
+    from lookupffn_b200 import ops
+
+    for tag in ("a", "b"):
+        ti, tw, tt = (torch.from_numpy(golden[f"gat_{tag}_{n}"]).to(dev) for n in ("idx", "w", "tables"))
+        out = t2n(ops.weighted_vector_gather_add(ti, tt, tw))
+        assert rel_err(out, golden[f"gat_{tag}_out_scalar"]) < 1e-6
+        assert rel_err(out, golden[f"gat_{tag}_out_torch"]) < 1e-6
+
+
+def test_gather_out_of_range_index_is_skipped_and_flagged(dev):
+    from lookupffn_b200 import _lib, ops
+
+    rng = np.random.RandomState(3)
+    N, I, S, d = 9, 12, 40, 64
+    idx = rng.randint(0, S, size=(N, I)).astype(np.int32)
+    idx[2, 5] = S
+    idx[4, 0] = -1
+    w = rng.randn(N, I).astype(np.float32)
+    tab = rng.randn(S, d).astype(np.float32)
+    _lib.device_status(dev)
+    out = ops.weighted_vector_gather_add(*(torch.from_numpy(a).to(dev) for a in (idx, tab, w)))
+    ref, bad = O.gather(idx, w, tab, return_bad=True)
+    assert bad == 2
+    np.testing.assert_array_equal(t2n(out), ref)
+    assert _lib.device_status(dev) & _lib.STATUS_INDEX_RANGE
+    assert _lib.device_status(dev) == 0  # reading clears it
+
+
+# ---- gather backward --------------------------------------------------------------------------------------
+BWD_CASES = [(1, 1, 5, 4), (32, 8, 300, 64), (19, 33, 777, 768), (8, 64, 100, 1024), (5, 40, 64, 1536), (6, 90, 64, 3072)]
+
+
+@pytest.mark.parametrize("N,I,S,d", BWD_CASES)
+def test_gather_bwd_weights(dev, N, I, S, d):
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(N + I)
+    idx = rng.randint(0, S, size=(N, I)).astype(np.int32)
+    tab = (0.02 * rng.randn(S, d)).astype(np.float32)
+    dy = rng.randn(N, d).astype(np.float32)
+    ti, tt, tg = (torch.from_numpy(a).to(dev) for a in (idx, tab, dy))
+    assert rel_err(t2n(ops.indexed_inner_product(ti, tg, tt)), O.gather_bwd_weights(idx, dy, tab)) < 1e-4
+    if d % 8 == 0:
+        tb = O.f32_to_bf16_bits(tab)
+        assert rel_err(t2n(ops.indexed_inner_product(ti, tg, bf16_tensor(tb, dev))),
+                       O.gather_bwd_weights(idx, dy, tb)) < 1e-4
+
+
+@pytest.mark.parametrize("N,I,S,d", BWD_CASES)
+def test_gather_bwd_tables_any_index_list(dev, N, I, S, d):
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(N + I + 7)
+    idx = rng.randint(0, S, size=(N, I)).astype(np.int32)
+    idx[0, :] = min(3, S - 1)  # many terms on one row
+    w = rng.randn(N, I).astype(np.float32)
+    dy = rng.randn(N, d).astype(np.float32)
+    ti, tw, tg = (torch.from_numpy(a).to(dev) for a in (idx, w, dy))
+    out = ops.weighted_vector_scatter_add(ti, tg, tw, S)
+    assert rel_err(t2n(out), O.gather_bwd_tables(idx, w, dy, S)) < 1e-5
+
+
+@pytest.mark.parametrize("N,T,m,rows,d", [(1, 1, 1, 2, 4), (50, 6, 1, 256, 64), (300, 5, 9, 256, 768),
+                                           (700, 3, 1, 64, 512), (64, 4, 7, 4096, 128), (2000, 2, 1, 16, 1024)])
+def test_gather_bwd_tables_sorted_bit_exact_and_deterministic(dev, N, T, m, rows, d):
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(N + T)
+    idx = (rng.randint(0, rows, size=(N, T, m)) + (np.arange(T) * rows)[None, :, None]).astype(np.int32).reshape(N, T * m)
+    w = rng.randn(N, T * m).astype(np.float32)
+    dy = rng.randn(N, d).astype(np.float32)
+    ti, tw, tg = (torch.from_numpy(a).to(dev) for a in (idx, w, dy))
+    out1 = t2n(ops.weighted_vector_scatter_add(ti, tg, tw, T * rows, structure=(T, m, rows)))
+    out2 = t2n(ops.weighted_vector_scatter_add(ti, tg, tw, T * rows, structure=(T, m, rows)))
+    np.testing.assert_array_equal(out1, out2)
+    np.testing.assert_array_equal(out1, O.gather_bwd_tables(idx, w, dy, T * rows))
+
+
+def test_gather_backward_matches_reference_golden(dev, golden):
+    from lookupffn_b200 import ops
+
+    ti, tw, tt, tg = (torch.from_numpy(golden[f"bwd_{n}"]).to(dev) for n in ("idx", "w", "tables", "dy"))
+    tt.requires_grad_(True)
+    tw.requires_grad_(True)
+    out = ops.weighted_gather_add(ti, tt, tw)
+    out.backward(tg)
+    assert rel_err(t2n(out.detach()), golden["bwd_out"]) < 1e-6
+    assert rel_err(t2n(tw.grad), golden["bwd_dw"]) < 1e-5
+    assert rel_err(t2n(tt.grad), golden["bwd_dtables"]) < 1e-5
+
+
+# ---- the module ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tag", ["bh4", "dense"])
+def test_module_matches_reference_golden(dev, golden, tag):
+    from lookupffn_b200 import LookupFFN
+
+    sd = {k[len(f"mod_{tag}_param_"):]: torch.from_numpy(v) for k, v in golden.items()
+          if k.startswith(f"mod_{tag}_param_")}
+    T, rows, d_out = sd["tables"].shape
+    cfg = Namespace(hidden_size=sd["LayerNorm.weight"].numel(), ffn_num_table=T, ffn_table_size=rows,
+                    layer_norm_eps=1e-5, projection_type=tag, block_size=64)
+    mod = LookupFFN(cfg, d_out)
+    mod.load_state_dict(sd, strict=True)
+    mod = mod.to(dev).eval()
+    x = torch.from_numpy(golden[f"mod_{tag}_x"]).to(dev)
+    with torch.no_grad():
+        y = mod(x)
+        u = mod.LayerNorm(x.reshape(-1, x.shape[-1]))
+        idx, w = mod.hash(u)
+    assert y.shape == golden[f"mod_{tag}_y"].shape  # leading dims kept (lookup.py:112-118)
+    code = t2n(idx) - (np.arange(T) * rows)[None].astype(np.int32)
+    ref_code = golden[f"mod_{tag}_code"]
+    # LayerNorm and (dense) the projection run in torch on the GPU: coordinates at rounding level may flip
+    zr = golden[f"mod_{tag}_z"].reshape(-1, T, int(np.log2(rows)))
+    flipped = code != ref_code
+    assert np.abs(zr[flipped]).min(axis=-1).max(initial=0.0) < 1e-5
+    if not flipped.any():
+        assert rel_err(t2n(w), golden[f"mod_{tag}_score"]) < 1e-4
+        assert rel_err(t2n(y), golden[f"mod_{tag}_y"]) < 1e-4
+
+
+def test_module_backward_tables_and_bias(dev):
+    from lookupffn_b200 import LookupFFN
+
+    torch.manual_seed(0)
+    cfg = Namespace(hidden_size=96, ffn_num_table=12, ffn_table_size=64, layer_norm_eps=1e-5,
+                    projection_type="bh4", block_size=32)
+    mod = LookupFFN(cfg, 64).to(dev).train()
+    x = torch.randn(4, 10, 96, device=dev)
+    y = mod(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    with torch.no_grad():
+        u = mod.LayerNorm(x.reshape(-1, 96))
+        idx, w = mod.hash(u)
+    ref = O.gather_bwd_tables(t2n(idx), t2n(w), t2n(g.reshape(-1, 64)), 12 * 64)
+    np.testing.assert_array_equal(t2n(mod.tables.grad).reshape(12 * 64, 64), ref)
+    assert rel_err(t2n(mod.bias.grad), t2n(g.reshape(-1, 64).sum(0))) < 1e-5
+
+
+# ---- full-size properties (benchmark config 3) -------------------------------------------------------------------
+def test_full_size_forward_properties(dev):
+    from lookupffn_b200 import ops
+
+    N, d_in, D, T, k, d_out = 65536, 768, 1024, 512, 8, 768
+    g = torch.Generator(device=dev).manual_seed(1)
+    x = torch.randn(N, d_in, generator=g, device=dev).to(torch.bfloat16)
+    tables = (0.02 * torch.randn(T << k, d_out, generator=g, device=dev)).to(torch.bfloat16)
+    signs = (2 * torch.randint(0, 2, (4, 2, D, 1, 1), generator=g, device=dev) - 1).float()
+    desc = ops.make_hash_desc(d_in, signs, None, T, k, had_scale=1 / 32, mix_a=1.0, mix_b=0.0)
+    idx, w, _ = ops.hash_fwd(x, desc)
+    y = ops.weighted_vector_gather_add(idx, tables, w)
+    # a random sample of tokens against the oracle, end to end (codes exact, outputs bit-exact given equal weights)
+    sel = torch.randperm(N, generator=torch.Generator().manual_seed(2))[:64]
+    xs = t2n(x[sel.to(dev)])
+    z_ref = O.project(O.bf16_bits_to_f32(xs), t2n(signs), T * k, had_scale=1 / 32, mix_a=1.0, mix_b=0.0)
+    idx_ref, w_ref = O.code_weights(z_ref, T, k)
+    np.testing.assert_array_equal(t2n(idx[sel.to(dev)]), idx_ref)
+    assert rel_err(t2n(w[sel.to(dev)]), w_ref) < 1e-5
+    y_ref = O.gather(idx_ref, t2n(w[sel.to(dev)]), t2n(tables), out_bf16=True)
+    np.testing.assert_array_equal(t2n(y[sel.to(dev)]), y_ref)
+    # codes are in range and use every row of every table about equally
+    codes = idx - (torch.arange(T, device=dev, dtype=torch.int32) << k)[None]
+    assert int(codes.min()) >= 0 and int(codes.max()) < (1 << k)
+    # permutation equivariance: permuting tokens permutes outputs, bit for bit
+    perm = torch.randperm(N, generator=g, device=dev)
+    y_p = ops.weighted_vector_gather_add(idx[perm].contiguous(), tables, w[perm].contiguous())
+    assert torch.equal(y_p.view(torch.int16), y[perm].view(torch.int16))
+    # scaling weights by a power of two scales fp32 outputs exactly
+    y32 = ops.weighted_vector_gather_add(idx, tables, w, out_dtype=torch.float32)
+    y32_2 = ops.weighted_vector_gather_add(idx, tables, w * 4.0, out_dtype=torch.float32)
+    assert torch.equal(y32 * 4.0, y32_2)
+    # additivity over a split of the tables: the two halves' partial sums add up to the whole within rounding
+    h = (T // 2)
+    ya = ops.weighted_vector_gather_add(idx[:, :h].contiguous(), tables, w[:, :h].contiguous(), out_dtype=torch.float32)
+    yb = ops.weighted_vector_gather_add(idx[:, h:].contiguous(), tables, w[:, h:].contiguous(), out_dtype=torch.float32)
+    err = (ya + yb - y32).abs().max() / y32.abs().max()
+    assert float(err) < 1e-5
