@@ -37,9 +37,11 @@ WORKLOADS = {
     "c3": dict(N=65536, d_in=768, d_out=768, T=512, k=8, dtype="bf16", weight_mode="score", bit_order="msb"),
     "c5k8": dict(N=262144, d_in=1024, d_out=1024, T=256, k=8, dtype="bf16", weight_mode="score", bit_order="msb"),
 }
-# DRAM bytes per gather launch of workload c3 from one ncu capture (dram__bytes_read.sum +
-# dram__bytes_write.sum; see profiles/).  None until captured.
-NCU_TRAFFIC_BYTES = {"c3": None}
+# DRAM bytes per gather launch from one ncu capture (dram__bytes_read.sum + dram__bytes_write.sum).
+# c3: captured at 16384 tokens (1.513 GB: tables re-fetched once per wave of resident warps, plus
+# idx/w/y) and scaled by 4 to the 65536-token launch, traffic being proportional to the waves of
+# tokens; see profiles/gather_fwd_c3.md.
+NCU_TRAFFIC_BYTES = {"c3": 4 * 1.5135e9}
 
 
 def padded_dim(d):
@@ -61,7 +63,7 @@ def load_peaks():
 
 # ---- clocks ------------------------------------------------------------------------------------
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every 100 ms."""
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every 20 ms."""
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
@@ -96,7 +98,7 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self.stop_flag.wait(0.1)
+            self.stop_flag.wait(0.02)
 
     def result(self):
         self.stop_flag.set()
@@ -138,7 +140,9 @@ def run_ours(args, rank, world, local):
     from lookupffn_b200 import _lib as L
     from lookupffn_b200 import ops
 
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        w["N"] = args.tokens
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
     lib = L.lib()
@@ -193,6 +197,13 @@ def run_ours(args, rank, world, local):
     hash_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in events)
     gather_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in events)
     status = L.device_status(device)
+
+    if args.no_e2e:  # profiling runs: device path only
+        if rank == 0:
+            print(json.dumps({"workload": args.workload, "N": N, "hash_ms": hash_ms, "gather_ms": gather_ms,
+                              "ms_per_step": elapsed_ms / args.steps,
+                              "gather_GBps": algorithmic_bytes_per_token(w) * N / gather_ms / 1e6}), flush=True)
+        return None
 
     # ---- end to end through the host-buffer entry point -------------------------------------------
     chunk = args.e2e_chunk
@@ -354,13 +365,15 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-chunk", type=int, default=8192)
     ap.add_argument("--cpu-tokens", type=int, default=4096)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on a small case)")
+    ap.add_argument("--no-e2e", action="store_true", help="device path only, short report (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 

@@ -9,7 +9,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "liblookupffn.so")
+# LFFN_LIBRARY_PATH selects another build of the same library (e.g. a tuning variant)
+LIB_PATH = os.environ.get("LFFN_LIBRARY_PATH") or os.path.join(_HERE, "liblookupffn.so")
 
 F32, BF16 = 0, 1
 MSB_FIRST, LSB_FIRST = 0, 1

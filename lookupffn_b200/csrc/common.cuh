@@ -58,9 +58,28 @@ int launch_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const fl
 // 16-byte read-only load that does not allocate in L1: table rows are touched once per SM.
 __device__ __forceinline__ uint4 ld_row16(const void *p) {
     uint4 v;
+#ifdef LFFN_ROW_LOAD_L1_ALLOCATE
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+#else
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+#endif
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
+    return v;
+}
+
+// the same load under a predicate (no branch); returns zeros when the predicate is false
+__device__ __forceinline__ uint4 ld_row16_pred(const void *p, bool pred) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile(
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+#ifdef LFFN_ROW_LOAD_L1_ALLOCATE
+        "@q ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+#else
+        "@q ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+#endif
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "l"(p), "r"((int)pred));
     return v;
 }
 

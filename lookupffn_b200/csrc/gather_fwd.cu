@@ -18,10 +18,28 @@
 // processed tokens even when the whole table set exceeds L2.
 #include "common.cuh"
 
+// Tuning constants (overridable at compile time): rows in flight per warp for narrow / medium /
+// wide rows, threads per CTA and the minimum CTAs per SM the register allocation must allow.
+#ifndef LFFN_GATHER_U_NARROW
+#define LFFN_GATHER_U_NARROW 4
+#endif
+#ifndef LFFN_GATHER_U_MEDIUM
+#define LFFN_GATHER_U_MEDIUM 2
+#endif
+#ifndef LFFN_GATHER_U_WIDE
+#define LFFN_GATHER_U_WIDE 2
+#endif
+#ifndef LFFN_GATHER_THREADS
+#define LFFN_GATHER_THREADS 128
+#endif
+#ifndef LFFN_GATHER_MINBLOCKS
+#define LFFN_GATHER_MINBLOCKS 4
+#endif
+
 namespace lffn {
 
-template <typename TableT, typename OutT, int VPL, int U>
-__global__ void __launch_bounds__(256) gather_fwd_kernel(const int32_t *__restrict__ idx, const float *__restrict__ w,
+template <typename TableT, typename OutT, int VPL, int U, bool FULLV>
+__global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) gather_fwd_kernel(const int32_t *__restrict__ idx, const float *__restrict__ w,
                                                          const TableT *__restrict__ tables, OutT *__restrict__ out,
                                                          long long N, int I, long long S, int d, int col0,
                                                          const float *__restrict__ bias, const int2 *__restrict__ seg,
@@ -66,35 +84,41 @@ __global__ void __launch_bounds__(256) gather_fwd_kernel(const int32_t *__restri
                 my_w = __ldg(wp + g0 + 32 + lane);
             }
             const int cnt = min(32, I - g0);
+            // The loop body is branch-free: an entry past the end of the list, or with an index outside
+            // [0, S), is replaced by (the group's first row, weight 0).  That row is part of the sum anyway,
+            // so the substitute adds exactly nothing even when the row holds Inf or NaN.
+            int safe = __shfl_sync(FULL, cur_i, 0);
+            safe = (unsigned long long)(long long)safe < (unsigned long long)S ? safe : 0;
 #pragma unroll 1
             for (int j0 = 0; j0 < cnt; j0 += U) {
                 uint4 buf[U][VPL];
                 float ww[U];
-                bool ok[U];
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     const int j = j0 + u;
-                    const int r = __shfl_sync(FULL, cur_i, j & 31);
-                    ww[u] = __shfl_sync(FULL, cur_w, j & 31);
-                    ok[u] = j < cnt && (unsigned long long)(long long)r < (unsigned long long)S;
-                    if (j < cnt && !ok[u]) bad = true;
-                    const uint4 *row = tv + (long long)(ok[u] ? r : 0) * row_vecs;
+                    int r = __shfl_sync(FULL, cur_i, j & 31);
+                    float wj = __shfl_sync(FULL, cur_w, j & 31);
+                    const bool in_list = j < cnt;
+                    const bool in_range = (unsigned long long)(long long)r < (unsigned long long)S;
+                    bad |= in_list && !in_range;
+                    const bool ok = in_list && in_range;
+                    r = ok ? r : safe;
+                    ww[u] = ok ? wj : 0.f;
+                    const uint4 *row = tv + (long long)r * row_vecs;
 #pragma unroll
                     for (int v = 0; v < VPL; v++) {
                         const int c = lane + 32 * v;
-                        if (ok[u] && c < nvec) buf[u][v] = ld_row16(row + c);
+                        buf[u][v] = FULLV ? ld_row16(row + c) : ld_row16_pred(row + c, c < nvec);
                     }
                 }
 #pragma unroll
                 for (int u = 0; u < U; u++) {
-                    if (ok[u]) {
 #pragma unroll
-                        for (int v = 0; v < VPL; v++) {
-                            float f[EPV];
-                            Elem<TableT>::unpack(buf[u][v], f);
+                    for (int v = 0; v < VPL; v++) {
+                        float f[EPV];
+                        Elem<TableT>::unpack(buf[u][v], f);
 #pragma unroll
-                            for (int e = 0; e < EPV; e++) acc[v][e] = fmaf(ww[u], f[e], acc[v][e]);
-                        }
+                        for (int e = 0; e < EPV; e++) acc[v][e] = fmaf(ww[u], f[e], acc[v][e]);
                     }
                 }
             }
@@ -138,12 +162,12 @@ __global__ void __launch_bounds__(256) gather_fwd_kernel(const int32_t *__restri
     if (bad) atomicOr(status, LFFN_STATUS_INDEX_RANGE);
 }
 
-template <typename TableT, typename OutT, int VPL>
-static int launch_vpl(const int32_t *idx, const float *w, const void *tables, void *out, int64_t N, int I, int64_t S,
+template <typename TableT, typename OutT, int VPL, bool FULLV>
+static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, void *out, int64_t N, int I, int64_t S,
                       int d, int col0, const float *bias, const int2 *seg, cudaStream_t st) {
-    constexpr int U = (VPL <= 3) ? 8 : (VPL <= 6 ? 4 : 2);
-    constexpr int THREADS = 256;
-    auto kern = gather_fwd_kernel<TableT, OutT, VPL, U>;
+    constexpr int U = (VPL <= 3) ? LFFN_GATHER_U_NARROW : (VPL <= 6 ? LFFN_GATHER_U_MEDIUM : LFFN_GATHER_U_WIDE);
+    constexpr int THREADS = LFFN_GATHER_THREADS;
+    auto kern = gather_fwd_kernel<TableT, OutT, VPL, U, FULLV>;
     int per_sm = 0;
     LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, 0));
     if (per_sm < 1) per_sm = 1;
@@ -155,6 +179,16 @@ static int launch_vpl(const int32_t *idx, const float *w, const void *tables, vo
                                              S, d, col0, bias, seg, status_word());
     LFFN_CHECK_CUDA(cudaGetLastError());
     return LFFN_OK;
+}
+
+// FULLV: the column tile is exactly VPL*32 vectors wide, so no lane needs a column predicate
+template <typename TableT, typename OutT, int VPL>
+static int launch_vpl(const int32_t *idx, const float *w, const void *tables, void *out, int64_t N, int I, int64_t S,
+                      int d, int col0, const float *bias, const int2 *seg, cudaStream_t st) {
+    const int nvec = min(d / Elem<TableT>::PER_VEC - col0, VPL * 32);
+    if (nvec == VPL * 32)
+        return launch_vpl_f<TableT, OutT, VPL, true>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st);
+    return launch_vpl_f<TableT, OutT, VPL, false>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st);
 }
 
 template <typename TableT, typename OutT>

@@ -53,17 +53,19 @@ def fast_hadamard_transform(X, scale=1.0):
 # ---- hashing ------------------------------------------------------------------------------------
 def make_hash_desc(d_in, proj_w, proj_bias, T, k, transpose_w=False, had_scale=1.0, mix_a=0.7, mix_b=1 - 0.7,
                    bit_order=MSB_FIRST, weight_mode=WEIGHT_SCORE, tau=0.5):
-    """proj_w [R, S, D/BS, BS, BS] fp32 CUDA tensor.  The descriptor holds raw pointers: keep the
-    tensors alive while it is used."""
+    """proj_w [R, S, D/BS, BS, BS] fp32 CUDA tensor.  The descriptor holds raw pointers and keeps a
+    reference to the tensors so that they outlive it."""
     L.require_cuda(proj_w, proj_bias)
     assert proj_w.dtype == torch.float32 and proj_w.is_contiguous() and proj_w.dim() == 5
     R, S, NB, BS, BS2 = proj_w.shape
     assert BS == BS2
     if proj_bias is not None:
         assert proj_bias.dtype == torch.float32 and proj_bias.is_contiguous() and proj_bias.numel() == T * k
-    return L.HashDesc(d_in=d_in, D=NB * BS, BS=BS, S=S, R=R, transpose_w=int(transpose_w), had_scale=had_scale,
+    desc = L.HashDesc(d_in=d_in, D=NB * BS, BS=BS, S=S, R=R, transpose_w=int(transpose_w), had_scale=had_scale,
                       mix_a=mix_a, mix_b=mix_b, T=T, k=k, bit_order=bit_order, weight_mode=weight_mode, tau=tau,
                       proj_w=proj_w.data_ptr(), proj_bias=0 if proj_bias is None else proj_bias.data_ptr())
+    desc._keepalive = (proj_w, proj_bias)  # the struct holds raw pointers; pin the tensors to its lifetime
+    return desc
 
 
 def hash_fwd(x, desc, t_begin=0, t_count=None, want_z=False, want_codes=True):
