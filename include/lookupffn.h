@@ -168,6 +168,27 @@ int lffn_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const floa
                                   size_t scratch_bytes, lffn_stream_t stream);
 
 /*
+ * The sorted table gradient for callers that are not allowed to allocate device memory.  (No counterpart in
+ * the reference: its scatter-add needs no scratch.)  Such callers exist: a plugin running inside a host
+ * whose memory pool is fixed at start-up, code on a stream that is being captured, a real-time loop that
+ * must not take the allocator's lock.  They cannot hand lffn_gather_bwd_tables_sorted its scratch buffer, so
+ * this variant sorts into an array compiled into the library, LFFN_STATIC_SCRATCH_BYTES (32 MiB) long; every
+ * GPU that loads the library holds those bytes until the process exits.  Same arguments and bit-identical
+ * result.  It calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - Limit: lffn_gather_bwd_tables_sorted_scratch_bytes(N, T, m, rows) <= LFFN_STATIC_SCRATCH_BYTES, about
+ *     N*T*m <= 4.1 million entries; larger problems return LFFN_ERR_SCRATCH with the sizes in the message.
+ *   - The first call on each device looks up the array's device address (one runtime query, no
+ *     allocation); make that first call outside any stream capture.
+ *   - All calls on a device share the one array and find the previous call's bytes in it.  Nothing needs
+ *     clearing (every word a call reads it has written first), but two calls whose kernels overlap on the
+ *     GPU (different streams, or two host threads) race on it: serialise them.
+ */
+#define LFFN_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int lffn_gather_bwd_tables_sorted_static(const int32_t *idx, const float *w, const float *dy, float *dtables,
+                                         int64_t N, int32_t T, int32_t m, int32_t rows, int32_t d,
+                                         lffn_stream_t stream);
+
+/*
  * Whole layer forward on device buffers = LookupFFN._forward without LayerNorm (lookup.py:101-110):
  * hash -> gather -> + bias for tables [t_begin, t_begin + t_count) (`tables` points at the first
  * of those, [t_count * 2^k, d_out]).  idx_ws/w_ws are caller-provided workspaces of

@@ -16,6 +16,7 @@ F32, BF16 = 0, 1
 MSB_FIRST, LSB_FIRST = 0, 1
 WEIGHT_SCORE, WEIGHT_ONES, WEIGHT_SOFT_FLIP = 0, 1, 2
 STATUS_INDEX_RANGE, STATUS_STRUCTURE = 1, 2
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 ERR_NAMES = {-1: "INVALID_ARG", -2: "UNSUPPORTED", -3: "CUDA", -4: "INDEX_RANGE", -5: "SCRATCH"}
 
@@ -54,6 +55,8 @@ _SIGNATURES = {
     "lffn_gather_bwd_tables_sorted_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32, C.c_int32]),
     "lffn_gather_bwd_tables_sorted": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                                 C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "lffn_gather_bwd_tables_sorted_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                                       C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "lffn_layer_fwd": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                                  C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
                                  C.c_void_p, C.c_void_p]),

@@ -19,6 +19,8 @@
 // forward gather kernel sums each output row's terms in ascending (n, c) order from dy and
 // writes the row once: no atomics on the output, no memset, bit-reproducible, and equal to the
 // CPU oracle's fmaf chain.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace lffn {
@@ -400,4 +402,54 @@ int launch_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const fl
     return launch_gather_segmented(s.ent_n, s.ent_w, dy, dtables, (int64_t)T * rows, s.seg, N, d, st);
 }
 
+// ---- the same sorted table gradient for callers that cannot allocate device memory -------------------
+// Its scratch is this fixed array instead of a caller buffer.  The array is part of the library image:
+// every GPU that loads liblookupffn.so keeps these bytes reserved until the process exits.
+constexpr size_t STATIC_SCRATCH_BYTES = LFFN_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+// Host code cannot use `g_static_scratch` as a pointer: in host code that name is only a handle for the
+// runtime.  The real device address is asked for once per device (with that device current) and cached.
+static int static_scratch_address(void **out) {
+    static std::mutex mu;
+    static void *addr[64] = {nullptr};
+    int dev = 0;
+    LFFN_CHECK_CUDA(cudaGetDevice(&dev));
+    LFFN_REQUIRE(dev >= 0 && dev < 64, LFFN_ERR_UNSUPPORTED, "device ordinal %d", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+        void *p = nullptr;
+        LFFN_CHECK_CUDA(cudaGetSymbolAddress((void **)&p, g_static_scratch));
+        LFFN_REQUIRE(p != nullptr, LFFN_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return LFFN_OK;
+}
+
 }  // namespace lffn
+
+extern "C" int lffn_gather_bwd_tables_sorted_static(const int32_t *idx, const float *w, const float *dy,
+                                                    float *dtables, int64_t N, int32_t T, int32_t m, int32_t rows,
+                                                    int32_t d, lffn_stream_t stream) {
+    using namespace lffn;
+    LFFN_REQUIRE(N >= 0 && T >= 1 && m >= 1 && rows >= 1 && d >= 1, LFFN_ERR_INVALID_ARG,
+                 "gather_bwd_tables_sorted_static: bad sizes N=%lld T=%d m=%d rows=%d d=%d", (long long)N, T, m, rows, d);
+    LFFN_REQUIRE(d % 4 == 0, LFFN_ERR_UNSUPPORTED, "gather_bwd_tables_sorted_static: d = %d must be a multiple of 4", d);
+    LFFN_REQUIRE(dtables != nullptr && (N == 0 || (idx != nullptr && w != nullptr && dy != nullptr)),
+                 LFFN_ERR_INVALID_ARG, "gather_bwd_tables_sorted_static: NULL buffer");
+    LFFN_REQUIRE((reinterpret_cast<uintptr_t>(dtables) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dy) & 15u) == 0,
+                 LFFN_ERR_INVALID_ARG, "gather_bwd_tables_sorted_static: dtables and dy must be 16-byte aligned");
+    LFFN_REQUIRE((long long)T * rows < (1ll << 31), LFFN_ERR_UNSUPPORTED,
+                 "gather_bwd_tables_sorted_static: T*rows does not fit int32 indices");
+    const size_t need = sorted_scratch_bytes(N, T, m, rows);
+    LFFN_REQUIRE(need <= STATIC_SCRATCH_BYTES, LFFN_ERR_SCRATCH,
+                 "gather_bwd_tables_sorted_static: this problem needs %zu bytes of scratch, the built-in array holds "
+                 "%zu (N*T*m = %lld entries); use lffn_gather_bwd_tables_sorted with a caller buffer",
+                 need, STATIC_SCRATCH_BYTES, (long long)N * T * m);
+    void *scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != LFFN_OK) return rc;
+    return launch_gather_bwd_tables_sorted(idx, w, dy, dtables, N, T, m, rows, d, scratch, STATIC_SCRATCH_BYTES,
+                                           static_cast<cudaStream_t>(stream));
+}
