@@ -29,13 +29,24 @@ int launch_gather_segmented(const int32_t *idx, const float *w, const float *src
                             const int2 *seg, int64_t n_src, int d, cudaStream_t st);  // gather_fwd.cu
 
 // ---- dw ----------------------------------------------------------------------------------------
-template <typename TableT, int VPL, int U>
-__global__ void __launch_bounds__(256) gather_bwd_weights_kernel(const int32_t *__restrict__ idx,
-                                                                 const float *__restrict__ dy,
-                                                                 const TableT *__restrict__ tables,
-                                                                 float *__restrict__ dw, long long N, int I,
-                                                                 long long S, int d, int col0, int accumulate,
-                                                                 uint32_t *status) {
+#ifndef LFFN_BWW_THREADS
+#define LFFN_BWW_THREADS 128
+#endif
+#ifndef LFFN_BWW_MINBLOCKS
+#define LFFN_BWW_MINBLOCKS 3
+#endif
+#ifndef LFFN_BWW_U_NARROW
+#define LFFN_BWW_U_NARROW 4
+#endif
+#ifndef LFFN_BWW_U_WIDE
+#define LFFN_BWW_U_WIDE 2
+#endif
+
+template <typename TableT, int VPL, int U, bool FULLV>
+__global__ void __launch_bounds__(LFFN_BWW_THREADS, LFFN_BWW_MINBLOCKS)
+    gather_bwd_weights_kernel(const int32_t *__restrict__ idx, const float *__restrict__ dy,
+                              const TableT *__restrict__ tables, float *__restrict__ dw, long long N, int I,
+                              long long S, int d, int col0, int accumulate, uint32_t *status) {
     constexpr int EPV = Elem<TableT>::PER_VEC;
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
@@ -63,26 +74,28 @@ __global__ void __launch_bounds__(256) gather_bwd_weights_kernel(const int32_t *
             }
         }
         const int32_t *ip = idx + n * I;
+        int next_i = lane < I ? __ldg(ip + lane) : 0;
         for (int g0 = 0; g0 < I; g0 += 32) {
             const int cnt = min(32, I - g0);
-            const int my_i = lane < cnt ? __ldg(ip + g0 + lane) : 0;
+            const int my_i = next_i;
+            if (g0 + 32 + lane < I) next_i = __ldg(ip + g0 + 32 + lane);
+            // branch-free: rows past the list end or out of range read a substitute row; their sums are discarded
             float p[32];
 #pragma unroll
             for (int j0 = 0; j0 < 32; j0 += U) {
                 uint4 buf[U][VPL];
-                bool ok[U];
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     const int j = j0 + u;
-                    const int r = __shfl_sync(FULL, my_i, j);
-                    ok[u] = j < cnt && (unsigned long long)(long long)r < (unsigned long long)S;
-                    if (j < cnt && !ok[u]) bad = true;
-                    const uint4 *row = tv + (long long)(ok[u] ? r : 0) * row_vecs;
+                    int r = __shfl_sync(FULL, my_i, j);
+                    const bool in_range = (unsigned long long)(long long)r < (unsigned long long)S;
+                    bad |= (j < cnt) && !in_range;
+                    r = in_range ? r : 0;
+                    const uint4 *row = tv + (long long)r * row_vecs;
 #pragma unroll
                     for (int v = 0; v < VPL; v++) {
                         const int c = lane + 32 * v;
-                        buf[u][v] = make_uint4(0u, 0u, 0u, 0u);
-                        if (ok[u] && c < nvec) buf[u][v] = ld_row16(row + c);
+                        buf[u][v] = FULLV ? ld_row16(row + c) : ld_row16_pred(row + c, c < nvec);
                     }
                 }
 #pragma unroll
@@ -110,8 +123,10 @@ __global__ void __launch_bounds__(256) gather_bwd_weights_kernel(const int32_t *
                 }
             }
             if (lane < cnt) {
+                const bool in_range = (unsigned long long)(long long)my_i < (unsigned long long)S;
+                const float val = in_range ? p[0] : 0.f;
                 float *o = dw + n * I + g0 + lane;
-                *o = accumulate ? (*o + p[0]) : p[0];
+                *o = accumulate ? (*o + val) : val;
             }
         }
     }
@@ -121,9 +136,11 @@ __global__ void __launch_bounds__(256) gather_bwd_weights_kernel(const int32_t *
 template <typename TableT, int VPL>
 static int launch_bww_vpl(const int32_t *idx, const float *dy, const void *tables, float *dw, int64_t N, int I,
                           int64_t S, int d, int col0, cudaStream_t st) {
-    constexpr int U = (VPL <= 3) ? 4 : 2;
-    constexpr int THREADS = 256;
-    auto kern = gather_bwd_weights_kernel<TableT, VPL, U>;
+    constexpr int U = (VPL <= 3) ? LFFN_BWW_U_NARROW : LFFN_BWW_U_WIDE;
+    constexpr int THREADS = LFFN_BWW_THREADS;
+    const int nvec_here = min(d / Elem<TableT>::PER_VEC - col0, VPL * 32);
+    auto kern = nvec_here == VPL * 32 ? gather_bwd_weights_kernel<TableT, VPL, U, true>
+                                      : gather_bwd_weights_kernel<TableT, VPL, U, false>;
     int per_sm = 0;
     LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, 0));
     if (per_sm < 1) per_sm = 1;

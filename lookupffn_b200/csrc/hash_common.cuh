@@ -75,4 +75,52 @@ __device__ __forceinline__ void emit_table(Get get, int k, int bit_order, int we
     }
 }
 
+// The same arithmetic for a table whose K coordinates sit in registers (compile-time K, fully
+// unrolled so that the register array is indexed statically).  Operation order = emit_table.
+template <int K>
+__device__ __forceinline__ void emit_table_regs(const float (&z)[8], int sub, int bit_order, int weight_mode, float tau,
+                                                int32_t offset, int32_t *io, float *wo) {
+    int32_t code = 0;
+    float zz[K];
+#pragma unroll
+    for (int j = 0; j < K; j++) {
+        float t = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8 / K; s++)
+            if (s == sub) t = z[s * K + j];
+        zz[j] = t;
+        if (t > 0.f) code |= 1 << j;
+    }
+    if (weight_mode == LFFN_WEIGHT_SCORE) {
+        float num = 0.f, den = 1.f;
+#pragma unroll
+        for (int j = 0; j < K; j++) {
+            const float a = fabsf(zz[j]);
+            num = __fadd_rn(num, a);
+            den = __fmul_rn(den, __fadd_rn(1.f, expf(__fmul_rn(-2.f, a))));
+        }
+        if (bit_order == LFFN_BIT_MSB_FIRST) code = (int32_t)(__brev((unsigned)code) >> (32 - K));
+        io[0] = code + offset;
+        wo[0] = __fdiv_rn(num, den);
+    } else if (weight_mode == LFFN_WEIGHT_ONES) {
+        if (bit_order == LFFN_BIT_MSB_FIRST) code = (int32_t)(__brev((unsigned)code) >> (32 - K));
+        io[0] = code + offset;
+        wo[0] = 1.f;
+    } else {
+        float s[K];
+#pragma unroll
+        for (int j = 0; j < K; j++) s[j] = __fdiv_rn(1.f, __fadd_rn(1.f, expf(__fdiv_rn(-fabsf(zz[j]), tau))));
+#pragma unroll
+        for (int c = 0; c <= K; c++) {
+            float p = 1.f;
+#pragma unroll
+            for (int j = 0; j < K; j++) p = __fmul_rn(p, (c == j + 1) ? __fsub_rn(1.f, s[j]) : s[j]);
+            int32_t cc = c == 0 ? code : (code ^ (1 << (c - 1)));
+            if (bit_order == LFFN_BIT_MSB_FIRST) cc = (int32_t)(__brev((unsigned)cc) >> (32 - K));
+            io[c] = cc + offset;
+            wo[c] = p;
+        }
+    }
+}
+
 }  // namespace lffn

@@ -161,6 +161,173 @@ __global__ void __launch_bounds__(128) hash_diag_kernel(HashArgs a) {
     }
 }
 
+// ---- the diagonal-projection hash kernel, vector layout ----------------------------------------------
+// For D >= 256 and code lengths that divide 8.  Lane l holds NV = D/256 vectors of 8 consecutive
+// coordinates: vector i covers e = (i*32 + l)*8 .. +7, so x, the diagonals and the bias are read with
+// 16/32-byte loads and the k coordinates of a table (k | 8) sit in one lane: codes and weights are
+// computed in registers, without shared memory, and consecutive lanes write consecutive tables.
+// Butterfly order is unchanged (stride D/2 -> 1): vector index bits (register pairs), lane bits
+// (shuffles; a +-1 multiplier turns the add/subtract choice into one fma, rounding as a plain
+// add/subtract), then the three bits inside a vector (register pairs).
+template <int NV>
+__device__ __forceinline__ void fwht_vec8(float (&v)[NV][8], const float (&sgn)[5]) {
+#pragma unroll
+    for (int s = NV / 2; s >= 1; s >>= 1) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            if ((i & s) == 0) {
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const float a = v[i][q], b = v[i + s][q];
+                    v[i][q] = __fadd_rn(a, b);
+                    v[i + s][q] = __fsub_rn(a, b);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < 5; b++) {
+        const int s = 16 >> b;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const float p = __shfl_xor_sync(FULL, v[i][q], s);
+                v[i][q] = __fmaf_rn(v[i][q], sgn[b], p);  // lower lane: v + p, upper lane: p - v
+            }
+        }
+    }
+#pragma unroll
+    for (int s = 4; s >= 1; s >>= 1) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                if ((q & s) == 0) {
+                    const float a = v[i][q], b = v[i][q + s];
+                    v[i][q] = __fadd_rn(a, b);
+                    v[i][q + s] = __fsub_rn(a, b);
+                }
+            }
+        }
+    }
+}
+
+template <int NV, typename XT>
+__device__ __forceinline__ void load_row_vec8(float (&v)[NV][8], const XT *row, int d_in, int lane, bool vec_ok) {
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const int e0 = (i * 32 + lane) * 8;
+        if (vec_ok && e0 + 8 <= d_in) {
+            if constexpr (sizeof(XT) == 2) {
+                const uint4 u = __ldg(reinterpret_cast<const uint4 *>(row + e0));
+                Elem<__nv_bfloat16>::unpack(u, v[i]);
+            } else {
+                const float4 a = __ldg(reinterpret_cast<const float4 *>(row + e0));
+                const float4 b = __ldg(reinterpret_cast<const float4 *>(row + e0 + 4));
+                v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+                v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) v[i][q] = (e0 + q < d_in) ? Elem<XT>::load1(row + e0 + q) : 0.f;
+        }
+    }
+}
+
+template <int NV, int K, typename XT>
+__global__ void __launch_bounds__(128, (NV >= 8 ? 2 : 4)) hash_diag_vec8_kernel(HashArgs a, int x_vec_ok, int bias_vec_ok) {
+    constexpr int D = NV * 256;
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+    constexpr int m_max = K + 1;
+    const int m = a.weight_mode == LFFN_WEIGHT_SOFT_FLIP ? m_max : 1;
+    const long long g_lo = (long long)a.t_begin * K, g_hi = (long long)(a.t_begin + a.t_count) * K;
+    const long long out_pitch = (long long)a.t_count * m;
+    float sgn[5];
+#pragma unroll
+    for (int b = 0; b < 5; b++) sgn[b] = (lane & (16 >> b)) ? -1.f : 1.f;
+
+    for (long long n = warp0; n < a.N; n += nwarps) {
+        const XT *xrow = static_cast<const XT *>(a.x) + n * a.d_in;
+        for (int r = a.r_lo; r <= a.r_hi; r++) {
+            float v[NV][8];
+            load_row_vec8<NV, XT>(v, xrow, a.d_in, lane, x_vec_ok != 0);
+            for (int s = 0; s < a.S; s++) {
+                const float *ws = a.w + ((long long)r * a.S + s) * D;
+#pragma unroll
+                for (int i = 0; i < NV; i++) {
+                    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(ws + (i * 32 + lane) * 8));
+                    const float4 w1 = __ldg(reinterpret_cast<const float4 *>(ws + (i * 32 + lane) * 8 + 4));
+                    v[i][0] = __fmul_rn(v[i][0], w0.x); v[i][1] = __fmul_rn(v[i][1], w0.y);
+                    v[i][2] = __fmul_rn(v[i][2], w0.z); v[i][3] = __fmul_rn(v[i][3], w0.w);
+                    v[i][4] = __fmul_rn(v[i][4], w1.x); v[i][5] = __fmul_rn(v[i][5], w1.y);
+                    v[i][6] = __fmul_rn(v[i][6], w1.z); v[i][7] = __fmul_rn(v[i][7], w1.w);
+                }
+                fwht_vec8<NV>(v, sgn);
+                if (a.had_scale != 1.f) {
+#pragma unroll
+                    for (int i = 0; i < NV; i++)
+#pragma unroll
+                        for (int q = 0; q < 8; q++) v[i][q] = __fmul_rn(v[i][q], a.had_scale);
+                }
+            }
+            // z = fl(fl(mix_a * y) + fl(mix_b * u)) + bias; with mix_b == 0 the second term is +0
+            if (a.mix_b != 0.f) {
+                float u[NV][8];
+                load_row_vec8<NV, XT>(u, xrow, a.d_in, lane, x_vec_ok != 0);
+#pragma unroll
+                for (int i = 0; i < NV; i++)
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        v[i][q] = __fadd_rn(__fmul_rn(a.mix_a, v[i][q]), __fmul_rn(a.mix_b, u[i][q]));
+            } else if (a.mix_a != 1.f) {
+#pragma unroll
+                for (int i = 0; i < NV; i++)
+#pragma unroll
+                    for (int q = 0; q < 8; q++) v[i][q] = __fmul_rn(a.mix_a, v[i][q]);
+            }
+#pragma unroll
+            for (int i = 0; i < NV; i++) {
+                const long long g0 = (long long)r * D + (i * 32 + lane) * 8;
+                if (a.bias != nullptr && g0 < (long long)a.T * K) {
+                    if (bias_vec_ok && g0 + 8 <= (long long)a.T * K) {
+                        const float4 b0 = __ldg(reinterpret_cast<const float4 *>(a.bias + g0));
+                        const float4 b1 = __ldg(reinterpret_cast<const float4 *>(a.bias + g0 + 4));
+                        v[i][0] = __fadd_rn(v[i][0], b0.x); v[i][1] = __fadd_rn(v[i][1], b0.y);
+                        v[i][2] = __fadd_rn(v[i][2], b0.z); v[i][3] = __fadd_rn(v[i][3], b0.w);
+                        v[i][4] = __fadd_rn(v[i][4], b1.x); v[i][5] = __fadd_rn(v[i][5], b1.y);
+                        v[i][6] = __fadd_rn(v[i][6], b1.z); v[i][7] = __fadd_rn(v[i][7], b1.w);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 8; q++)
+                            if (g0 + q < (long long)a.T * K) v[i][q] = __fadd_rn(v[i][q], __ldg(a.bias + g0 + q));
+                    }
+                }
+                if (a.z_out != nullptr) {
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {
+                        const long long g = g0 + q;
+                        if (g >= g_lo && g < g_hi) a.z_out[n * (g_hi - g_lo) + (g - g_lo)] = v[i][q];
+                    }
+                }
+                if (a.idx_out != nullptr) {
+#pragma unroll
+                    for (int sub = 0; sub < 8 / K; sub++) {
+                        const long long t = g0 / K + sub;
+                        if (t >= a.t_begin && t < a.t_begin + a.t_count) {
+                            const long long o = n * out_pitch + (t - a.t_begin) * m;
+                            emit_table_regs<K>(v[i], sub, a.bit_order, a.weight_mode, a.tau,
+                                               (int32_t)((t - a.t_begin) << K), a.idx_out + o, a.w_out + o);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
 // ---- codes and weights from z in global memory (one thread per (token, table)) ------------------
 __global__ void __launch_bounds__(256) code_weights_kernel(const float *__restrict__ z, long long NT, int T, int k,
                                                            int bit_order, int weight_mode, float tau, int add_offsets,
@@ -229,8 +396,46 @@ static int launch_hash_diag_v(const HashArgs &a, cudaStream_t st) {
     return LFFN_OK;
 }
 
+template <int NV, int K, typename XT>
+static int launch_hash_vec8_nk(const HashArgs &a, cudaStream_t st) {
+    constexpr int WARPS = 4;
+    auto kern = hash_diag_vec8_kernel<NV, K, XT>;
+    int per_sm = 0;
+    LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, WARPS * 32, 0));
+    if (per_sm < 1) per_sm = 1;
+    long long grid = (long long)num_sms() * per_sm;
+    const long long want = (a.N + WARPS - 1) / WARPS;
+    if (grid > want) grid = want;
+    if (grid < 1) grid = 1;
+    const size_t esz = sizeof(XT);
+    const int x_vec_ok = ((a.d_in * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15u) == 0);
+    const int bias_vec_ok = a.bias != nullptr && (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0;
+    kern<<<(unsigned)grid, WARPS * 32, 0, st>>>(a, x_vec_ok, bias_vec_ok);
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return LFFN_OK;
+}
+
+template <int NV, typename XT>
+static int launch_hash_vec8_n(const HashArgs &a, cudaStream_t st) {
+    switch (a.k) {
+        case 1: return launch_hash_vec8_nk<NV, 1, XT>(a, st);
+        case 2: return launch_hash_vec8_nk<NV, 2, XT>(a, st);
+        case 4: return launch_hash_vec8_nk<NV, 4, XT>(a, st);
+        default: return launch_hash_vec8_nk<NV, 8, XT>(a, st);
+    }
+}
+
 template <typename XT>
 static int launch_hash_diag_t(const HashArgs &a, cudaStream_t st) {
+    const bool w_aligned = (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0;
+    if (w_aligned && (a.k == 1 || a.k == 2 || a.k == 4 || a.k == 8)) {  // vector layout
+        switch (a.D) {
+            case 256: return launch_hash_vec8_n<1, XT>(a, st);
+            case 512: return launch_hash_vec8_n<2, XT>(a, st);
+            case 1024: return launch_hash_vec8_n<4, XT>(a, st);
+            case 2048: return launch_hash_vec8_n<8, XT>(a, st);
+        }
+    }
     switch (a.D) {
         case 64: return launch_hash_diag_v<2, XT>(a, st);
         case 128: return launch_hash_diag_v<4, XT>(a, st);
