@@ -268,6 +268,95 @@ def run_ours(args, rank, world, local):
     return out
 
 
+def run_table_sharded(args, rank, world, local):
+    """Config-5 style: every rank sees all N tokens, owns T_per_gpu tables (the whole layer has
+    T_per_gpu * world), partial sums are reduce-scattered over NVLink chunk by chunk."""
+    from lookupffn_b200 import _lib as L
+    from lookupffn_b200 import ops, sharded
+
+    w = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        w["N"] = args.tokens
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    N, k, d_in, d_out = w["N"], w["k"], w["d_in"], w["d_out"]
+    t_count = w["T"]
+    T = t_count * world
+    t_begin = rank * t_count
+    dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
+    D = padded_dim(d_in)
+    R = max(1, -(-T * k // D))
+    g = torch.Generator(device=device).manual_seed(1234)
+    signs = (2 * torch.randint(0, 2, (R, 2, D, 1, 1), generator=g, device=device) - 1).float()
+    x = torch.randn(N, d_in, generator=g, device=device).to(dt)          # identical on every rank
+    gt = torch.Generator(device=device).manual_seed(77 + rank)
+    tables = (0.02 * torch.randn(t_count << k, d_out, generator=gt, device=device)).to(dt)
+    bias = torch.zeros(d_out, device=device)
+    desc = ops.make_hash_desc(d_in, signs, None, T, k, had_scale=float(1.0 / np.sqrt(D)), mix_a=1.0, mix_b=0.0)
+    chunk = args.rs_chunk
+
+    def step():
+        return sharded.lookup_forward_table_sharded(x, desc, tables, t_begin, t_count, bias=bias,
+                                                    chunk_tokens=chunk, out_dtype=torch.float32)[0]
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(local))
+    torch.distributed.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        y = step()
+    e1.record()
+    torch.cuda.synchronize()
+    torch.distributed.barrier()
+    clocks = sampler.result()
+    elapsed_ms = e0.elapsed_time(e1)
+
+    # end to end: x from pinned host memory every step, the rank's rows of y back to pinned host memory
+    x_host = torch.empty(x.shape, dtype=dt).pin_memory()
+    x_host.copy_(x)
+    y_host = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        y_host.copy_(step(), non_blocking=True)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    torch.distributed.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([elapsed_ms, e2e_s], dtype=torch.float64, device=device)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    elapsed_ms, e2e_s = (float(v) for v in t.tolist())
+    if rank != 0:
+        return None
+    eb = 2 if w["dtype"] == "bf16" else 4
+    chunks = len(sharded.chunk_plan(N, world, chunk))
+    return {
+        "metric": "lookupffn_layer_forward_throughput", "value": N * args.steps / (elapsed_ms * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": f"{args.workload}, tables sharded: N={N} tokens on every GPU, d={d_in}, T={t_count} "
+                               f"tables per GPU ({T} in the layer), k={k}, {w['dtype']} x/tables, fp32 partial sums, "
+                               f"NCCL reduce-scatter in {chunks} chunks",
+                   "sharding": f"tables x{world}", "l2": "inputs larger than L2"},
+        "table_rows_per_s": world * N * t_count * args.steps / (elapsed_ms * 1e-3),
+        "rs_bytes_per_step_per_gpu": N * d_out * 4,
+        "e2e": {"value": N * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": N * d_in * eb,
+                "d2h_bytes_per_step": (N // world) * d_out * 4, "api": "sharded.lookup_forward_table_sharded"},
+        "gpu_launches": 2 * chunks * args.steps, "clocks": clocks,
+    }
+
+
 # ---- the reference's CPU path, on this box's host cores ---------------------------------------------------
 def load_ref_modules():
     """The reference's own CPU extensions compiled (unmodified) into oracle/_ref, or None."""
@@ -371,6 +460,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-chunk", type=int, default=8192)
     ap.add_argument("--cpu-tokens", type=int, default=4096)
+    ap.add_argument("--shard", default="tokens", choices=["tokens", "tables"],
+                    help="tokens: each rank its own tokens, tables replicated (default); tables: tables split by T, "
+                         "partial sums reduce-scattered")
+    ap.add_argument("--rs-chunk", type=int, default=32768, help="tokens per reduce-scatter chunk (--shard tables)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on a small case)")
     ap.add_argument("--no-e2e", action="store_true", help="device path only, short report (for ncu captures)")
@@ -387,10 +480,18 @@ def main():
             print(json.dumps(out), flush=True)
         return 0
 
-    if world > 1:
+    if world > 1 or args.shard == "tables":
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29512")
         torch.cuda.set_device(local)
-        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+        torch.distributed.init_process_group("nccl", rank=rank, world_size=world,
+                                             device_id=torch.device("cuda", local))
+    if args.shard == "tables":
+        out = run_table_sharded(args, rank, world, local)
+        if out is not None:
+            print(json.dumps(out), flush=True)
+        torch.distributed.destroy_process_group()
+        return 0
     out = run_ours(args, rank, world, local)
     if out is not None:
         if world == 1 and not args.no_cpu_baseline:

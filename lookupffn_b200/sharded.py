@@ -1,0 +1,135 @@
+"""Multi-GPU forms of the LookupFFN forward, one process per GPU over torch.distributed.
+
+Token sharding (the default; tables replicated): tokens are independent, rank g runs the ordinary
+module on its own rows and no collective is needed in the forward.  `token_range` gives the split.
+
+Table sharding (table sets too large to replicate): rank g owns tables [t_begin, t_begin + t_count),
+sees all N tokens, computes the partial sum over its tables in fp32 and the partials are combined
+by a reduce-scatter(sum) over tokens, chunk by chunk so that the collective of chunk c overlaps the
+kernels of chunk c+1 (NCCL runs on its own stream).  After the call rank g holds N/world rows; the
+rows it owns are returned with it.  The reference has no counterpart (it is data-parallel only,
+main.py:40-47); the partition follows BASELINE.json config 5.
+"""
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import ops
+
+
+def token_range(N, rank, world):
+    """Contiguous split of N tokens; the first N % world ranks take one more."""
+    base, rem = divmod(N, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def table_range(T, rank, world):
+    """(t_begin, t_count) of rank's contiguous share of T tables; the first T % world ranks take one more."""
+    lo, hi = token_range(T, rank, world)
+    return lo, hi - lo
+
+
+def rotations_needed(t_begin, t_count, k, D):
+    """Inclusive range of projection rotations whose coordinates tables [t_begin, t_begin+t_count) read
+    (tables may straddle a rotation boundary when k does not divide D)."""
+    return (t_begin * k) // D, ((t_begin + t_count) * k - 1) // D
+
+
+def chunk_plan(N, world, chunk_tokens):
+    """[(start, size)] covering N tokens; every size is a multiple of world."""
+    if N % world != 0:
+        raise ValueError(f"table sharding needs N ({N}) divisible by the world size ({world})")
+    step = max(world, (chunk_tokens // world) * world)
+    return [(s, min(step, N - s)) for s in range(0, N, step)]
+
+
+def owned_tokens(N, rank, world, chunk_tokens):
+    """Token indices (ascending within each chunk) that end up on `rank` after the chunked reduce-scatter."""
+    out = []
+    for s, n in chunk_plan(N, world, chunk_tokens):
+        per = n // world
+        out.append(torch.arange(s + rank * per, s + (rank + 1) * per))
+    return torch.cat(out) if out else torch.empty(0, dtype=torch.long)
+
+
+def reduce_scatter_partials(partial_fn, N, d_out, device, group=None, chunk_tokens=32768, bias=None,
+                            out_dtype=torch.float32):
+    """Runs partial_fn(start, size) -> fp32 [size, d_out] (this rank's partial sum for tokens
+    [start, start+size)) over all chunks and reduce-scatters each chunk.  Returns [N/world, d_out]."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    plan = chunk_plan(N, world, chunk_tokens)
+    out = torch.empty((N // world, d_out), dtype=torch.float32, device=device)
+    works, keep, pos = [], [], 0
+    for s, n in plan:
+        part = partial_fn(s, n)
+        if part.dtype != torch.float32 or part.shape != (n, d_out):
+            raise ValueError("partial_fn must return fp32 [size, d_out]")
+        dst = out[pos:pos + n // world]
+        works.append(dist.reduce_scatter_tensor(dst, part.contiguous(), op=dist.ReduceOp.SUM, group=group,
+                                                async_op=True))
+        keep.append(part)  # the collective reads it asynchronously
+        pos += n // world
+    for w in works:
+        w.wait()
+    del keep, rank
+    if bias is not None:
+        out += bias.to(out.dtype)
+    return out if out_dtype == torch.float32 else out.to(out_dtype)
+
+
+def lookup_forward_table_sharded(x, desc, tables_local, t_begin, t_count, bias=None, group=None,
+                                 chunk_tokens=32768, out_dtype=torch.float32):
+    """x [N, d_in] (the same on every rank); desc describes the WHOLE layer's projection;
+    tables_local [t_count * 2^k, d_out] are this rank's tables.  Returns (y_local [N/world, d_out],
+    owned token indices)."""
+    N = x.shape[0]
+    d_out = tables_local.shape[1]
+
+    def partial(start, size):
+        idx, w, _ = ops.hash_fwd(x[start:start + size], desc, t_begin=t_begin, t_count=t_count)
+        return ops.weighted_vector_gather_add(idx, tables_local, w, out_dtype=torch.float32)
+
+    y = reduce_scatter_partials(partial, N, d_out, x.device, group=group, chunk_tokens=chunk_tokens, bias=bias,
+                                out_dtype=out_dtype)
+    world = dist.get_world_size(group)
+    return y, owned_tokens(N, dist.get_rank(group), world, chunk_tokens)
+
+
+class TableShardedLookupFFN(nn.Module):
+    """A LookupFFN whose tables are split by T across the ranks of `group`.  Built from a full module
+    (every rank constructs or loads the same one) and keeps only its own slice of `tables`;
+    LayerNorm, projection and bias stay replicated."""
+
+    def __init__(self, full, group=None, chunk_tokens=32768):
+        super().__init__()
+        self.group = group
+        self.chunk_tokens = chunk_tokens
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.t_begin, self.t_count = table_range(full.num_table, rank, world)
+        self.LayerNorm = full.LayerNorm
+        self.hash = full.hash
+        self.bias = full.bias
+        self.table_size = full.table_size
+        self.output_size = full.output_size
+        self.tables = nn.Parameter(full.tables.detach()[self.t_begin:self.t_begin + self.t_count].clone(),
+                                   requires_grad=False)
+
+    @torch.no_grad()
+    def forward(self, hidden_states):
+        """hidden_states [N, hidden], identical on all ranks -> (y_local [N/world, out], owned token indices)."""
+        if not hidden_states.is_cuda:
+            raise RuntimeError("lookupffn_b200 runs on CUDA tensors only (no CPU fallback)")
+        u = self.LayerNorm(hidden_states)
+        N = u.shape[0]
+        flat = self.tables.reshape(self.t_count * self.table_size, self.output_size)
+
+        def partial(start, size):
+            idx, w = self.hash(u[start:start + size], t_begin=self.t_begin, t_count=self.t_count)
+            return ops.weighted_vector_gather_add(idx, flat, w, out_dtype=torch.float32)
+
+        y = reduce_scatter_partials(partial, N, self.output_size, u.device, group=self.group,
+                                    chunk_tokens=self.chunk_tokens, bias=self.bias)
+        world = dist.get_world_size(self.group)
+        return y, owned_tokens(N, dist.get_rank(self.group), world, self.chunk_tokens)
