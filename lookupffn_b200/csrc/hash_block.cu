@@ -195,6 +195,166 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, i
     }
 }
 
+// ---- fast path: 64 x 64 blocks, weights stored [block][i][o] ------------------------------------------
+// Same tile layout and arithmetic as hash_block_kernel; what changes is how the weights travel and how the
+// multiply-adds are issued.  Weights stream through two 32 KB shared buffers in chunks of (4 blocks) x (32
+// input rows) x (64 outputs), fetched with 16-byte cp.async one chunk ahead of the arithmetic -- across
+// passes, stages and rotations, so the Hadamard passes hide the next stage's first chunk -- and land
+// already in the swizzled [i][o] layout.  The 8 x 4 register tile is held as 16 packed pairs and updated
+// with fma.rn.f32x2 (two IEEE fp32 fused multiply-adds per instruction): 16 packed FMAs + 4 register moves
+// per input coordinate instead of 32 scalar FMAs.  Each output is still one fmaf chain over i ascending.
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ unsigned long long dup2(float w) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(w));
+    return r;
+}
+__device__ __forceinline__ void ffma2(unsigned long long &acc, unsigned long long a, unsigned long long b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+
+constexpr int HF_CHUNK_FLOATS = 4 * 32 * 64;  // 4 blocks x 32 rows x 64 outputs
+
+template <typename XT>
+__global__ void __launch_bounds__(HB_THREADS, 1) hash_block64_kernel(HashArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    const int D = a.D;
+    float *Y = smem;                              // [D][HB_MP]
+    float *Wb = Y + (size_t)D * HB_MP;            // 2 x HF_CHUNK_FLOATS
+    float *carry = Wb + 2 * HF_CHUNK_FLOATS;      // [HB_CARRY][HB_MP]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int k = a.k;
+    const int m = a.weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
+    const long long g_lo = (long long)a.t_begin * k, g_hi = (long long)(a.t_begin + a.t_count) * k;
+    const long long out_pitch = (long long)a.t_count * m;
+    const int NB = D / 64;
+    const int cps = D / 128;                          // chunks per stage: D/256 passes x 2 halves
+    const int nrot = a.r_hi - a.r_lo + 1;
+    const long long chunks_per_tile = (long long)nrot * a.S * cps;
+    const long long ntiles = (a.N + HB_M - 1) / HB_M;
+    long long my_tiles = 0;
+    for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) my_tiles++;
+    const long long total_chunks = my_tiles * chunks_per_tile;
+
+    // global chunk counter -> source of that chunk (the weights do not depend on the tile)
+    auto issue_chunk = [&](long long gc) {
+        if (gc >= total_chunks) return;
+        const long long in_tile = gc % chunks_per_tile;
+        const int r = a.r_lo + (int)(in_tile / (a.S * cps));
+        const int rem = (int)(in_tile % (a.S * cps));
+        const int s = rem / cps, c = rem % cps;
+        const int p = c >> 1, h = c & 1;
+        const float *src = a.w + (((long long)r * a.S + s) * NB + 4 * p) * 4096 + h * 32 * 64;
+        float *dst = Wb + (gc & 1) * HF_CHUNK_FLOATS;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int q = tid + HB_THREADS * j;          // 16-byte piece 0..2047
+            const int g = q >> 9, rm = q & 511, il = rm >> 4, o4 = rm & 15;
+            cp_async16(dst + g * 2048 + il * 64 + ((o4 ^ (il & 15)) << 2), src + (long long)g * 4096 + il * 64 + o4 * 4);
+        }
+        cp_async_commit();
+    };
+
+    long long gc = 0;
+    issue_chunk(0);
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const long long n0 = tile * HB_M;
+        const int mt = (int)min((long long)HB_M, a.N - n0);
+        for (int r = a.r_lo; r <= a.r_hi; r++) {
+            __syncthreads();
+            for (int i = tid; i < HB_CARRY * HB_M; i += HB_THREADS) {
+                const int e = i / HB_M, mm = i % HB_M;
+                carry[e * HB_MP + mm] = Y[(D - HB_CARRY + e) * HB_MP + mm];
+            }
+            __syncthreads();
+            for (int mm = warp; mm < HB_M; mm += HB_THREADS / 32) {
+                const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
+                for (int e = lane; e < D; e += 32)
+                    Y[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+            }
+            for (int s = 0; s < a.S; s++) {
+                const int cq = tid & 63, tq = tid >> 6;          // 64 column quads x 4 token octets
+                const int g = cq >> 4, o4 = cq & 15;
+                for (int p = 0; p < D / 256; p++) {
+                    const int col0 = p * 256;
+                    unsigned long long acc[4][4];               // [token pair][column]
+#pragma unroll
+                    for (int pp = 0; pp < 4; pp++)
+#pragma unroll
+                        for (int q = 0; q < 4; q++) acc[pp][q] = 0ull;
+                    for (int h = 0; h < 2; h++) {
+                        cp_async_wait_all();
+                        __syncthreads();           // chunk gc landed for everyone; buffer (gc+1)&1 is free; Y is loaded
+                        issue_chunk(gc + 1);
+                        const float *wb = Wb + (gc & 1) * HF_CHUNK_FLOATS + g * 2048;
+                        const float *yb = Y + (size_t)(col0 + g * 64 + h * 32) * HB_MP + tq * 8;
+#pragma unroll 8
+                        for (int il = 0; il < 32; il++) {
+                            const ulonglong2 x0 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP);
+                            const ulonglong2 x1 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP + 4);
+                            const float4 w4 = *reinterpret_cast<const float4 *>(wb + il * 64 + ((o4 ^ (il & 15)) << 2));
+                            const unsigned long long wq[4] = {dup2(w4.x), dup2(w4.y), dup2(w4.z), dup2(w4.w)};
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                ffma2(acc[0][q], x0.x, wq[q]);
+                                ffma2(acc[1][q], x0.y, wq[q]);
+                                ffma2(acc[2][q], x1.x, wq[q]);
+                                ffma2(acc[3][q], x1.y, wq[q]);
+                            }
+                        }
+                        gc++;
+                    }
+                    __syncthreads();  // every thread finished reading this pass's 256 input columns
+                    float *yo = Y + (size_t)(col0 + cq * 4) * HB_MP + tq * 8;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        *reinterpret_cast<ulonglong2 *>(yo + q * HB_MP) = make_ulonglong2(acc[0][q], acc[1][q]);
+                        *reinterpret_cast<ulonglong2 *>(yo + q * HB_MP + 4) = make_ulonglong2(acc[2][q], acc[3][q]);
+                    }
+                }
+                __syncthreads();
+                fwht_tile(Y, D, a.had_scale, warp, lane);
+            }
+            const long long c_lo = (long long)r * D, c_hi = c_lo + D;
+            for (int mm = warp; mm < HB_M; mm += HB_THREADS / 32) {
+                const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
+                for (int e = lane; e < D; e += 32) {
+                    const float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+                    const long long g2 = c_lo + e;
+                    float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + mm]), __fmul_rn(a.mix_b, u));
+                    if (a.bias != nullptr && g2 < (long long)a.T * k) z = __fadd_rn(z, __ldg(a.bias + g2));
+                    Y[e * HB_MP + mm] = z;
+                    if (a.z_out != nullptr && mm < mt && g2 >= g_lo && g2 < g_hi)
+                        a.z_out[(n0 + mm) * (g_hi - g_lo) + (g2 - g_lo)] = z;
+                }
+            }
+            __syncthreads();
+            long long t_first = c_lo / k;
+            if (t_first < a.t_begin) t_first = a.t_begin;
+            long long t_end = c_hi / k;
+            if (t_end > a.t_begin + a.t_count) t_end = a.t_begin + a.t_count;
+            if (lane < mt && a.idx_out != nullptr) {
+                for (long long t = t_first + warp; t < t_end; t += HB_THREADS / 32) {
+                    const int local0 = (int)(t * k - c_lo);
+                    auto get = [&](int j) -> float {
+                        const int e = local0 + j;
+                        return e >= 0 ? Y[e * HB_MP + lane] : carry[(HB_CARRY + e) * HB_MP + lane];
+                    };
+                    const long long o = (n0 + lane) * out_pitch + (t - a.t_begin) * m;
+                    emit_table(get, k, a.bit_order, a.weight_mode, a.tau, (int32_t)((t - a.t_begin) << k), false, 0,
+                               a.idx_out + o, a.w_out + o);
+                }
+            }
+        }
+    }
+    cp_async_wait_all();
+}
+
 int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, cudaStream_t st) {
     if (BS < 4 || BS > 128 || (BS & (BS - 1)) != 0 || a.D % BS != 0) {
         set_error("hash_fwd: block size %d unsupported (1, or a power of two in [4, 128] dividing D)", BS);
@@ -209,6 +369,23 @@ int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, c
     long long grid = num_sms();
     if (grid > ntiles) grid = ntiles;
     if (grid < 1) grid = 1;
+    if (BS == 64 && transpose_w && a.D % 256 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0) {
+        static_assert(2 * HF_CHUNK_FLOATS == HB_WFLOATS, "same shared-memory footprint as the generic kernel");
+        if (x_dtype == LFFN_F32) {
+            auto kern = hash_block64_kernel<float>;
+            LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            kern<<<(unsigned)grid, HB_THREADS, smem, st>>>(a);
+        } else if (x_dtype == LFFN_BF16) {
+            auto kern = hash_block64_kernel<__nv_bfloat16>;
+            LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            kern<<<(unsigned)grid, HB_THREADS, smem, st>>>(a);
+        } else {
+            set_error("hash_fwd: unknown x dtype %d", x_dtype);
+            return LFFN_ERR_INVALID_ARG;
+        }
+        LFFN_CHECK_CUDA(cudaGetLastError());
+        return LFFN_OK;
+    }
     if (x_dtype == LFFN_F32) {
         auto kern = hash_block_kernel<float>;
         LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -56,12 +56,26 @@ class BH4(nn.Module):
     def mix(self):
         return self.decay_coeff, 1 - self.decay_coeff
 
+    def kernel_weight(self):
+        """(weight tensor, transpose_w flag) to hand to the hash kernel.  The 64 x 64 fast path streams the
+        blocks in [i][o] order, so for that shape a transposed copy of the parameter is kept and refreshed
+        whenever the parameter changes (optimizer step, load_state_dict, .to())."""
+        w = self.weight.detach()
+        if self.block_size != 64 or self.padded_in_dim % 256 != 0:
+            return w.contiguous(), False
+        key = (w.data_ptr(), w._version, w.device)
+        if getattr(self, "_wt_key", None) != key:
+            self._wt = w.transpose(-1, -2).contiguous()
+            self._wt_key = key
+        return self._wt, True
+
     def forward(self, xs):
         """The projection alone, z [..., out_dim] (reference BH4.forward)."""
         shape = xs.shape[:-1]
         x = xs.reshape(-1, xs.shape[-1])
-        desc = ops.make_hash_desc(self.in_dim, self.weight.detach().contiguous(), self.bias.detach().contiguous(),
-                                  self.out_dim, 1, had_scale=self.had_scale, mix_a=self.mix[0], mix_b=self.mix[1],
+        wk, tw = self.kernel_weight()
+        desc = ops.make_hash_desc(self.in_dim, wk, self.bias.detach().contiguous(), self.out_dim, 1, transpose_w=tw,
+                                  had_scale=self.had_scale, mix_a=self.mix[0], mix_b=self.mix[1],
                                   weight_mode=WEIGHT_ONES)
         _, _, z = ops.hash_fwd(x, desc, want_z=True, want_codes=False)
         return z.reshape(*shape, self.out_dim)
@@ -116,8 +130,9 @@ class Hashing(nn.Module):
             return ops.compute_code_score(z, bit_order=self.bit_order, weight_mode=self.weight_mode, tau=self.tau,
                                           add_offsets=True)
         p = self.projection
-        desc = ops.make_hash_desc(self.hidden_size, p.weight.detach().contiguous(), p.bias.detach().contiguous(),
-                                  self.num_table, self.code_length, had_scale=p.had_scale, mix_a=p.mix[0],
+        wk, tw = p.kernel_weight()
+        desc = ops.make_hash_desc(self.hidden_size, wk, p.bias.detach().contiguous(), self.num_table,
+                                  self.code_length, transpose_w=tw, had_scale=p.had_scale, mix_a=p.mix[0],
                                   mix_b=p.mix[1], bit_order=self.bit_order, weight_mode=self.weight_mode, tau=self.tau)
         idx, w, _ = ops.hash_fwd(x, desc, t_begin=t_begin, t_count=t_count)
         return idx, w
