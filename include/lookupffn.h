@@ -125,6 +125,13 @@ int lffn_code_weights(const float *z, int64_t N, int32_t T, int32_t k, int32_t b
                       float tau, int32_t add_offsets, int32_t *idx_out, float *w_out, lffn_stream_t stream);
 
 /*
+ * Gradient of those weights with respect to z: dz [N, T, k] from dw [N, T*m].  Replaces what autograd derives
+ * from compute_code_score_torch (compute_code_score/kernel.py:43-55); the codes carry no gradient.
+ */
+int lffn_code_weights_bwd(const float *z, const float *dw, int64_t N, int32_t T, int32_t k, int32_t weight_mode,
+                          float tau, float *dz, lffn_stream_t stream);
+
+/*
  * out[n, :] = sum_i w[n, i] * tables[idx[n, i], :] (+ bias): replaces
  * gather_add.weighted_vector_gather_add_fp32/_fp16 (gather/cuda/extension/torch_extension.cpp:6-33,
  * gather/cuda/kernel.py:22-70) and gather_add_cpu.weighted_vector_gather_add_* (gather/cpu/

@@ -46,6 +46,8 @@ _SIGNATURES = {
                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lffn_code_weights": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                     C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lffn_code_weights_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float,
+                                        C.c_void_p, C.c_void_p]),
     "lffn_gather_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64,
                                   C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "lffn_gather_bwd_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64,

@@ -145,6 +145,18 @@ int lffn_code_weights(const float *z, int64_t N, int32_t T, int32_t k, int32_t b
                                static_cast<cudaStream_t>(stream));
 }
 
+int lffn_code_weights_bwd(const float *z, const float *dw, int64_t N, int32_t T, int32_t k, int32_t weight_mode,
+                          float tau, float *dz, lffn_stream_t stream) {
+    LFFN_REQUIRE(z != nullptr && dw != nullptr && dz != nullptr, LFFN_ERR_INVALID_ARG, "code_weights_bwd: NULL buffer");
+    LFFN_REQUIRE(N >= 0 && T >= 1, LFFN_ERR_INVALID_ARG, "code_weights_bwd: bad sizes");
+    LFFN_REQUIRE(k >= 1 && k <= 16, LFFN_ERR_UNSUPPORTED, "code_weights_bwd: k = %d outside [1, 16]", k);
+    LFFN_REQUIRE(weight_mode >= LFFN_WEIGHT_SCORE && weight_mode <= LFFN_WEIGHT_SOFT_FLIP, LFFN_ERR_INVALID_ARG,
+                 "code_weights_bwd: weight_mode %d", weight_mode);
+    LFFN_REQUIRE(weight_mode != LFFN_WEIGHT_SOFT_FLIP || tau > 0.f, LFFN_ERR_INVALID_ARG, "code_weights_bwd: tau <= 0");
+    if (N == 0) return LFFN_OK;
+    return launch_code_weights_bwd(z, dw, N, T, k, weight_mode, tau, dz, static_cast<cudaStream_t>(stream));
+}
+
 int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype, void *out,
                     int32_t out_dtype, int64_t N, int32_t I, int64_t S, int32_t d, const float *bias,
                     lffn_stream_t stream) {

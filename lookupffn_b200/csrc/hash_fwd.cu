@@ -342,6 +342,70 @@ __global__ void __launch_bounds__(256) code_weights_kernel(const float *__restri
     }
 }
 
+// ---- gradient of the weights with respect to z (one thread per (token, table)) --------------------------
+// score = num / den, num = sum_j a_j, den = prod_j (1 + e^{-2 a_j}), a = |z|:
+//   d score / d z_j = sign(z_j) * (1 / den + score * 2 e^{-2 a_j} / (1 + e^{-2 a_j}))
+// soft flip, w_c = prod_j f_cj with f = s_j or 1 - s_j, s = sigmoid(a / tau):
+//   d w_c / d z_j = sign(z_j) / tau * w_c * (c == j+1 ? -s_j : 1 - s_j)
+// sign(0) = 0, as torch.abs differentiates (compute_code_score/kernel.py:51-53 under autograd).
+__global__ void __launch_bounds__(256) code_weights_bwd_kernel(const float *__restrict__ z, const float *__restrict__ dw,
+                                                               long long NT, int k, int weight_mode, float tau,
+                                                               float *__restrict__ dz) {
+    const int m = weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < NT; i += (long long)gridDim.x * blockDim.x) {
+        const float *zp = z + i * k;
+        float *dp = dz + i * k;
+        if (weight_mode == LFFN_WEIGHT_ONES) {
+            for (int j = 0; j < k; j++) dp[j] = 0.f;
+        } else if (weight_mode == LFFN_WEIGHT_SCORE) {
+            float num = 0.f, den = 1.f;
+            for (int j = 0; j < k; j++) {
+                const float a = fabsf(__ldg(zp + j));
+                num += a;
+                den *= 1.f + expf(-2.f * a);
+            }
+            const float score = num / den, g = __ldg(dw + i), inv_den = 1.f / den;
+            for (int j = 0; j < k; j++) {
+                const float zj = __ldg(zp + j), e = expf(-2.f * fabsf(zj));
+                const float sg = zj > 0.f ? 1.f : (zj < 0.f ? -1.f : 0.f);
+                dp[j] = g * sg * (inv_den + score * 2.f * e / (1.f + e));
+            }
+        } else {
+            float s[16], acc[16];
+            float hard = 1.f;
+            for (int j = 0; j < k; j++) {
+                s[j] = 1.f / (1.f + expf(-fabsf(__ldg(zp + j)) / tau));
+                hard *= s[j];
+                acc[j] = 0.f;
+            }
+            for (int c = 0; c <= k; c++) {
+                float wc = 1.f;
+                for (int j = 0; j < k; j++) wc *= (c == j + 1) ? (1.f - s[j]) : s[j];
+                const float g = __ldg(dw + i * m + c) * wc;
+                for (int j = 0; j < k; j++) acc[j] += g * ((c == j + 1) ? -s[j] : (1.f - s[j]));
+            }
+            for (int j = 0; j < k; j++) {
+                const float zj = __ldg(zp + j);
+                const float sg = zj > 0.f ? 1.f : (zj < 0.f ? -1.f : 0.f);
+                dp[j] = sg * acc[j] / tau;
+            }
+            (void)hard;
+        }
+    }
+}
+
+int launch_code_weights_bwd(const float *z, const float *dw, int64_t N, int T, int k, int weight_mode, float tau,
+                            float *dz, cudaStream_t st) {
+    const long long NT = (long long)N * T;
+    long long grid = (NT + 255) / 256;
+    const long long cap = (long long)num_sms() * 8;
+    if (grid > cap) grid = cap;
+    if (grid < 1) grid = 1;
+    code_weights_bwd_kernel<<<(unsigned)grid, 256, 0, st>>>(z, dw, NT, k, weight_mode, tau, dz);
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return LFFN_OK;
+}
+
 // ---- launchers -------------------------------------------------------------------------------
 template <int V, typename XT>
 static int launch_fwht_v(const void *x, void *out, int64_t N, float scale, cudaStream_t st) {

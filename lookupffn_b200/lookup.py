@@ -124,13 +124,23 @@ class Hashing(nn.Module):
     def forward(self, x, t_begin=0, t_count=None):
         """x [N, hidden] -> (row indices int32 [N, T*m] with table offsets added, weights fp32 [N, T*m])."""
         t_count = self.num_table - t_begin if t_count is None else t_count
-        if isinstance(self.projection, nn.Linear):
-            z = self.projection(x).float().reshape(x.shape[0], self.num_table, self.code_length)
+        p = self.projection
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or any(q.requires_grad for q in p.parameters()))
+        if isinstance(p, nn.Linear):
+            z = p(x).float().reshape(x.shape[0], self.num_table, self.code_length)
             z = z[:, t_begin:t_begin + t_count].contiguous()
+            if needs_grad:
+                return ops.CodeScore.apply(z, self.bit_order, self.weight_mode, self.tau)
             return ops.compute_code_score(z, bit_order=self.bit_order, weight_mode=self.weight_mode, tau=self.tau,
                                           add_offsets=True)
-        p = self.projection
         wk, tw = p.kernel_weight()
+        if needs_grad:
+            # training: projection and weights as two differentiable steps (z makes one round trip through HBM);
+            # inference below runs the single fused kernel
+            assert t_begin == 0 and t_count == self.num_table, "training runs on the whole table range"
+            z = ops.Projection.apply(x, p.weight, p.bias, p.had_scale, p.mix[0], p.mix[1], wk, tw)
+            return ops.CodeScore.apply(z.reshape(x.shape[0], self.num_table, self.code_length), self.bit_order,
+                                       self.weight_mode, self.tau)
         desc = ops.make_hash_desc(self.hidden_size, wk, p.bias.detach().contiguous(), self.num_table,
                                   self.code_length, transpose_w=tw, had_scale=p.had_scale, mix_a=p.mix[0],
                                   mix_b=p.mix[1], bit_order=self.bit_order, weight_mode=self.weight_mode, tau=self.tau)

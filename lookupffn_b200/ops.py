@@ -118,6 +118,101 @@ def compute_code_score(hash_scores, training=False, bit_order=MSB_FIRST, weight_
     return code, score
 
 
+def code_weights_bwd(z, dw, weight_mode=WEIGHT_SCORE, tau=0.5):
+    """dz [N, T, k] from dw [N, T*m]: the gradient autograd derives from compute_code_score_torch
+    (compute_code_score/kernel.py:43-55)."""
+    L.require_cuda(z, dw)
+    z, dw = _contig(z), _contig(dw.float())
+    N, T, k = z.shape
+    dz = torch.empty_like(z)
+    with torch.cuda.device(z.device):
+        L.check(L.lib().lffn_code_weights_bwd(L.ptr(z), L.ptr(dw), N, T, k, weight_mode, float(tau), L.ptr(dz),
+                                              L.stream_ptr(z.device)))
+    return dz
+
+
+class CodeScore(torch.autograd.Function):
+    """z [N, T, k] -> (row indices with table offsets, weights); the weights are differentiable in z."""
+
+    @staticmethod
+    def forward(ctx, z, bit_order, weight_mode, tau):
+        z = _contig(z.float())
+        idx, w = compute_code_score(z, bit_order=bit_order, weight_mode=weight_mode, tau=tau, add_offsets=True)
+        ctx.save_for_backward(z)
+        ctx.weight_mode, ctx.tau = weight_mode, tau
+        ctx.mark_non_differentiable(idx)
+        return idx, w
+
+    @staticmethod
+    def backward(ctx, _didx, dw):
+        (z,) = ctx.saved_tensors
+        return code_weights_bwd(z, dw, ctx.weight_mode, ctx.tau), None, None, None
+
+
+class Projection(torch.autograd.Function):
+    """z = BH4(x): forward by the fused hash kernel (projection only); backward recomputes the S stage inputs
+    per rotation and walks them in reverse with the Hadamard kernel (the transform is symmetric) and batched
+    64 x 64 library GEMMs (torch.einsum) for the block-diagonal factors -- the reference's own backward is
+    autograd over the same einsum/hadamard chain (bh4/kernel.py:23-36)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, had_scale, mix_a, mix_b, kernel_weight, kernel_transposed):
+        R, S, NB, BS, _ = weight.shape
+        D = NB * BS
+        out_dim = bias.numel()
+        desc = make_hash_desc(x.shape[1], kernel_weight, _contig(bias.detach().float()), out_dim, 1,
+                              transpose_w=kernel_transposed, had_scale=had_scale, mix_a=mix_a, mix_b=mix_b,
+                              weight_mode=WEIGHT_ONES)
+        _, _, z = hash_fwd(x, desc, want_z=True, want_codes=False)
+        ctx.save_for_backward(x, weight)
+        ctx.meta = (D, BS, S, R, out_dim, had_scale, mix_a, mix_b)
+        return z
+
+    @staticmethod
+    def backward(ctx, dz):
+        x, weight = ctx.saved_tensors
+        D, BS, S, R, out_dim, had_scale, mix_a, mix_b = ctx.meta
+        N, d_in = x.shape
+        NB = D // BS
+        dz = _contig(dz.float())
+        dbias = dz.sum(0) if ctx.needs_input_grad[2] else None
+        dzp = dz if out_dim == R * D else torch.nn.functional.pad(dz, (0, R * D - out_dim))
+        u = x.float()
+        if d_in < D:
+            u = torch.nn.functional.pad(u, (0, D - d_in))
+        du = (mix_b * dzp.reshape(N, R, D).sum(1)) if mix_b != 0 else torch.zeros(N, D, device=x.device)
+        need_w = ctx.needs_input_grad[1]
+        dweight = torch.zeros_like(weight, dtype=torch.float32) if need_w else None
+        w = weight.detach().float()
+        for r in range(R):
+            ys = []
+            y = u
+            for j in range(S):  # recompute the inputs of every stage
+                ys.append(y)
+                if BS == 1:
+                    t = y * w[r, j].reshape(D)
+                else:
+                    t = torch.einsum("bni,noi->bno", y.reshape(N, NB, BS), w[r, j]).reshape(N, D)
+                y = hadamard(_contig(t), had_scale) if j < S - 1 else None
+            g = _contig(mix_a * dzp[:, r * D:(r + 1) * D])
+            for j in range(S - 1, -1, -1):
+                g = hadamard(g, had_scale)
+                if BS == 1:
+                    if need_w:
+                        dweight[r, j] = (g * ys[j]).sum(0).reshape(NB, 1, 1)
+                    g = _contig(g * w[r, j].reshape(D))
+                else:
+                    g3 = g.reshape(N, NB, BS)
+                    if need_w:
+                        dweight[r, j] = torch.einsum("bno,bni->noi", g3, ys[j].reshape(N, NB, BS))
+                    g = _contig(torch.einsum("bno,noi->bni", g3, w[r, j]).reshape(N, D))
+            du = du + g
+        dx = du[:, :d_in].to(x.dtype) if ctx.needs_input_grad[0] else None
+        if need_w:
+            dweight = dweight.to(weight.dtype)
+        return dx, dweight, dbias, None, None, None, None, None
+
+
 # ---- gather and its backward ------------------------------------------------------------------------
 def _check_gather_args(indexes, source, weights):
     # the reference's asserts (gather/cuda/kernel.py:28-43) minus its `index_size % 2` and

@@ -413,3 +413,71 @@ def test_full_size_forward_properties(dev):
     yb = ops.weighted_vector_gather_add(idx[:, h:].contiguous(), tables, w[:, h:].contiguous(), out_dtype=torch.float32)
     err = (ya + yb - y32).abs().max() / y32.abs().max()
     assert float(err) < 1e-5
+
+
+# ---- gradients through the whole layer --------------------------------------------------------------------------
+def _torch_reference_layer(mod, x, idx):
+    """fp64 PyTorch restatement of the layer for gradient checks (lookup.py:29-39,98-129, bh4/kernel.py:23-36,
+    compute_code_score/kernel.py:51-53).  The discrete row indices come from the CUDA forward: codes carry no
+    gradient, and reusing them keeps a coordinate at rounding level from picking another row."""
+    from scipy.linalg import hadamard as sylvester
+
+    p = mod.hash.projection
+    T, k = mod.hash.num_table, mod.hash.code_length
+    u = torch.nn.functional.layer_norm(x.double(), (x.shape[-1],), mod.LayerNorm.weight.double(),
+                                       mod.LayerNorm.bias.double(), mod.LayerNorm.eps)
+    N = u.shape[0]
+    if isinstance(p, torch.nn.Linear):
+        z = u @ p.weight.double().t() + p.bias.double()
+    else:
+        D, BS, R = p.padded_in_dim, p.block_size, p.num_repeat
+        H = torch.tensor(sylvester(D), dtype=torch.float64, device=x.device)
+        up = torch.nn.functional.pad(u, (0, D - u.shape[1]))
+        outs = []
+        for r in range(R):
+            y = up
+            for j in range(p.weight.shape[1]):
+                y = torch.einsum("bni,noi->bno", y.reshape(N, D // BS, BS), p.weight[r, j].double()).reshape(N, D)
+                y = (y @ H) * p.had_scale
+            outs.append(y)
+        z = p.mix[0] * torch.cat(outs, -1) + p.mix[1] * up.repeat(1, R)
+        z = z[:, :T * k] + p.bias.double()
+    a = z.reshape(N, T, k).abs()
+    score = a.sum(-1) / torch.prod(1 + torch.exp(-2 * a), dim=-1)
+    rows = mod.tables.double().reshape(-1, mod.tables.shape[-1])[idx.long()]     # [N, T, d]
+    return (rows * score[:, :, None]).sum(1) + mod.bias.double()
+
+
+@pytest.mark.parametrize("ptype,block", [("bh4", 64), ("bh4", 16), ("dense", 64), ("sign_hadamard", 1)])
+def test_layer_gradients_match_torch_reference(dev, ptype, block):
+    from lookupffn_b200 import LookupFFN
+
+    torch.manual_seed(3)
+    hidden = 256 if block == 64 else 96
+    cfg = Namespace(hidden_size=hidden, ffn_num_table=40, ffn_table_size=64, layer_norm_eps=1e-5,
+                    projection_type=ptype, block_size=block)
+    mod = LookupFFN(cfg, 64).to(dev).train()
+    with torch.no_grad():
+        mod.hash.projection.bias.normal_(0, 0.05)
+        if ptype == "bh4":
+            mod.hash.projection.weight.mul_(4.0)  # z of order 1, so that the score's exponentials matter
+    x = torch.randn(50, hidden, device=dev, requires_grad=True)
+    y = mod(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    got = {n: q.grad.clone() for n, q in mod.named_parameters() if q.grad is not None}
+    got["x"] = x.grad.clone()
+    with torch.no_grad():
+        idx, _ = mod.hash(mod.LayerNorm(x))
+    for q in mod.parameters():
+        q.grad = None
+    x2 = x.detach().clone().requires_grad_(True)
+    y_ref = _torch_reference_layer(mod, x2, idx)
+    assert rel_err(t2n(y.detach()), y_ref.detach().cpu().numpy()) < 1e-4
+    y_ref.backward(g.double())
+    want = {n: q.grad for n, q in mod.named_parameters() if q.grad is not None}
+    want["x"] = x2.grad
+    assert set(got) == set(want)
+    for n in want:
+        # north-star bar for gradients with fp32 tables: 1e-3 relative
+        assert rel_err(t2n(got[n].float()), want[n].float().cpu().numpy()) < 1e-3, n
