@@ -357,6 +357,83 @@ def run_table_sharded(args, rank, world, local):
     }
 
 
+def run_encoder(args, rank, world, local):
+    """BASELINE config 2: RoBERTa-small prenorm encoder inference with every FFN a LookupFFN (4 layers, hidden
+    512, 8 heads, seq 512, batch 32 per GPU, T=256, k=8, fp32 tables, reference BH4 projection).  seq/s."""
+    from argparse import Namespace
+
+    from lookupffn_b200.encoder import Lookup
+
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    cfg = Namespace(vocab_size=50265, type_vocab_size=1, pad_token_id=1, num_hidden_layers=4, num_attention_heads=8,
+                    attention_head_size=64, layer_norm_eps=1e-5, hidden_size=512, hidden_dropout_prob=0.1,
+                    attention_probs_dropout_prob=0.1, max_position_embeddings=512, projection_type=args.projection,
+                    block_size=64, ffn_num_table=256, ffn_table_size=256)
+    torch.manual_seed(1234)
+    model = Lookup(cfg).to(device).eval()
+    B, S = 32, 512
+    g = torch.Generator().manual_seed(99 + rank)
+    ids_host = torch.randint(5, cfg.vocab_size, (B, S), generator=g)
+    ids_host[:, 0] = 0
+    ids_host = ids_host.pin_memory()
+    ids = ids_host.to(device)
+    tt = torch.zeros(B, S, dtype=torch.long, device=device)
+    pos = torch.arange(S, device=device)[None].repeat(B, 1)
+    mask = torch.ones(B, S, device=device)
+    out_host = torch.empty(B, S, cfg.hidden_size).pin_memory()
+
+    def step():
+        with torch.inference_mode():
+            return model(ids, tt, pos, mask)[0]
+
+    def e2e_step():
+        ids.copy_(ids_host, non_blocking=True)
+        out_host.copy_(step(), non_blocking=True)
+
+    def timed(fn):
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        return e0.elapsed_time(e1)
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    ms = timed(step)
+    clocks = sampler.result()
+    e2e_step()
+    e2e_ms = timed(e2e_step)
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms, e2e_ms = (float(v) for v in t.tolist())
+    if rank != 0:
+        return None
+    return {
+        "metric": "roberta_small_lookupffn_encoder_inference", "value": world * B * args.steps / (ms * 1e-3),
+        "unit": "seq/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c2: RoBERTa-small prenorm encoder inference, 4 layers, hidden 512, 8 heads, seq 512, "
+                               "batch 32 per GPU, vocab 50265, LookupFFN T=256 k=8 d_out=512 fp32 tables, "
+                               f"projection {args.projection}, random-init weights",
+                   "l2": "inputs larger than L2: 4 x 134 MB of tables per step"},
+        "tokens_per_s": world * B * S * args.steps / (ms * 1e-3),
+        "e2e": {"value": world * B * args.steps / (e2e_ms * 1e-3), "unit": "seq/s", "h2d_bytes_per_step": B * S * 8,
+                "d2h_bytes_per_step": B * S * cfg.hidden_size * 4, "api": "lookupffn_b200.encoder.Lookup.forward"},
+        "gpu_launches": 2 * cfg.num_hidden_layers * args.steps, "clocks": clocks,
+    }
+
+
 # ---- the reference's CPU path, on this box's host cores ---------------------------------------------------
 def load_ref_modules():
     """The reference's own CPU extensions compiled (unmodified) into oracle/_ref, or None."""
@@ -456,7 +533,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c2enc"])
+    ap.add_argument("--projection", default="bh4", choices=["bh4", "sign_hadamard", "dense"],
+                    help="projection of the c2enc workload (bh4 = the reference configs)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-chunk", type=int, default=8192)
     ap.add_argument("--cpu-tokens", type=int, default=4096)
@@ -486,6 +565,13 @@ def main():
         torch.cuda.set_device(local)
         torch.distributed.init_process_group("nccl", rank=rank, world_size=world,
                                              device_id=torch.device("cuda", local))
+    if args.workload == "c2enc":
+        out = run_encoder(args, rank, world, local)
+        if out is not None:
+            print(json.dumps(out), flush=True)
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return 0
     if args.shard == "tables":
         out = run_table_sharded(args, rank, world, local)
         if out is not None:

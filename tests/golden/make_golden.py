@@ -19,6 +19,7 @@ Python modules and calling them on seeded inputs.  What is executed, per group:
              C++ weighted_vector_gather_add_scalar / _avx2_par (gather/cpu/torch_extension.cpp)
   bwd_*      indexed_inner_product(use_torch=True), weighted_vector_scatter_add(use_torch=True)
              and WeightedVectorGatherAdd's torch path (gather/cuda/kernel.py:72-173)
+  enc_*      Lookup.forward (encoder.py:21-32), eval, 2 layers, on CPU, same bindings as mod_*
   mod_*      LookupFFN.forward (lookup.py:79-129), eval, on CPU, for projection_type "dense"
              and "bh4"; bh4/gather dispatch bound to the functions above because the
              reference's CPU wrappers assert one fixed shape and need libxsmm
@@ -207,6 +208,28 @@ def main():
         g[f"mod_{tag}_code"] = code.numpy()
         g[f"mod_{tag}_score"] = score.numpy()
         g[f"mod_{tag}_y"] = y.numpy()
+
+    # ---- the Lookup encoder (the caller of the layer): layer.py:66-78, encoder.py:9-37 -----------------
+    import src.roberta.models.prenorm_lookup.encoder as ref_encoder
+
+    cfg = Namespace(vocab_size=120, type_vocab_size=1, pad_token_id=1, num_hidden_layers=2, num_attention_heads=4,
+                    attention_head_size=16, layer_norm_eps=1e-5, hidden_size=64, hidden_dropout_prob=0.1,
+                    attention_probs_dropout_prob=0.1, max_position_embeddings=32, projection_type="bh4",
+                    block_size=64, ffn_num_table=12, ffn_table_size=16, intermediate_size=256,
+                    initializer_range=0.02)
+    enc = ref_encoder.Lookup(cfg)
+    enc.eval()
+    B, S = 3, 24  # B*S a multiple of 8: the reference torch gather works in mini-batches of 8
+    ids = rng.randint(5, cfg.vocab_size, size=(B, S)).astype(np.int64)
+    ids[:, 0] = 0
+    mask = np.ones((B, S), dtype=np.float32)
+    mask[1, 17:] = 0.0
+    with torch.no_grad():
+        out, _ = enc(torch.from_numpy(ids), torch.zeros(B, S, dtype=torch.long),
+                     torch.arange(S)[None].repeat(B, 1), torch.from_numpy(mask))
+    for name, p in enc.state_dict().items():
+        g[f"enc_param_{name}"] = p.numpy().copy()
+    g["enc_ids"], g["enc_mask"], g["enc_out"] = ids, mask, out.numpy()
 
     np.savez_compressed(OUT, **g)
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(g), "arrays")

@@ -91,3 +91,21 @@ def test_module_loads_reference_state_dict(golden):
                         layer_norm_eps=1e-5, projection_type=ptype, block_size=64)
         mod = LookupFFN(cfg, d_out)
         mod.load_state_dict(sd, strict=True)
+
+
+def _encoder_config():
+    from argparse import Namespace
+
+    return Namespace(vocab_size=120, type_vocab_size=1, pad_token_id=1, num_hidden_layers=2, num_attention_heads=4,
+                     attention_head_size=16, layer_norm_eps=1e-5, hidden_size=64, hidden_dropout_prob=0.1,
+                     attention_probs_dropout_prob=0.1, max_position_embeddings=32, projection_type="bh4",
+                     block_size=64, ffn_num_table=12, ffn_table_size=16)
+
+
+def test_encoder_loads_reference_state_dict(golden):
+    from lookupffn_b200.encoder import Lookup
+
+    sd = {k[len("enc_param_"):]: torch.from_numpy(v) for k, v in golden.items() if k.startswith("enc_param_")}
+    enc = Lookup(_encoder_config())
+    assert set(enc.state_dict()) == set(sd)
+    enc.load_state_dict(sd, strict=True)
