@@ -88,6 +88,29 @@ def hash_fwd(x, desc, t_begin=0, t_count=None, want_z=False, want_codes=True):
     return idx, w, z
 
 
+def layer_fwd(x, desc, tables, bias=None, t_begin=0, t_count=None, out_dtype=None):
+    """Hash -> gather -> + bias for tables [t_begin, t_begin+t_count) through lffn_layer_fwd: one fused kernel when
+    the shape allows it, otherwise the hash and gather kernels with workspaces allocated here.
+    Reference: LookupFFN._forward after LayerNorm (lookup.py:101-110)."""
+    L.require_cuda(x, tables, bias)
+    x, tables = _contig(x), _contig(tables)
+    N = x.shape[0]
+    t_count = desc.T - t_begin if t_count is None else t_count
+    m = desc.k + 1 if desc.weight_mode == WEIGHT_SOFT_FLIP else 1
+    d_out = tables.shape[1]
+    out_dtype = tables.dtype if out_dtype is None else out_dtype
+    out = torch.empty((N, d_out), dtype=out_dtype, device=x.device)
+    idx = torch.empty((N, t_count * m), dtype=torch.int32, device=x.device)
+    w = torch.empty((N, t_count * m), dtype=torch.float32, device=x.device)
+    if bias is not None:
+        bias = _contig(bias.float())
+    with torch.cuda.device(x.device):
+        L.check(L.lib().lffn_layer_fwd(C.byref(desc), L.ptr(x), L.dtype_code(x.dtype), N, t_begin, t_count, L.ptr(tables),
+                                       L.dtype_code(tables.dtype), d_out, L.ptr(bias), L.ptr(out),
+                                       L.dtype_code(out_dtype), L.ptr(idx), L.ptr(w), L.stream_ptr(x.device)))
+    return out
+
+
 def bh4(x, w, training=False, transpose_w=False, had_scale=1.0):
     """x [N, D] (D a power of two), w [R, S, D/BS, BS, BS] -> [N, R*D]: R repeats of S x (block-diagonal
     multiply, Hadamard).  Reference: bh4(x, w, training) (bh4/kernel.py:10-36), CUDA semantics."""

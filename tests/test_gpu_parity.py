@@ -539,3 +539,55 @@ def test_code_weights_bwd_matches_autograd(dev, mode, k):
     assert rel_err(t2n(dz), zd.grad.float().cpu().numpy()) < 1e-5 or float(zd.grad.abs().max()) == 0.0
     if mode == "ones":
         assert float(dz.abs().max()) == 0.0
+
+
+# ---- the whole-layer entry point (lffn_layer_fwd) --------------------------------------------------------------------
+FUSED_CASES = [
+    # N, d_in, D, T, d_out, bf16, weight_mode, bit_order, (t_begin, t_count)
+    (77, 768, 1024, 512, 768, True, O.WEIGHT_SCORE, O.MSB_FIRST, None),      # benchmark config 3
+    (50, 512, 512, 128, 512, False, O.WEIGHT_ONES, O.LSB_FIRST, None),       # benchmark config 1
+    (33, 400, 512, 200, 512, True, O.WEIGHT_SCORE, O.MSB_FIRST, None),       # T*k not a multiple of D; VPL 2
+    (20, 1000, 1024, 300, 1024, True, O.WEIGHT_SCORE, O.LSB_FIRST, (64, 170)),  # a rank's share of the tables
+    (9, 512, 512, 96, 768, False, O.WEIGHT_SCORE, O.MSB_FIRST, (32, 64)),    # VPL 6
+    (9, 512, 512, 64, 1024, False, O.WEIGHT_SCORE, O.MSB_FIRST, None),       # VPL 8
+    (12, 100, 128, 40, 64, False, O.WEIGHT_SCORE, O.MSB_FIRST, None),        # small D: the scalar-layout hash kernel
+    (12, 512, 512, 64, 512, False, O.WEIGHT_SCORE, O.MSB_FIRST, (10, 40)),   # table range not aligned to anything
+]
+
+
+@pytest.mark.parametrize("case", FUSED_CASES, ids=[f"f{i}" for i in range(len(FUSED_CASES))])
+def test_layer_fwd_matches_oracle_and_separate_calls(dev, case):
+    from lookupffn_b200 import ops
+
+    N, d_in, D, T, d_out, bf16, wm, bo, rng_t = case
+    k = 8
+    rng = np.random.RandomState(N + T)
+    R = max(1, -(-T * k // D))
+    signs = make_proj(rng, D, 1, 2, R, signs=True)
+    pbias = (0.05 * rng.randn(T * k)).astype(np.float32)
+    obias = rng.randn(d_out).astype(np.float32)
+    x = rng.randn(N, d_in).astype(np.float32)
+    tab = (0.02 * rng.randn(T << k, d_out)).astype(np.float32)
+    tb, tc = (0, T) if rng_t is None else rng_t
+    hs = 1.0 / 32
+    if bf16:
+        xb, tabb = O.f32_to_bf16_bits(x), O.f32_to_bf16_bits(tab)
+        xt, tt = bf16_tensor(xb, dev), bf16_tensor(tabb, dev)
+        x_ref, tab_ref = O.bf16_bits_to_f32(xb), tabb
+    else:
+        xt, tt = torch.from_numpy(x).to(dev), torch.from_numpy(tab).to(dev)
+        x_ref, tab_ref = x, tab
+    desc = ops.make_hash_desc(d_in, torch.from_numpy(signs).to(dev), torch.from_numpy(pbias).to(dev), T, k,
+                              had_scale=hs, mix_a=1.0, mix_b=0.0, bit_order=bo, weight_mode=wm)
+    local = tt[tb << k:(tb + tc) << k].contiguous()
+    y = ops.layer_fwd(xt, desc, local, bias=torch.from_numpy(obias).to(dev), t_begin=tb, t_count=tc)
+    # lffn_hash_fwd + lffn_gather_fwd called separately on the same inputs: bit-identical
+    idx, w, _ = ops.hash_fwd(xt, desc, t_begin=tb, t_count=tc)
+    y2 = ops.weighted_vector_gather_add(idx, local, w, bias=torch.from_numpy(obias).to(dev))
+    np.testing.assert_array_equal(t2n(y), t2n(y2))
+    # the oracle, with the GPU's weights (expf differs in the last bits between libm and CUDA)
+    z_ref = O.project(x_ref, signs, T * k, had_scale=hs, mix_a=1.0, mix_b=0.0, bias=pbias)
+    idx_ref, _ = O.code_weights(z_ref[:, tb * k:(tb + tc) * k], tc, k, bit_order=bo, weight_mode=wm)
+    np.testing.assert_array_equal(t2n(idx), idx_ref)
+    y_ref = O.gather(idx_ref, t2n(w), tab_ref[tb << k:(tb + tc) << k], bias=obias, out_bf16=bf16)
+    np.testing.assert_array_equal(t2n(y), y_ref)
