@@ -14,6 +14,8 @@
 // Weights of 256 output columns (PC/BS blocks) are staged per pass into shared memory as
 // Ws[g][i][o] with a 16-byte XOR swizzle, from either global layout ([o][i] or [i][o]).
 // No tensor cores: sign bits must reproduce the fp32 fmaf chain.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "hash_common.cuh"
 
@@ -41,11 +43,11 @@ __device__ __forceinline__ void radix_butterflies(float (&v)[RADIX]) {
 }
 
 // One pass of the transform over bits [lo, lo+nb) of the coordinate index, RADIX = 2^nb.
-template <int RADIX>
+template <int RADIX, int NW>
 __device__ __forceinline__ void fwht_pass(float *Y, int D, int lo, float scale, int warp, int lane) {
     const int ngroups = D / RADIX;
     const int lo_mask = (1 << lo) - 1;
-    for (int gi = warp; gi < ngroups; gi += HB_THREADS / 32) {
+    for (int gi = warp; gi < ngroups; gi += NW) {
         const int base = ((gi >> lo) * RADIX << lo) | (gi & lo_mask);
         float v[RADIX];
 #pragma unroll
@@ -60,16 +62,17 @@ __device__ __forceinline__ void fwht_pass(float *Y, int D, int lo, float scale, 
     }
 }
 
+template <int NW = HB_THREADS / 32>
 __device__ __forceinline__ void fwht_tile(float *Y, int D, float scale, int warp, int lane) {
     int bits = 31 - __clz(D);
     while (bits > 0) {
         const int nb = bits >= 4 ? 4 : bits;
         const int lo = bits - nb;
         const float sc = lo == 0 ? scale : 1.f;
-        if (nb == 4) fwht_pass<16>(Y, D, lo, sc, warp, lane);
-        else if (nb == 3) fwht_pass<8>(Y, D, lo, sc, warp, lane);
-        else if (nb == 2) fwht_pass<4>(Y, D, lo, sc, warp, lane);
-        else fwht_pass<2>(Y, D, lo, sc, warp, lane);
+        if (nb == 4) fwht_pass<16, NW>(Y, D, lo, sc, warp, lane);
+        else if (nb == 3) fwht_pass<8, NW>(Y, D, lo, sc, warp, lane);
+        else if (nb == 2) fwht_pass<4, NW>(Y, D, lo, sc, warp, lane);
+        else fwht_pass<2, NW>(Y, D, lo, sc, warp, lane);
         bits = lo;
         __syncthreads();
     }
@@ -220,8 +223,14 @@ __device__ __forceinline__ void ffma2(unsigned long long &acc, unsigned long lon
 
 constexpr int HF_CHUNK_FLOATS = 4 * 32 * 64;  // 4 blocks x 32 rows x 64 outputs
 
-template <typename XT>
-__global__ void __launch_bounds__(HB_THREADS, 1) hash_block64_kernel(HashArgs a) {
+// THREADS = columns per pass (one 8 x 4 item per thread): 256 threads work on 4 blocks x 32-row chunks, 512 threads
+// on 8 blocks x 16-row chunks; the chunk is 32 KB either way.
+template <typename XT, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
+    constexpr int PC = THREADS;            // columns per pass
+    constexpr int CR = 8192 / PC;          // input rows per chunk
+    constexpr int NBLK = PC / 64;          // blocks per pass
+    constexpr int NW = THREADS / 32;
     extern __shared__ __align__(16) float smem[];
     const int D = a.D;
     float *Y = smem;                              // [D][HB_MP]
@@ -233,7 +242,7 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block64_kernel(HashArgs a)
     const long long g_lo = (long long)a.t_begin * k, g_hi = (long long)(a.t_begin + a.t_count) * k;
     const long long out_pitch = (long long)a.t_count * m;
     const int NB = D / 64;
-    const int cps = D / 128;                          // chunks per stage: D/256 passes x 2 halves
+    const int cps = (D / PC) * (64 / CR);            // chunks per stage: passes x row slices
     const int nrot = a.r_hi - a.r_lo + 1;
     const long long chunks_per_tile = (long long)nrot * a.S * cps;
     const long long ntiles = (a.N + HB_M - 1) / HB_M;
@@ -248,14 +257,15 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block64_kernel(HashArgs a)
         const int r = a.r_lo + (int)(in_tile / (a.S * cps));
         const int rem = (int)(in_tile % (a.S * cps));
         const int s = rem / cps, c = rem % cps;
-        const int p = c >> 1, h = c & 1;
-        const float *src = a.w + (((long long)r * a.S + s) * NB + 4 * p) * 4096 + h * 32 * 64;
+        const int p = c / (64 / CR), h = c % (64 / CR);
+        const float *src = a.w + (((long long)r * a.S + s) * NB + NBLK * p) * 4096 + h * CR * 64;
         float *dst = Wb + (gc & 1) * HF_CHUNK_FLOATS;
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const int q = tid + HB_THREADS * j;          // 16-byte piece 0..2047
-            const int g = q >> 9, rm = q & 511, il = rm >> 4, o4 = rm & 15;
-            cp_async16(dst + g * 2048 + il * 64 + ((o4 ^ (il & 15)) << 2), src + (long long)g * 4096 + il * 64 + o4 * 4);
+        for (int j = 0; j < 2048 / THREADS; j++) {
+            const int q = tid + THREADS * j;             // 16-byte piece 0..2047
+            const int g = q / (CR * 16), rm = q % (CR * 16), il = rm >> 4, o4 = rm & 15;
+            cp_async16(dst + g * (CR * 64) + il * 64 + ((o4 ^ (il & 15)) << 2),
+                       src + (long long)g * 4096 + il * 64 + o4 * 4);
         }
         cp_async_commit();
     };
@@ -267,34 +277,34 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block64_kernel(HashArgs a)
         const int mt = (int)min((long long)HB_M, a.N - n0);
         for (int r = a.r_lo; r <= a.r_hi; r++) {
             __syncthreads();
-            for (int i = tid; i < HB_CARRY * HB_M; i += HB_THREADS) {
+            for (int i = tid; i < HB_CARRY * HB_M; i += THREADS) {
                 const int e = i / HB_M, mm = i % HB_M;
                 carry[e * HB_MP + mm] = Y[(D - HB_CARRY + e) * HB_MP + mm];
             }
             __syncthreads();
-            for (int mm = warp; mm < HB_M; mm += HB_THREADS / 32) {
+            for (int mm = warp; mm < HB_M; mm += NW) {
                 const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
                 for (int e = lane; e < D; e += 32)
                     Y[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
             }
             for (int s = 0; s < a.S; s++) {
-                const int cq = tid & 63, tq = tid >> 6;          // 64 column quads x 4 token octets
+                const int cq = tid % (PC / 4), tq = tid / (PC / 4);   // PC/4 column quads x 4 token octets
                 const int g = cq >> 4, o4 = cq & 15;
-                for (int p = 0; p < D / 256; p++) {
-                    const int col0 = p * 256;
+                for (int p = 0; p < D / PC; p++) {
+                    const int col0 = p * PC;
                     unsigned long long acc[4][4];               // [token pair][column]
 #pragma unroll
                     for (int pp = 0; pp < 4; pp++)
 #pragma unroll
                         for (int q = 0; q < 4; q++) acc[pp][q] = 0ull;
-                    for (int h = 0; h < 2; h++) {
+                    for (int h = 0; h < 64 / CR; h++) {
                         cp_async_wait_all();
                         __syncthreads();           // chunk gc landed for everyone; buffer (gc+1)&1 is free; Y is loaded
                         issue_chunk(gc + 1);
-                        const float *wb = Wb + (gc & 1) * HF_CHUNK_FLOATS + g * 2048;
-                        const float *yb = Y + (size_t)(col0 + g * 64 + h * 32) * HB_MP + tq * 8;
+                        const float *wb = Wb + (gc & 1) * HF_CHUNK_FLOATS + g * (CR * 64);
+                        const float *yb = Y + (size_t)(col0 + g * 64 + h * CR) * HB_MP + tq * 8;
 #pragma unroll 8
-                        for (int il = 0; il < 32; il++) {
+                        for (int il = 0; il < CR; il++) {
                             const ulonglong2 x0 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP);
                             const ulonglong2 x1 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP + 4);
                             const float4 w4 = *reinterpret_cast<const float4 *>(wb + il * 64 + ((o4 ^ (il & 15)) << 2));
@@ -318,10 +328,10 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block64_kernel(HashArgs a)
                     }
                 }
                 __syncthreads();
-                fwht_tile(Y, D, a.had_scale, warp, lane);
+                fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
             }
             const long long c_lo = (long long)r * D, c_hi = c_lo + D;
-            for (int mm = warp; mm < HB_M; mm += HB_THREADS / 32) {
+            for (int mm = warp; mm < HB_M; mm += NW) {
                 const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
                 for (int e = lane; e < D; e += 32) {
                     const float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
@@ -339,7 +349,7 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block64_kernel(HashArgs a)
             long long t_end = c_hi / k;
             if (t_end > a.t_begin + a.t_count) t_end = a.t_begin + a.t_count;
             if (lane < mt && a.idx_out != nullptr) {
-                for (long long t = t_first + warp; t < t_end; t += HB_THREADS / 32) {
+                for (long long t = t_first + warp; t < t_end; t += NW) {
                     const int local0 = (int)(t * k - c_lo);
                     auto get = [&](int j) -> float {
                         const int e = local0 + j;
@@ -371,14 +381,17 @@ int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, c
     if (grid < 1) grid = 1;
     if (BS == 64 && transpose_w && a.D % 256 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0) {
         static_assert(2 * HF_CHUNK_FLOATS == HB_WFLOATS, "same shared-memory footprint as the generic kernel");
+        static const bool narrow_only = [] { const char *e = getenv("LFFN_BLOCK64_NARROW"); return e && e[0] == '1'; }();
+        const bool wide = a.D % 512 == 0 && !narrow_only;   // 512 threads: 16 warps per SM instead of 8
+        const int threads = wide ? 512 : 256;
         if (x_dtype == LFFN_F32) {
-            auto kern = hash_block64_kernel<float>;
+            auto kern = wide ? hash_block64_kernel<float, 512> : hash_block64_kernel<float, 256>;
             LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<(unsigned)grid, HB_THREADS, smem, st>>>(a);
+            kern<<<(unsigned)grid, threads, smem, st>>>(a);
         } else if (x_dtype == LFFN_BF16) {
-            auto kern = hash_block64_kernel<__nv_bfloat16>;
+            auto kern = wide ? hash_block64_kernel<__nv_bfloat16, 512> : hash_block64_kernel<__nv_bfloat16, 256>;
             LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<(unsigned)grid, HB_THREADS, smem, st>>>(a);
+            kern<<<(unsigned)grid, threads, smem, st>>>(a);
         } else {
             set_error("hash_fwd: unknown x dtype %d", x_dtype);
             return LFFN_ERR_INVALID_ARG;

@@ -133,3 +133,54 @@ class TableShardedLookupFFN(nn.Module):
                                     chunk_tokens=self.chunk_tokens, bias=self.bias)
         world = dist.get_world_size(self.group)
         return y, owned_tokens(N, dist.get_rank(self.group), world, self.chunk_tokens)
+
+
+class ShardedTableAdamW:
+    """Data-parallel training step for the `tables` parameter without a dense all-reduce.
+
+    Under the reference's DDP (main.py:40-47) every rank all-reduces the full [T, 2^k, d] table gradient
+    (67-134 MB per layer) and then runs the same optimizer update on every GPU.  Here the gradients are
+    reduce-scattered over the table dimension, rank g updates only tables [t_begin, t_begin + t_count) with
+    AdamW state for that shard only (1/world of the optimizer memory and arithmetic), and the updated shards
+    are all-gathered back.  Bytes on the wire equal an all-reduce; state and update work are divided by world.
+    T must be divisible by the world size.  The arithmetic is torch.optim.AdamW's (decoupled weight decay).
+    """
+
+    def __init__(self, tables, group=None, lr=1e-4, betas=(0.9, 0.98), eps=1e-6, weight_decay=0.01):
+        self.tables, self.group = tables, group
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        T = tables.shape[0]
+        if T % self.world != 0:
+            raise ValueError(f"T = {T} tables must be divisible by the world size {self.world}")
+        self.t_count = T // self.world
+        self.t_begin = self.rank * self.t_count
+        shard_shape = (self.t_count,) + tuple(tables.shape[1:])
+        self.exp_avg = torch.zeros(shard_shape, dtype=torch.float32, device=tables.device)
+        self.exp_avg_sq = torch.zeros(shard_shape, dtype=torch.float32, device=tables.device)
+        self.steps = 0
+
+    @torch.no_grad()
+    def step(self):
+        g_full = self.tables.grad
+        if g_full is None:
+            raise RuntimeError("tables.grad is None: run backward first")
+        g_full = g_full.float().contiguous()
+        g = torch.empty_like(self.exp_avg)
+        dist.reduce_scatter_tensor(g, g_full, op=dist.ReduceOp.SUM, group=self.group)
+        g /= self.world  # DDP averages gradients over ranks
+        self.steps += 1
+        b1, b2 = self.betas
+        shard = self.tables.data[self.t_begin:self.t_begin + self.t_count]
+        p = shard.float()
+        p.mul_(1 - self.lr * self.weight_decay)
+        self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+        self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+        bc1, bc2 = 1 - b1 ** self.steps, 1 - b2 ** self.steps
+        denom = (self.exp_avg_sq.sqrt() / (bc2 ** 0.5)).add_(self.eps)
+        p.addcdiv_(self.exp_avg, denom, value=-self.lr / bc1)
+        new_shard = p.to(self.tables.dtype).contiguous()
+        dist.all_gather_into_tensor(self.tables.data, new_shard, group=self.group)
+
+    def zero_grad(self):
+        self.tables.grad = None

@@ -91,3 +91,47 @@ def test_table_sharded_reduce_scatter_world2():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert res == [(0, True, True, 24), (1, True, True, 24)]
+
+
+def _adam_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        T, rows, d = 8, 16, 12
+        init = torch.randn(T, rows, d)
+        tables = torch.nn.Parameter(init.clone())
+        ref = torch.nn.Parameter(init.clone())
+        opt = sharded.ShardedTableAdamW(tables, lr=1e-2, betas=(0.9, 0.98), eps=1e-6, weight_decay=0.01)
+        ref_opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.98), eps=1e-6, weight_decay=0.01)
+        for step in range(3):
+            g_local = torch.randn(T, rows, d, generator=torch.Generator().manual_seed(100 * step + rank))
+            tables.grad = g_local.clone()
+            opt.step()
+            # what DDP does: all-reduce (mean) the dense gradient, then the full update on every rank
+            g_avg = g_local.clone()
+            dist.all_reduce(g_avg)
+            ref.grad = g_avg / world
+            ref_opt.step()
+        err = float((tables.detach() - ref.detach()).abs().max())
+        q.put((rank, err, tuple(opt.exp_avg.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_table_adamw_equals_ddp_allreduce_world2():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + os.getpid() % 90
+    procs = [ctx.Process(target=_adam_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=180) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, shape in res:
+        assert shape == (4, 16, 12)   # optimizer state covers half of the tables
+        assert err < 1e-6
