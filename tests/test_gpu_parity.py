@@ -591,3 +591,50 @@ def test_layer_fwd_matches_oracle_and_separate_calls(dev, case):
     np.testing.assert_array_equal(t2n(idx), idx_ref)
     y_ref = O.gather(idx_ref, t2n(w), tab_ref[tb << k:(tb + tc) << k], bias=obias, out_bf16=bf16)
     np.testing.assert_array_equal(t2n(y), y_ref)
+
+
+# ---- edge cases ----------------------------------------------------------------------------------------------------
+def test_empty_inputs(dev):
+    from lookupffn_b200 import ops
+
+    signs = torch.ones(1, 2, 256, 1, 1, device=dev)
+    desc = ops.make_hash_desc(200, signs, None, 32, 8)
+    idx, w, z = ops.hash_fwd(torch.zeros(0, 200, device=dev), desc, want_z=True)
+    assert idx.shape == (0, 32) and w.shape == (0, 32) and z.shape == (0, 256)
+    tab = torch.randn(64, 16, device=dev)
+    out = ops.weighted_vector_gather_add(torch.zeros(0, 4, dtype=torch.int32, device=dev), tab, torch.zeros(0, 4, device=dev))
+    assert out.shape == (0, 16)
+    # an empty index list gives the bias (or zeros)
+    b = torch.arange(16, device=dev, dtype=torch.float32)
+    out = ops.weighted_vector_gather_add(torch.zeros(3, 0, dtype=torch.int32, device=dev), tab, torch.zeros(3, 0, device=dev), bias=b)
+    assert torch.equal(out, b[None].repeat(3, 1))
+    dt = ops.weighted_vector_scatter_add(torch.zeros(0, 4, dtype=torch.int32, device=dev), torch.zeros(0, 16, device=dev),
+                                         torch.zeros(0, 4, device=dev), 64)
+    assert dt.shape == (64, 16) and float(dt.abs().max()) == 0.0
+    dt = ops.weighted_vector_scatter_add(torch.zeros(0, 4, dtype=torch.int32, device=dev), torch.zeros(0, 16, device=dev),
+                                         torch.zeros(0, 4, device=dev), 64, structure=(4, 1, 16))
+    assert float(dt.abs().max()) == 0.0
+    assert ops.hadamard(torch.zeros(0, 64, device=dev)).shape == (0, 64)
+
+
+def test_module_bf16_tables_and_leading_dims(dev):
+    from lookupffn_b200 import LookupFFN
+
+    torch.manual_seed(1)
+    cfg = Namespace(hidden_size=768, ffn_num_table=64, ffn_table_size=256, layer_norm_eps=1e-5,
+                    projection_type="sign_hadamard", block_size=1, lookup_table_dtype=torch.bfloat16)
+    mod = LookupFFN(cfg, 768).to(dev).eval()
+    x = torch.randn(2, 3, 5, 768, device=dev)
+    with torch.no_grad():
+        y = mod(x)
+        u = mod.LayerNorm(x.reshape(-1, 768))
+        idx, w = mod.hash(u)
+    assert y.shape == (2, 3, 5, 768) and y.dtype == torch.bfloat16
+    ref = O.gather(t2n(idx), t2n(w), t2n(mod.tables.reshape(-1, 768)), bias=t2n(mod.bias), out_bf16=True)
+    np.testing.assert_array_equal(t2n(y.reshape(-1, 768)), ref)
+    # codes from the oracle's projection of the same layer-normed input
+    p = mod.hash.projection
+    z_ref = O.project(t2n(u), t2n(p.weight), 64 * 8, had_scale=float(np.float32(p.had_scale)), mix_a=1.0, mix_b=0.0,
+                      bias=t2n(p.bias))
+    idx_ref, _ = O.code_weights(z_ref, 64, 8)
+    np.testing.assert_array_equal(t2n(idx), idx_ref)
