@@ -110,9 +110,9 @@ int lffn_device_status(uint32_t *status_out, lffn_stream_t stream) {
 }
 
 int lffn_fwht(const void *x, void *out, int64_t N, int32_t D, int32_t dtype, float scale, lffn_stream_t stream) {
-    LFFN_REQUIRE(x != nullptr && out != nullptr, LFFN_ERR_INVALID_ARG, "fwht: NULL buffer");
     LFFN_REQUIRE(N >= 0, LFFN_ERR_INVALID_ARG, "fwht: N = %lld", (long long)N);
-    if (N == 0) return LFFN_OK;
+    if (N == 0) return LFFN_OK;  // nothing to do; empty buffers may be NULL
+    LFFN_REQUIRE(x != nullptr && out != nullptr, LFFN_ERR_INVALID_ARG, "fwht: NULL buffer");
     return launch_fwht(x, out, N, D, dtype, scale, static_cast<cudaStream_t>(stream));
 }
 
@@ -120,20 +120,20 @@ int lffn_hash_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, in
                   int32_t t_count, int32_t *idx_out, float *w_out, float *z_out, lffn_stream_t stream) {
     int rc = check_hash_desc(desc, t_begin, t_count);
     if (rc != LFFN_OK) return rc;
+    LFFN_REQUIRE(N >= 0, LFFN_ERR_INVALID_ARG, "hash_fwd: N = %lld", (long long)N);
+    if (N == 0) return LFFN_OK;  // nothing to do; empty buffers may be NULL
     LFFN_REQUIRE(x != nullptr, LFFN_ERR_INVALID_ARG, "hash_fwd: x is NULL");
     LFFN_REQUIRE((idx_out != nullptr) == (w_out != nullptr) && (idx_out != nullptr || z_out != nullptr),
                  LFFN_ERR_INVALID_ARG, "hash_fwd: give idx_out and w_out together, or z_out alone");
-    LFFN_REQUIRE(N >= 0, LFFN_ERR_INVALID_ARG, "hash_fwd: N = %lld", (long long)N);
-    if (N == 0) return LFFN_OK;
     return launch_hash_fwd(*desc, x, x_dtype, N, t_begin, t_count, idx_out, w_out, z_out,
                            static_cast<cudaStream_t>(stream));
 }
 
 int lffn_code_weights(const float *z, int64_t N, int32_t T, int32_t k, int32_t bit_order, int32_t weight_mode,
                       float tau, int32_t add_offsets, int32_t *idx_out, float *w_out, lffn_stream_t stream) {
-    LFFN_REQUIRE(z != nullptr && idx_out != nullptr && w_out != nullptr, LFFN_ERR_INVALID_ARG,
-                 "code_weights: NULL buffer");
     LFFN_REQUIRE(N >= 0 && T >= 1, LFFN_ERR_INVALID_ARG, "code_weights: bad sizes");
+    LFFN_REQUIRE(N == 0 || (z != nullptr && idx_out != nullptr && w_out != nullptr), LFFN_ERR_INVALID_ARG,
+                 "code_weights: NULL buffer");
     LFFN_REQUIRE(k >= 1 && k <= 16, LFFN_ERR_UNSUPPORTED, "code_weights: k = %d outside [1, 16]", k);
     LFFN_REQUIRE(bit_order == LFFN_BIT_MSB_FIRST || bit_order == LFFN_BIT_LSB_FIRST, LFFN_ERR_INVALID_ARG,
                  "code_weights: bit_order %d", bit_order);
@@ -147,8 +147,9 @@ int lffn_code_weights(const float *z, int64_t N, int32_t T, int32_t k, int32_t b
 
 int lffn_code_weights_bwd(const float *z, const float *dw, int64_t N, int32_t T, int32_t k, int32_t weight_mode,
                           float tau, float *dz, lffn_stream_t stream) {
-    LFFN_REQUIRE(z != nullptr && dw != nullptr && dz != nullptr, LFFN_ERR_INVALID_ARG, "code_weights_bwd: NULL buffer");
     LFFN_REQUIRE(N >= 0 && T >= 1, LFFN_ERR_INVALID_ARG, "code_weights_bwd: bad sizes");
+    LFFN_REQUIRE(N == 0 || (z != nullptr && dw != nullptr && dz != nullptr), LFFN_ERR_INVALID_ARG,
+                 "code_weights_bwd: NULL buffer");
     LFFN_REQUIRE(k >= 1 && k <= 16, LFFN_ERR_UNSUPPORTED, "code_weights_bwd: k = %d outside [1, 16]", k);
     LFFN_REQUIRE(weight_mode >= LFFN_WEIGHT_SCORE && weight_mode <= LFFN_WEIGHT_SOFT_FLIP, LFFN_ERR_INVALID_ARG,
                  "code_weights_bwd: weight_mode %d", weight_mode);
@@ -162,13 +163,13 @@ int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int3
                     lffn_stream_t stream) {
     int rc = check_gather(N, I, S, d, table_dtype);
     if (rc != LFFN_OK) return rc;
-    LFFN_REQUIRE(tables != nullptr && out != nullptr && (I == 0 || (idx != nullptr && w != nullptr)),
-                 LFFN_ERR_INVALID_ARG, "gather_fwd: NULL buffer");
     LFFN_REQUIRE(out_dtype == LFFN_F32 || out_dtype == LFFN_BF16, LFFN_ERR_INVALID_ARG, "gather_fwd: out dtype %d",
                  out_dtype);
+    if (N == 0) return LFFN_OK;  // nothing to do; empty buffers may be NULL
+    LFFN_REQUIRE(tables != nullptr && out != nullptr && (I == 0 || (idx != nullptr && w != nullptr)),
+                 LFFN_ERR_INVALID_ARG, "gather_fwd: NULL buffer");
     LFFN_REQUIRE(aligned16(tables) && aligned16(out), LFFN_ERR_INVALID_ARG,
                  "gather_fwd: tables and out must be 16-byte aligned");
-    if (N == 0) return LFFN_OK;
     return launch_gather_fwd(idx, w, tables, table_dtype, out, out_dtype, N, I, S, d, bias,
                              static_cast<cudaStream_t>(stream));
 }
@@ -177,11 +178,11 @@ int lffn_gather_bwd_weights(const int32_t *idx, const float *dy, const void *tab
                             int64_t N, int32_t I, int64_t S, int32_t d, lffn_stream_t stream) {
     int rc = check_gather(N, I, S, d, table_dtype);
     if (rc != LFFN_OK) return rc;
+    if (N == 0 || I == 0) return LFFN_OK;  // nothing to do; empty buffers may be NULL
     LFFN_REQUIRE(idx != nullptr && dy != nullptr && tables != nullptr && dw != nullptr, LFFN_ERR_INVALID_ARG,
                  "gather_bwd_weights: NULL buffer");
     LFFN_REQUIRE(aligned16(tables) && aligned16(dy), LFFN_ERR_INVALID_ARG,
                  "gather_bwd_weights: tables and dy must be 16-byte aligned");
-    if (N == 0 || I == 0) return LFFN_OK;
     return launch_gather_bwd_weights(idx, dy, tables, table_dtype, dw, N, I, S, d, static_cast<cudaStream_t>(stream));
 }
 

@@ -44,6 +44,7 @@ def test_argument_errors_are_reported_not_raised_by_cuda():
     lib = L.lib()
     rc = lib.lffn_gather_fwd(None, None, None, 0, None, 0, 4, 2, 8, 64, None, None)
     assert rc == -1 and b"NULL" in lib.lffn_last_error_string()
+    assert lib.lffn_gather_fwd(None, None, None, 0, None, 0, 0, 2, 8, 64, None, None) == 0  # no tokens: nothing to do
     buf = (C.c_float * 64)()
     p = C.cast(buf, C.c_void_p)
     rc = lib.lffn_gather_fwd(p, p, p, 0, p, 0, 4, 2, 8, 6, None, None)  # d not a multiple of 4

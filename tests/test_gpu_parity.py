@@ -630,11 +630,12 @@ def test_module_bf16_tables_and_leading_dims(dev):
         u = mod.LayerNorm(x.reshape(-1, 768))
         idx, w = mod.hash(u)
     assert y.shape == (2, 3, 5, 768) and y.dtype == torch.bfloat16
-    ref = O.gather(t2n(idx), t2n(w), t2n(mod.tables.reshape(-1, 768)), bias=t2n(mod.bias), out_bf16=True)
+    ref = O.gather(t2n(idx), t2n(w), t2n(mod.tables.detach().reshape(-1, 768)), bias=t2n(mod.bias.detach()),
+                   out_bf16=True)
     np.testing.assert_array_equal(t2n(y.reshape(-1, 768)), ref)
     # codes from the oracle's projection of the same layer-normed input
     p = mod.hash.projection
-    z_ref = O.project(t2n(u), t2n(p.weight), 64 * 8, had_scale=float(np.float32(p.had_scale)), mix_a=1.0, mix_b=0.0,
-                      bias=t2n(p.bias))
+    z_ref = O.project(t2n(u), t2n(p.weight.detach()), 64 * 8, had_scale=float(np.float32(p.had_scale)), mix_a=1.0,
+                      mix_b=0.0, bias=t2n(p.bias.detach()))
     idx_ref, _ = O.code_weights(z_ref, 64, 8)
     np.testing.assert_array_equal(t2n(idx), idx_ref)
