@@ -357,6 +357,92 @@ def run_table_sharded(args, rank, world, local):
     }
 
 
+def run_train_gather(args, rank, world, local):
+    """BASELINE config 4: training-mode weighted gather-add, forward and backward, fp32: N=16384 tokens, d=768,
+    T=512, k=8, m=k+1 soft-flip candidates per (token, table) (tau=0.5), upstream gradient dy ~ N(0,1).
+    One step = candidates/weights (hash kernel) + gather forward + gradient of the weights + gradient of the
+    tables (sorted, deterministic)."""
+    from lookupffn_b200 import _lib as L
+    from lookupffn_b200 import ops
+
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    lib = L.lib()
+    N, d, T, k = (args.tokens or 16384), 768, 512, 8
+    m, rows, D = k + 1, 1 << k, 1024
+    R = -(-T * k // D)
+    g = torch.Generator(device=device).manual_seed(4321 + rank)
+    x = torch.randn(N, d, generator=g, device=device)
+    signs = (2 * torch.randint(0, 2, (R, 2, D, 1, 1), generator=g, device=device) - 1).float()
+    tables = 0.02 * torch.randn(T * rows, d, generator=g, device=device)
+    dy = torch.randn(N, d, generator=g, device=device)
+    desc = ops.make_hash_desc(d, signs, None, T, k, had_scale=1.0 / 32, mix_a=1.0, mix_b=0.0,
+                              weight_mode=L.WEIGHT_SOFT_FLIP, tau=0.5)
+    I = T * m
+    idx = torch.empty(N, I, dtype=torch.int32, device=device)
+    w = torch.empty(N, I, device=device)
+    y = torch.empty(N, d, device=device)
+    dw = torch.empty(N, I, device=device)
+    dt = torch.empty(T * rows, d, device=device)
+    nbytes = lib.lffn_gather_bwd_tables_sorted_scratch_bytes(N, T, m, rows)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream(device)
+    sp = C.c_void_p(stream.cuda_stream)
+    names = ["hash_soft_flip", "gather_fwd", "grad_weights", "grad_tables_sorted"]
+
+    def step(ev=None):
+        calls = [
+            lambda: lib.lffn_hash_fwd(C.byref(desc), L.ptr(x), 0, N, 0, T, L.ptr(idx), L.ptr(w), None, sp),
+            lambda: lib.lffn_gather_fwd(L.ptr(idx), L.ptr(w), L.ptr(tables), 0, L.ptr(y), 0, N, I, T * rows, d, None, sp),
+            lambda: lib.lffn_gather_bwd_weights(L.ptr(idx), L.ptr(dy), L.ptr(tables), 0, L.ptr(dw), N, I, T * rows, d, sp),
+            lambda: lib.lffn_gather_bwd_tables_sorted(L.ptr(idx), L.ptr(w), L.ptr(dy), L.ptr(dt), N, T, m, rows, d,
+                                                      L.ptr(scratch), nbytes, sp),
+        ]
+        for i, c in enumerate(calls):
+            if ev is not None:
+                ev[i].record(stream)
+            L.check(c())
+        if ev is not None:
+            ev[4].record(stream)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(local))
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    for s_ in range(args.steps):
+        step(events[s_])
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    clocks = sampler.result()
+    elapsed_ms = events[0][0].elapsed_time(events[-1][4])
+    per = {n: statistics.mean(e[i].elapsed_time(e[i + 1]) for e in events) for i, n in enumerate(names)}
+    if world > 1:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        elapsed_ms = float(t[0])
+    if rank != 0:
+        return None
+    logical = N * I * d * 4
+    return {
+        "metric": "lookupffn_gather_forward_backward_throughput", "value": world * N * args.steps / (elapsed_ms * 1e-3),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"c4: training-mode weighted gather-add forward + backward, N={N} tokens per GPU, d={d}, "
+                               f"T={T}, k={k}, m={m} soft-flip candidates (tau 0.5), fp32 tables",
+                   "l2": "inputs larger than L2: tables 403 MB, indices+weights 604 MB"},
+        "kernels_ms": per,
+        "algorithmic_GBps": {n: logical / (per[n] * 1e-3) / 1e9 for n in names[1:]},
+        "gpu_launches": 5 * args.steps, "clocks": clocks, "device_status": L.device_status(device),
+    }
+
+
 def run_encoder(args, rank, world, local):
     """BASELINE config 2: RoBERTa-small prenorm encoder inference with every FFN a LookupFFN (4 layers, hidden
     512, 8 heads, seq 512, batch 32 per GPU, T=256, k=8, fp32 tables, reference BH4 projection).  seq/s."""
@@ -533,7 +619,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c2enc"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c2enc", "c4"])
     ap.add_argument("--projection", default="bh4", choices=["bh4", "sign_hadamard", "dense"],
                     help="projection of the c2enc workload (bh4 = the reference configs)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -565,8 +651,8 @@ def main():
         torch.cuda.set_device(local)
         torch.distributed.init_process_group("nccl", rank=rank, world_size=world,
                                              device_id=torch.device("cuda", local))
-    if args.workload == "c2enc":
-        out = run_encoder(args, rank, world, local)
+    if args.workload in ("c2enc", "c4"):
+        out = run_encoder(args, rank, world, local) if args.workload == "c2enc" else run_train_gather(args, rank, world, local)
         if out is not None:
             print(json.dumps(out), flush=True)
         if world > 1:

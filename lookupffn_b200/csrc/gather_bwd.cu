@@ -46,7 +46,8 @@ template <typename TableT, int VPL, int U, bool FULLV>
 __global__ void __launch_bounds__(LFFN_BWW_THREADS, LFFN_BWW_MINBLOCKS)
     gather_bwd_weights_kernel(const int32_t *__restrict__ idx, const float *__restrict__ dy,
                               const TableT *__restrict__ tables, float *__restrict__ dw, long long N, int I,
-                              long long S, int d, int col0, int accumulate, uint32_t *status) {
+                              long long S, int d, int col0, int accumulate, int i0, int icnt, uint32_t *status) {
+    // i0/icnt: the slice of each token's index list this launch covers (see launch_bww_vpl)
     constexpr int EPV = Elem<TableT>::PER_VEC;
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
@@ -73,12 +74,12 @@ __global__ void __launch_bounds__(LFFN_BWW_THREADS, LFFN_BWW_MINBLOCKS)
                 g[v][4 * q + 3] = t.w;
             }
         }
-        const int32_t *ip = idx + n * I;
-        int next_i = lane < I ? __ldg(ip + lane) : 0;
-        for (int g0 = 0; g0 < I; g0 += 32) {
-            const int cnt = min(32, I - g0);
+        const int32_t *ip = idx + n * I + i0;
+        int next_i = lane < icnt ? __ldg(ip + lane) : 0;
+        for (int g0 = 0; g0 < icnt; g0 += 32) {
+            const int cnt = min(32, icnt - g0);
             const int my_i = next_i;
-            if (g0 + 32 + lane < I) next_i = __ldg(ip + g0 + 32 + lane);
+            if (g0 + 32 + lane < icnt) next_i = __ldg(ip + g0 + 32 + lane);
             // branch-free: rows past the list end or out of range read a substitute row; their sums are discarded
             float p[32];
 #pragma unroll
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(LFFN_BWW_THREADS, LFFN_BWW_MINBLOCKS)
             if (lane < cnt) {
                 const bool in_range = (unsigned long long)(long long)my_i < (unsigned long long)S;
                 const float val = in_range ? p[0] : 0.f;
-                float *o = dw + n * I + g0 + lane;
+                float *o = dw + n * I + i0 + g0 + lane;
                 *o = accumulate ? (*o + val) : val;
             }
         }
@@ -148,9 +149,23 @@ static int launch_bww_vpl(const int32_t *idx, const float *dy, const void *table
     long long grid = (long long)num_sms() * per_sm;
     if (grid > want) grid = want;
     if (grid < 1) grid = 1;
-    kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, dy, static_cast<const TableT *>(tables), dw, N, I, S, d, col0,
-                                             col0 > 0 ? 1 : 0, status_word());
-    LFFN_CHECK_CUDA(cudaGetLastError());
+    // Long lists over table sets beyond L2 are consumed in slices, one launch per slice over all tokens, which
+    // keeps the warps aligned along the list and each launch's rows L2-resident (same reason as in the forward
+    // gather); every dw element belongs to exactly one slice, so nothing else changes.
+    int slices = 1;
+    if (I >= 512) {
+        const double table_bytes = (double)S * d * sizeof(TableT);
+        if (table_bytes > 256e6) slices = (int)(table_bytes / 32e6);
+        if (slices > I / 128) slices = I / 128;
+        if (slices < 1) slices = 1;
+    }
+    const int per = slices == 1 ? I : ((I + slices - 1) / slices + 31) / 32 * 32;
+    for (int i0 = 0; i0 < I; i0 += per) {
+        const int icnt = I - i0 < per ? I - i0 : per;
+        kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, dy, static_cast<const TableT *>(tables), dw, N, I, S, d, col0,
+                                                 col0 > 0 ? 1 : 0, i0, icnt, status_word());
+        LFFN_CHECK_CUDA(cudaGetLastError());
+    }
     return LFFN_OK;
 }
 

@@ -639,3 +639,24 @@ def test_module_bf16_tables_and_leading_dims(dev):
                       mix_b=0.0, bias=t2n(p.bias.detach()))
     idx_ref, _ = O.code_weights(z_ref, 64, 8)
     np.testing.assert_array_equal(t2n(idx), idx_ref)
+
+
+def test_sliced_index_lists_are_bit_exact(dev):
+    """A table set beyond 256 MB with a long index list takes the sliced path of the forward gather and of the
+    weight gradient (one launch per slice of the list, fp32 partial sums resumed): results must not change."""
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(11)
+    N, T, m, rows, d = 24, 176, 9, 512, 768          # 176 * 512 rows * 768 * 4 B = 277 MB, I = 1584
+    S, I = T * rows, T * m
+    idx = (rng.randint(0, rows, size=(N, T, m)) + (np.arange(T) * rows)[None, :, None]).astype(np.int32).reshape(N, I)
+    w = rng.randn(N, I).astype(np.float32)
+    dy = rng.randn(N, d).astype(np.float32)
+    bias = rng.randn(d).astype(np.float32)
+    tab = torch.empty(S, d, device=dev).normal_(0, 0.02, generator=torch.Generator(device=dev).manual_seed(3))
+    ti, tw, tg, tb = (torch.from_numpy(a).to(dev) for a in (idx, w, dy, bias))
+    y = ops.weighted_vector_gather_add(ti, tab, tw, bias=tb)
+    dw = ops.indexed_inner_product(ti, tg, tab)
+    tabn = t2n(tab)
+    np.testing.assert_array_equal(t2n(y), O.gather(idx, w, tabn, bias=bias))
+    assert rel_err(t2n(dw), O.gather_bwd_weights(idx, dy, tabn)) < 1e-4
