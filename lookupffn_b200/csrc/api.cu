@@ -226,6 +226,7 @@ int lffn_layer_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, i
                            (int64_t)t_count << desc->k, d_out, bias, stream);
 }
 
+constexpr int HOST_LANES = 3;  // streams alternating over token chunks in lffn_layer_fwd_host
 static size_t esize(int dtype) { return dtype == LFFN_BF16 ? 2 : 4; }
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -236,10 +237,10 @@ size_t lffn_layer_fwd_host_ws_bytes(const lffn_hash_desc *desc, int32_t x_dtype,
     const size_t per_lane = up256((size_t)chunk_tokens * desc->d_in * esize(x_dtype)) +
                             up256((size_t)chunk_tokens * d_out * esize(out_dtype)) +
                             2 * up256((size_t)chunk_tokens * desc->T * m * 4);
-    return 2 * per_lane;
+    return HOST_LANES * per_lane;
 }
 
-// Two lanes (streams) alternate over token chunks; within a lane copy-in, the two kernels and
+// HOST_LANES lanes (streams) take the token chunks in turn; within a lane copy-in, the two kernels and
 // copy-out are stream-ordered, and the lanes overlap each other's copies with kernels.
 int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t x_dtype, int64_t N,
                         const void *tables, int32_t table_dtype, int32_t d_out, const float *bias, void *out_host,
@@ -255,8 +256,8 @@ int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t 
     if (N == 0) return LFFN_OK;
 
     struct Lanes {
-        cudaStream_t s[2] = {nullptr, nullptr};
-        cudaEvent_t done[2] = {nullptr, nullptr};
+        cudaStream_t s[HOST_LANES] = {};
+        cudaEvent_t done[HOST_LANES] = {};
         cudaEvent_t start = nullptr;
     };
     static Lanes lanes[MAX_DEV];
@@ -267,7 +268,7 @@ int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t 
     std::lock_guard<std::mutex> lock(mu);  // one host-buffer call at a time per process: the lanes are shared
     Lanes &L = lanes[dev];
     if (L.s[0] == nullptr) {
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < HOST_LANES; i++) {
             LFFN_CHECK_CUDA(cudaStreamCreateWithFlags(&L.s[i], cudaStreamNonBlocking));
             LFFN_CHECK_CUDA(cudaEventCreateWithFlags(&L.done[i], cudaEventDisableTiming));
         }
@@ -280,10 +281,10 @@ int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t 
     const size_t ob = up256((size_t)chunk_tokens * d_out * esize(out_dtype));
     const size_t ib = up256((size_t)chunk_tokens * desc->T * m * 4);
     const size_t per_lane = xb + ob + 2 * ib;
-    for (int i = 0; i < 2; i++) LFFN_CHECK_CUDA(cudaStreamWaitEvent(L.s[i], L.start, 0));
+    for (int i = 0; i < HOST_LANES; i++) LFFN_CHECK_CUDA(cudaStreamWaitEvent(L.s[i], L.start, 0));
     int64_t c = 0;
     for (int64_t n0 = 0; n0 < N; n0 += chunk_tokens, c++) {
-        const int lane = (int)(c & 1);
+        const int lane = (int)(c % HOST_LANES);
         const int64_t nt = (N - n0 < chunk_tokens) ? (N - n0) : chunk_tokens;
         char *base = static_cast<char *>(ws) + lane * per_lane;
         void *xd = base;
@@ -298,7 +299,7 @@ int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t 
         if (rc != LFFN_OK) return rc;
         LFFN_CHECK_CUDA(cudaMemcpyAsync(os, od, (size_t)nt * d_out * esize(out_dtype), cudaMemcpyDeviceToHost, L.s[lane]));
     }
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < HOST_LANES; i++) {
         LFFN_CHECK_CUDA(cudaEventRecord(L.done[i], L.s[i]));
         LFFN_CHECK_CUDA(cudaStreamWaitEvent(user, L.done[i], 0));
     }
