@@ -35,7 +35,11 @@ WORKLOADS = {
     "c1": dict(N=4096, d_in=512, d_out=512, T=128, k=8, dtype="f32", weight_mode="ones", bit_order="lsb"),
     "c2": dict(N=16384, d_in=512, d_out=512, T=256, k=8, dtype="f32", weight_mode="score", bit_order="msb"),
     "c3": dict(N=65536, d_in=768, d_out=768, T=512, k=8, dtype="bf16", weight_mode="score", bit_order="msb"),
+    # config 5 (table-sharded sweep): T here = tables PER GPU = (1 GB / (2^k * 1024 * 2 B)) / 8
+    "c5k6": dict(N=262144, d_in=1024, d_out=1024, T=1024, k=6, dtype="bf16", weight_mode="score", bit_order="msb"),
     "c5k8": dict(N=262144, d_in=1024, d_out=1024, T=256, k=8, dtype="bf16", weight_mode="score", bit_order="msb"),
+    "c5k10": dict(N=262144, d_in=1024, d_out=1024, T=64, k=10, dtype="bf16", weight_mode="score", bit_order="msb"),
+    "c5k12": dict(N=262144, d_in=1024, d_out=1024, T=16, k=12, dtype="bf16", weight_mode="score", bit_order="msb"),
 }
 # DRAM bytes per gather launch from one ncu capture (dram__bytes_read.sum + dram__bytes_write.sum).
 # c3: captured at 16384 tokens (1.513 GB: tables re-fetched once per wave of resident warps, plus
@@ -134,6 +138,21 @@ def make_inputs(w, device, seed):
     gx = torch.Generator(device=device).manual_seed(1000 + seed)
     x = torch.randn(w["N"], w["d_in"], generator=gx, device=device).to(dt)
     return x, tables, signs, bias, D, R
+
+
+def layer_config(args, w, world):
+    """The `config` object of the JSON line; identical for this arm and for the reference arm."""
+    eb = 2 if w["dtype"] == "bf16" else 4
+    D = padded_dim(w["d_in"])
+    R = max(1, -(-w["T"] * w["k"] // D))
+    N, T = w["N"], w["T"]
+    return {"workload": f"{args.workload}: LookupFFN layer forward, N={N} tokens per GPU, d={w['d_in']}->D={D}, "
+                        f"T={T}, k={w['k']}, d_out={w['d_out']}, {w['dtype']} x/tables/y, fp32 accumulate",
+            "projection": f"sign-diagonal Hadamard, R={R} rotations x 2 stages, normalised",
+            "weights": w["weight_mode"], "bit_order": w["bit_order"],
+            "sharding": f"tokens x{world}, tables replicated",
+            "l2": "inputs larger than L2: tables %.0f MB + idx/w %.0f MB + x/y %.0f MB per step" % (
+                (T << w["k"]) * w["d_out"] * eb / 1e6, N * T * 8 / 1e6, 2 * N * w["d_in"] * eb / 1e6)}
 
 
 def run_ours(args, rank, world, local):
@@ -248,12 +267,7 @@ def run_ours(args, rank, world, local):
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": w["dtype"], "data": "synthetic",
-        "config": {"workload": f"{args.workload}: LookupFFN layer forward, N={N} tokens per GPU, d={w['d_in']}->D={D}, "
-                               f"T={T}, k={k}, d_out={w['d_out']}, {w['dtype']} x/tables/y, fp32 accumulate",
-                   "projection": f"sign-diagonal Hadamard, R={R} rotations x 2 stages, normalised",
-                   "weights": w["weight_mode"], "bit_order": w["bit_order"], "sharding": f"tokens x{world}, tables replicated",
-                   "l2": "inputs larger than L2: tables %.0f MB + idx/w %.0f MB + x/y %.0f MB per step" % (
-                       tables.numel() * eb / 1e6, N * T * 8 / 1e6, 2 * N * w["d_in"] * eb / 1e6)},
+        "config": layer_config(args, w, world),
         "kernels_ms": {"hash_fwd": hash_ms, "gather_fwd": gather_ms},
         "roofline": {"bound": "hbm", "kernel": "gather_fwd_kernel", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
@@ -592,8 +606,9 @@ def cpu_path(args, budget_s):
 def run_reference(args, rank, world):
     if rank != 0:
         return None
-    w = WORKLOADS[args.workload]
-    D = padded_dim(w["d_in"])
+    w = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        w["N"] = args.tokens
     per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
     base = None
     vals = []
@@ -607,8 +622,10 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "lookupffn_layer_forward_throughput", "value": v, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": args.cpu_tokens / v * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: LookupFFN layer forward, CPU path on host cores, bounded sample of "
-                               f"{args.cpu_tokens} tokens per step, d={w['d_in']}->D={D}, T={w['T']}, k={w['k']}"},
+        "config": dict(layer_config(args, w, world),
+                       reference_arm=f"the reference's CPU path on {base['cores']} host cores; each step is a bounded sample "
+                                     f"of {args.cpu_tokens} tokens of this workload with fp32 tables (its CPU kernels are "
+                                     "fp32 only)"),
         "cpu_baseline": base,
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
