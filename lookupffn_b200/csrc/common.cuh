@@ -58,6 +58,24 @@ int launch_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const fl
 #ifdef __CUDACC__
 
 // 16-byte read-only load that does not allocate in L1: table rows are touched once per SM.
+// Streaming operands (index and weight lists, read once) are loaded with an L2 evict-first policy so that
+// they do not push table rows out of L2.
+__device__ __forceinline__ unsigned long long policy_evict_first() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ int ld_stream_i32(const int *p, unsigned long long pol) {
+    int v;
+    asm volatile("ld.global.nc.L2::cache_hint.s32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol));
+    return v;
+}
+__device__ __forceinline__ float ld_stream_f32(const float *p, unsigned long long pol) {
+    float v;
+    asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol));
+    return v;
+}
+
 __device__ __forceinline__ uint4 ld_row16(const void *p) {
     uint4 v;
 #ifdef LFFN_ROW_LOAD_L1_ALLOCATE

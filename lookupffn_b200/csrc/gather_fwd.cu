@@ -95,16 +95,17 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
         }
         int my_i = 0;
         float my_w = 0.f;
+        const unsigned long long pol_stream = policy_evict_first();
         if (lane < In) {
-            my_i = __ldg(ip + lane);
-            my_w = __ldg(wp + lane);
+            my_i = ld_stream_i32(ip + lane, pol_stream);
+            my_w = ld_stream_f32(wp + lane, pol_stream);
         }
         for (int g0 = 0; g0 < In; g0 += 32) {
             const int cur_i = my_i;
             const float cur_w = my_w;
             if (g0 + 32 + lane < In) {  // prefetch the next 32 (idx, w) pairs
-                my_i = __ldg(ip + g0 + 32 + lane);
-                my_w = __ldg(wp + g0 + 32 + lane);
+                my_i = ld_stream_i32(ip + g0 + 32 + lane, pol_stream);
+                my_w = ld_stream_f32(wp + g0 + 32 + lane, pol_stream);
             }
             const int cnt = min(32, In - g0);
             // The loop body is branch-free: an entry past the end of the list, or with an index outside
