@@ -160,10 +160,12 @@ static int launch_bww_vpl(const int32_t *idx, const float *dy, const void *table
         if (slices < 1) slices = 1;
     }
     const int per = slices == 1 ? I : ((I + slices - 1) / slices + 31) / 32 * 32;
+    uint32_t *status = status_word();
+    LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
     for (int i0 = 0; i0 < I; i0 += per) {
         const int icnt = I - i0 < per ? I - i0 : per;
         kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, dy, static_cast<const TableT *>(tables), dw, N, I, S, d, col0,
-                                                 col0 > 0 ? 1 : 0, i0, icnt, status_word());
+                                                 col0 > 0 ? 1 : 0, i0, icnt, status);
         LFFN_CHECK_CUDA(cudaGetLastError());
     }
     return LFFN_OK;
@@ -260,7 +262,9 @@ static int launch_red_vpl(const int32_t *idx, const float *w, const float *dy, f
     long long grid = (long long)num_sms() * per_sm;
     if (grid > want) grid = want;
     if (grid < 1) grid = 1;
-    kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, w, dy, dtables, N, I, S, d, col0, status_word());
+    uint32_t *status = status_word();
+    LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
+    kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, w, dy, dtables, N, I, S, d, col0, status);
     LFFN_CHECK_CUDA(cudaGetLastError());
     return LFFN_OK;
 }
@@ -428,8 +432,9 @@ int launch_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const fl
         LFFN_CHECK_CUDA(cudaFuncSetAttribute(sort_table_entries_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem));
     int grid = T < 4 * num_sms() ? T : 4 * num_sms();
-    sort_table_entries_kernel<<<grid, SORT_THREADS, smem, st>>>(idx, w, N, T, m, rows, s.seg, s.ent_n, s.ent_w,
-                                                                status_word());
+    uint32_t *status = status_word();
+    LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
+    sort_table_entries_kernel<<<grid, SORT_THREADS, smem, st>>>(idx, w, N, T, m, rows, s.seg, s.ent_n, s.ent_w, status);
     LFFN_CHECK_CUDA(cudaGetLastError());
     return launch_gather_segmented(s.ent_n, s.ent_w, dy, dtables, (int64_t)T * rows, s.seg, N, d, st);
 }

@@ -213,11 +213,13 @@ static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, 
         if (slices < 1) slices = 1;
     }
     const int per = slices == 1 ? I : ((I + slices - 1) / slices + 31) / 32 * 32;
+    uint32_t *status = status_word();
+    LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
     for (int i0 = 0; i0 == 0 || i0 < I; i0 += per) {
         const int icnt = I - i0 < per ? I - i0 : per;
         kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, w, static_cast<const TableT *>(tables), static_cast<OutT *>(out), N,
                                                  I, S, d, col0, bias, seg, i0, icnt, i0 > 0 ? 1 : 0,
-                                                 i0 + icnt >= I ? 1 : 0, status_word());
+                                                 i0 + icnt >= I ? 1 : 0, status);
         LFFN_CHECK_CUDA(cudaGetLastError());
         if (I == 0) break;
     }

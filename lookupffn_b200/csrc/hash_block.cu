@@ -78,6 +78,67 @@ __device__ __forceinline__ void fwht_tile(float *Y, int D, float scale, int warp
     }
 }
 
+// ---- tile phases shared by the two kernels (THREADS threads, NW = THREADS / 32 warps) ---------------------------------
+// Start of a rotation: keep the last coordinates of the previous rotation (for a table that straddles the
+// boundary), then load the tile transposed and zero-padded.  The caller synchronises afterwards.
+template <typename XT, int THREADS>
+__device__ __forceinline__ void tile_begin_rotation(float *Y, float *carry, const HashArgs &a, long long n0, int mt, int D) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __syncthreads();
+    for (int i = tid; i < HB_CARRY * HB_M; i += THREADS) {
+        const int e = i / HB_M, mm = i % HB_M;
+        carry[e * HB_MP + mm] = Y[(D - HB_CARRY + e) * HB_MP + mm];
+    }
+    __syncthreads();
+    for (int mm = warp; mm < HB_M; mm += THREADS / 32) {
+        const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
+        for (int e = lane; e < D; e += 32)
+            Y[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+    }
+}
+
+// End of a rotation: z = fl(fl(mix_a * y) + fl(mix_b * u)) + bias in place, then codes and weights of the
+// tables that end inside this rotation (lane = token, warps stride over tables).
+template <typename XT, int THREADS>
+__device__ __forceinline__ void tile_end_rotation(float *Y, const float *carry, const HashArgs &a, long long n0, int mt,
+                                                  int D, int r) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int k = a.k;
+    const int m = a.weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
+    const long long g_lo = (long long)a.t_begin * k, g_hi = (long long)(a.t_begin + a.t_count) * k;
+    const long long out_pitch = (long long)a.t_count * m;
+    const long long c_lo = (long long)r * D, c_hi = c_lo + D;
+    for (int mm = warp; mm < HB_M; mm += THREADS / 32) {
+        const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
+        for (int e = lane; e < D; e += 32) {
+            const float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+            const long long g = c_lo + e;
+            float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + mm]), __fmul_rn(a.mix_b, u));
+            if (a.bias != nullptr && g < (long long)a.T * k) z = __fadd_rn(z, __ldg(a.bias + g));
+            Y[e * HB_MP + mm] = z;
+            if (a.z_out != nullptr && mm < mt && g >= g_lo && g < g_hi)
+                a.z_out[(n0 + mm) * (g_hi - g_lo) + (g - g_lo)] = z;
+        }
+    }
+    __syncthreads();
+    long long t_first = c_lo / k;
+    if (t_first < a.t_begin) t_first = a.t_begin;
+    long long t_end = c_hi / k;
+    if (t_end > a.t_begin + a.t_count) t_end = a.t_begin + a.t_count;
+    if (lane < mt && a.idx_out != nullptr) {
+        for (long long t = t_first + warp; t < t_end; t += THREADS / 32) {
+            const int local0 = (int)(t * k - c_lo);
+            auto get = [&](int j) -> float {
+                const int e = local0 + j;
+                return e >= 0 ? Y[e * HB_MP + lane] : carry[(HB_CARRY + e) * HB_MP + lane];
+            };
+            const long long o = (n0 + lane) * out_pitch + (t - a.t_begin) * m;
+            emit_table(get, k, a.bit_order, a.weight_mode, a.tau, (int32_t)((t - a.t_begin) << k), false, 0,
+                       a.idx_out + o, a.w_out + o);
+        }
+    }
+}
+
 template <typename XT>
 __global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, int BS, int transpose_w) {
     extern __shared__ __align__(16) float smem[];
@@ -86,10 +147,6 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, i
     float *Ws = Y + (size_t)D * HB_MP;       // [PC/BS][BS][BS] swizzled
     float *carry = Ws + HB_WFLOATS;          // [HB_CARRY][HB_MP]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int k = a.k;
-    const int m = a.weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
-    const long long g_lo = (long long)a.t_begin * k, g_hi = (long long)(a.t_begin + a.t_count) * k;
-    const long long out_pitch = (long long)a.t_count * m;
     const int PC = min(D, BS <= 64 ? 256 : HB_WFLOATS / BS);  // columns per pass
     const int bs4mask = BS / 4 - 1;
     const long long ntiles = (a.N + HB_M - 1) / HB_M;
@@ -98,19 +155,7 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, i
         const long long n0 = tile * HB_M;
         const int mt = (int)min((long long)HB_M, a.N - n0);  // valid tokens in the tile
         for (int r = a.r_lo; r <= a.r_hi; r++) {
-            __syncthreads();
-            // keep the last coordinates of the previous rotation for a straddling table
-            for (int i = tid; i < HB_CARRY * HB_M; i += HB_THREADS) {
-                const int e = i / HB_M, mm = i % HB_M;
-                carry[e * HB_MP + mm] = Y[(D - HB_CARRY + e) * HB_MP + mm];
-            }
-            __syncthreads();
-            // load the tile, transposed and zero-padded
-            for (int mm = warp; mm < HB_M; mm += HB_THREADS / 32) {
-                const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
-                for (int e = lane; e < D; e += 32)
-                    Y[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
-            }
+            tile_begin_rotation<XT, HB_THREADS>(Y, carry, a, n0, mt, D);
             __syncthreads();
             for (int s = 0; s < a.S; s++) {
                 const float *wstage = a.w + ((long long)r * a.S + s) * D * BS;
@@ -162,38 +207,7 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, i
                 }
                 fwht_tile(Y, D, a.had_scale, warp, lane);
             }
-            // mix + bias:  z = fl(fl(mix_a * y) + fl(mix_b * u)) + bias
-            const long long c_lo = (long long)r * D, c_hi = c_lo + D;
-            for (int mm = warp; mm < HB_M; mm += HB_THREADS / 32) {
-                const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
-                for (int e = lane; e < D; e += 32) {
-                    const float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
-                    const long long g = c_lo + e;
-                    float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + mm]), __fmul_rn(a.mix_b, u));
-                    if (a.bias != nullptr && g < (long long)a.T * k) z = __fadd_rn(z, __ldg(a.bias + g));
-                    Y[e * HB_MP + mm] = z;
-                    if (a.z_out != nullptr && mm < mt && g >= g_lo && g < g_hi)
-                        a.z_out[(n0 + mm) * (g_hi - g_lo) + (g - g_lo)] = z;
-                }
-            }
-            __syncthreads();
-            // tables that end inside this rotation; lane = token, warps stride over tables
-            long long t_first = c_lo / k;
-            if (t_first < a.t_begin) t_first = a.t_begin;
-            long long t_end = c_hi / k;
-            if (t_end > a.t_begin + a.t_count) t_end = a.t_begin + a.t_count;
-            if (lane < mt && a.idx_out != nullptr) {
-                for (long long t = t_first + warp; t < t_end; t += HB_THREADS / 32) {
-                    const int local0 = (int)(t * k - c_lo);
-                    auto get = [&](int j) -> float {
-                        const int e = local0 + j;
-                        return e >= 0 ? Y[e * HB_MP + lane] : carry[(HB_CARRY + e) * HB_MP + lane];
-                    };
-                    const long long o = (n0 + lane) * out_pitch + (t - a.t_begin) * m;
-                    emit_table(get, k, a.bit_order, a.weight_mode, a.tau, (int32_t)((t - a.t_begin) << k), false, 0,
-                               a.idx_out + o, a.w_out + o);
-                }
-            }
+            tile_end_rotation<XT, HB_THREADS>(Y, carry, a, n0, mt, D, r);
         }
     }
 }
@@ -237,10 +251,6 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     float *Wb = Y + (size_t)D * HB_MP;            // 2 x HF_CHUNK_FLOATS
     float *carry = Wb + 2 * HF_CHUNK_FLOATS;      // [HB_CARRY][HB_MP]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int k = a.k;
-    const int m = a.weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
-    const long long g_lo = (long long)a.t_begin * k, g_hi = (long long)(a.t_begin + a.t_count) * k;
-    const long long out_pitch = (long long)a.t_count * m;
     const int NB = D / 64;
     const int cps = (D / PC) * (64 / CR);            // chunks per stage: passes x row slices
     const int nrot = a.r_hi - a.r_lo + 1;
@@ -276,17 +286,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
         const long long n0 = tile * HB_M;
         const int mt = (int)min((long long)HB_M, a.N - n0);
         for (int r = a.r_lo; r <= a.r_hi; r++) {
-            __syncthreads();
-            for (int i = tid; i < HB_CARRY * HB_M; i += THREADS) {
-                const int e = i / HB_M, mm = i % HB_M;
-                carry[e * HB_MP + mm] = Y[(D - HB_CARRY + e) * HB_MP + mm];
-            }
-            __syncthreads();
-            for (int mm = warp; mm < HB_M; mm += NW) {
-                const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
-                for (int e = lane; e < D; e += 32)
-                    Y[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
-            }
+            tile_begin_rotation<XT, THREADS>(Y, carry, a, n0, mt, D);
             for (int s = 0; s < a.S; s++) {
                 const int cq = tid % (PC / 4), tq = tid / (PC / 4);   // PC/4 column quads x 4 token octets
                 const int g = cq >> 4, o4 = cq & 15;
@@ -330,36 +330,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                 __syncthreads();
                 fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
             }
-            const long long c_lo = (long long)r * D, c_hi = c_lo + D;
-            for (int mm = warp; mm < HB_M; mm += NW) {
-                const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
-                for (int e = lane; e < D; e += 32) {
-                    const float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
-                    const long long g2 = c_lo + e;
-                    float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + mm]), __fmul_rn(a.mix_b, u));
-                    if (a.bias != nullptr && g2 < (long long)a.T * k) z = __fadd_rn(z, __ldg(a.bias + g2));
-                    Y[e * HB_MP + mm] = z;
-                    if (a.z_out != nullptr && mm < mt && g2 >= g_lo && g2 < g_hi)
-                        a.z_out[(n0 + mm) * (g_hi - g_lo) + (g2 - g_lo)] = z;
-                }
-            }
-            __syncthreads();
-            long long t_first = c_lo / k;
-            if (t_first < a.t_begin) t_first = a.t_begin;
-            long long t_end = c_hi / k;
-            if (t_end > a.t_begin + a.t_count) t_end = a.t_begin + a.t_count;
-            if (lane < mt && a.idx_out != nullptr) {
-                for (long long t = t_first + warp; t < t_end; t += NW) {
-                    const int local0 = (int)(t * k - c_lo);
-                    auto get = [&](int j) -> float {
-                        const int e = local0 + j;
-                        return e >= 0 ? Y[e * HB_MP + lane] : carry[(HB_CARRY + e) * HB_MP + lane];
-                    };
-                    const long long o = (n0 + lane) * out_pitch + (t - a.t_begin) * m;
-                    emit_table(get, k, a.bit_order, a.weight_mode, a.tau, (int32_t)((t - a.t_begin) << k), false, 0,
-                               a.idx_out + o, a.w_out + o);
-                }
-            }
+            tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r);
         }
     }
     cp_async_wait_all();
