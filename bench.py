@@ -257,6 +257,11 @@ def run_ours(args, rank, world, local):
 
     if rank != 0:
         return None
+    parity = None
+    if world == 1 and not args.no_cpu_baseline and not args.tokens:
+        step()
+        torch.cuda.synchronize()
+        parity = parity_sample(args, x, signs, tables, idx, wgt, y, float(1.0 / np.sqrt(D)))
     eb = 2 if w["dtype"] == "bf16" else 4
     alg = algorithmic_bytes_per_token(w)
     peak, peak_kind = load_peaks()
@@ -277,7 +282,7 @@ def run_ours(args, rank, world, local):
                 "api": "lffn_layer_fwd_host (pinned host x -> pinned host y)", "chunk_tokens": chunk,
                 "matches_device_path": e2e_ok},
         "gpu_launches": 2 * args.steps + 2 * chunks * args.steps,
-        "clocks": clocks, "device_status": status,
+        "clocks": clocks, "device_status": status, "parity_sample": parity,
     }
     return out
 
@@ -551,6 +556,46 @@ def load_ref_modules():
         spec.loader.exec_module(mod)
         mods[name] = mod
     return mods
+
+
+def parity_sample(args, x, signs, tables, idx, wgt, y, hs):
+    """Part of the CPU-baseline leg: the oracle re-computes the first `cpu_tokens` tokens of the benchmark's own
+    inputs and the GPU results for those tokens are compared with it.  Codes are expected to agree bit for bit;
+    any mismatch is counted, with the share whose projected coordinate is below 1e-6 in magnitude."""
+    from oracle import oracle as O
+
+    w = WORKLOADS[args.workload]
+    n = min(args.cpu_tokens, x.shape[0])
+    T, k = w["T"], w["k"]
+    bf16 = x.dtype == torch.bfloat16
+
+    def host(t):
+        t = t[:n] if t.shape[0] == x.shape[0] else t
+        if t.dtype == torch.bfloat16:
+            return t.view(torch.int16).cpu().numpy().view(np.uint16)
+        return t.cpu().numpy()
+
+    xs = host(x)
+    x32 = O.bf16_bits_to_f32(xs) if bf16 else xs
+    z = O.project(x32, signs.cpu().numpy(), T * k, had_scale=hs, mix_a=1.0, mix_b=0.0)
+    wm = {"score": O.WEIGHT_SCORE, "ones": O.WEIGHT_ONES}[w["weight_mode"]]
+    bo = {"msb": O.MSB_FIRST, "lsb": O.LSB_FIRST}[w["bit_order"]]
+    idx_ref, w_ref = O.code_weights(z, T, k, bit_order=bo, weight_mode=wm)
+    idx_gpu, w_gpu = host(idx), host(wgt)
+    bad = idx_gpu != idx_ref
+    tiny = 0
+    if bad.any():
+        zmin = np.abs(z.reshape(n, T, k)).min(-1)
+        tiny = int((zmin[bad] < 1e-6).sum())
+    y_ref = O.gather(idx_ref, w_gpu, host(tables), out_bf16=bf16)
+    y_gpu = host(y)
+    if bf16:
+        y_ref, y_gpu = O.bf16_bits_to_f32(y_ref), O.bf16_bits_to_f32(y_gpu)
+    return {"tokens": int(n), "hash_codes_checked": int(idx_ref.size), "hash_code_mismatches": int(bad.sum()),
+            "mismatches_with_abs_v_below_1e-6": tiny,
+            "weights_max_rel_err": float(np.abs(w_gpu - w_ref).max() / np.abs(w_ref).max()),
+            "output_max_rel_err": float(np.abs(y_gpu - y_ref).max() / np.abs(y_ref).max()),
+            "outputs_bit_identical_given_gpu_weights": bool(np.array_equal(y_gpu, y_ref))}
 
 
 def cpu_path(args, budget_s):
