@@ -314,7 +314,13 @@ def run_table_sharded(args, rank, world, local):
     desc = ops.make_hash_desc(d_in, signs, None, T, k, had_scale=float(1.0 / np.sqrt(D)), mix_a=1.0, mix_b=0.0)
     chunk = args.rs_chunk
 
+    peers = None
+    if args.rs != "nccl":
+        peers = sharded.PeerOutput(N // world, d_out, device, mode="add" if args.rs == "fused" else "store")
+
     def step():
+        if peers is not None:  # gather and reduce-scatter in one kernel over peer-mapped buffers
+            return sharded.lookup_forward_table_sharded_fused(x, desc, tables, t_begin, t_count, peers, bias=bias)
         return sharded.lookup_forward_table_sharded(x, desc, tables, t_begin, t_count, bias=bias,
                                                     chunk_tokens=chunk, out_dtype=torch.float32)[0]
 
@@ -366,7 +372,8 @@ def run_table_sharded(args, rank, world, local):
         "dtype": w["dtype"], "data": "synthetic",
         "config": {"workload": f"{args.workload}, tables sharded: N={N} tokens on every GPU, d={d_in}, T={t_count} "
                                f"tables per GPU ({T} in the layer), k={k}, {w['dtype']} x/tables, fp32 partial sums, "
-                               f"NCCL reduce-scatter in {chunks} chunks",
+                               + (f"NCCL reduce-scatter in {chunks} chunks" if peers is None else
+                                  f"exchange fused into the gather kernel (peer {peers.mode} over NVLink)"),
                    "sharding": f"tables x{world}", "l2": "inputs larger than L2"},
         "table_rows_per_s": world * N * t_count * args.steps / (elapsed_ms * 1e-3),
         "rs_bytes_per_step_per_gpu": N * d_out * 4,
@@ -692,6 +699,8 @@ def main():
                     help="tokens: each rank its own tokens, tables replicated (default); tables: tables split by T, "
                          "partial sums reduce-scattered")
     ap.add_argument("--rs-chunk", type=int, default=32768, help="tokens per reduce-scatter chunk (--shard tables)")
+    ap.add_argument("--rs", default="nccl", choices=["nccl", "fused", "fused-store"],
+                    help="--shard tables: combine partial sums with NCCL reduce-scatter, or inside the gather kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on a small case)")
     ap.add_argument("--no-e2e", action="store_true", help="device path only, short report (for ncu captures)")

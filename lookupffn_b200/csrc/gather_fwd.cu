@@ -38,12 +38,23 @@
 
 namespace lffn {
 
-template <typename TableT, typename OutT, int VPL, int U, bool FULLV>
+// 16-byte vector reduction into global memory, which may be another GPU's memory mapped over NVLink
+__device__ __forceinline__ void red_add_v4_f32(float *p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// SCATTER: instead of storing the row locally, send it to the rank that owns token n (n / rows_per_owner),
+// peers[] holding every rank's buffer address (peer-mapped over NVLink): either added in place (vector
+// reductions) or stored into this rank's slab of the owner's staging buffer.  Gather and the exchange step of the
+// reduce-scatter become one kernel; the partial sums are never written to this GPU's HBM.
+template <typename TableT, typename OutT, int VPL, int U, bool FULLV, bool SCATTER = false>
 __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) gather_fwd_kernel(const int32_t *__restrict__ idx, const float *__restrict__ w,
                                                          const TableT *__restrict__ tables, OutT *__restrict__ out,
                                                          long long N, int I, long long S, int d, int col0,
                                                          const float *__restrict__ bias, const int2 *__restrict__ seg,
-                                                         int i0, int icnt, int resume, int finish, uint32_t *status) {
+                                                         int i0, int icnt, int resume, int finish, uint32_t *status,
+                                                         float *const *__restrict__ peers, long long rows_per_owner,
+                                                         int slab) {
     // i0/icnt: the slice of each token's index list this launch consumes; resume: start from the fp32 partial
     // sums already in `out`; finish: last slice, add the bias and convert (see launch_vpl_f on why lists are sliced)
     constexpr int EPV = Elem<TableT>::PER_VEC;
@@ -148,6 +159,28 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
             }
         }
 
+        if constexpr (SCATTER) {
+            // slab < 0: add into the owner's [rows_per_owner, d] buffer; slab >= 0: plain 16-byte stores into slab
+            // `slab` of the owner's [n_ranks, rows_per_owner, d] staging buffer (the owner sums the slabs afterwards)
+            const long long row = (slab < 0 ? 0 : (long long)slab * rows_per_owner) + n % rows_per_owner;
+            float *prow = peers[n / rows_per_owner] + row * d + (long long)col0 * EPV;
+#pragma unroll
+            for (int v = 0; v < VPL; v++) {
+                const int c = lane + 32 * v;
+                if (c < nvec) {
+#pragma unroll
+                    for (int q = 0; q < EPV / 4; q++) {
+                        if (slab < 0)
+                            red_add_v4_f32(prow + c * EPV + 4 * q, acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2],
+                                           acc[v][4 * q + 3]);
+                        else
+                            *reinterpret_cast<float4 *>(prow + c * EPV + 4 * q) =
+                                make_float4(acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2], acc[v][4 * q + 3]);
+                    }
+                }
+            }
+            continue;
+        }
         // epilogue: + bias (one rounded add, as `outputs + self.bias`), convert, 16-byte stores
         OutT *orow = out + n * d + (long long)col0 * EPV;
 #pragma unroll
@@ -219,11 +252,73 @@ static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, 
         const int icnt = I - i0 < per ? I - i0 : per;
         kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, w, static_cast<const TableT *>(tables), static_cast<OutT *>(out), N,
                                                  I, S, d, col0, bias, seg, i0, icnt, i0 > 0 ? 1 : 0,
-                                                 i0 + icnt >= I ? 1 : 0, status);
+                                                 i0 + icnt >= I ? 1 : 0, status, nullptr, 0, -1);
         LFFN_CHECK_CUDA(cudaGetLastError());
         if (I == 0) break;
     }
     return LFFN_OK;
+}
+
+template <typename TableT, int VPL, bool FULLV>
+static int launch_scatter_f(const int32_t *idx, const float *w, const void *tables, float *const *peers,
+                            long long rows_per_owner, int slab, int64_t N, int I, int64_t S, int d, int col0,
+                            cudaStream_t st) {
+    constexpr int U = (VPL <= 3) ? LFFN_GATHER_U_NARROW : (VPL <= 6 ? LFFN_GATHER_U_MEDIUM : LFFN_GATHER_U_WIDE);
+    constexpr int THREADS = LFFN_GATHER_THREADS;
+    auto kern = gather_fwd_kernel<TableT, float, VPL, U, FULLV, true>;
+    int per_sm = 0;
+    LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, 0));
+    if (per_sm < 1) per_sm = 1;
+    const long long want = (N + THREADS / 32 - 1) / (THREADS / 32);
+    long long grid = (long long)num_sms() * per_sm;
+    if (grid > want) grid = want;
+    if (grid < 1) grid = 1;
+    uint32_t *status = status_word();
+    LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
+    kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, w, static_cast<const TableT *>(tables), nullptr, N, I, S, d, col0, nullptr,
+                                             nullptr, 0, I, 0, 1, status, peers, rows_per_owner, slab);
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return LFFN_OK;
+}
+
+template <typename TableT>
+static int launch_scatter_typed(const int32_t *idx, const float *w, const void *tables, float *const *peers,
+                                long long rows_per_owner, int slab, int64_t N, int I, int64_t S, int d, cudaStream_t st) {
+    constexpr int EPV = Elem<TableT>::PER_VEC;
+    const int row_vecs = d / EPV;
+    constexpr int MAXV = 8;
+    for (int col0 = 0; col0 < row_vecs; col0 += MAXV * 32) {
+        const int nvec = min(row_vecs - col0, MAXV * 32);
+        const int vpl = (nvec + 31) / 32;
+        const bool full = nvec == vpl * 32;
+        int rc;
+#define LFFN_SCATTER_CASE(V)                                                                                              \
+    rc = full ? launch_scatter_f<TableT, V, true>(idx, w, tables, peers, rows_per_owner, slab, N, I, S, d, col0, st)      \
+              : launch_scatter_f<TableT, V, false>(idx, w, tables, peers, rows_per_owner, slab, N, I, S, d, col0, st)
+        switch (vpl) {
+            case 1: LFFN_SCATTER_CASE(1); break;
+            case 2: LFFN_SCATTER_CASE(2); break;
+            case 3: LFFN_SCATTER_CASE(3); break;
+            case 4: LFFN_SCATTER_CASE(4); break;
+            case 5:
+            case 6: LFFN_SCATTER_CASE(6); break;
+            default: LFFN_SCATTER_CASE(8); break;
+        }
+#undef LFFN_SCATTER_CASE
+        if (rc != LFFN_OK) return rc;
+    }
+    return LFFN_OK;
+}
+
+int launch_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tables, int table_dtype,
+                              float *const *peers, long long rows_per_owner, int slab, int64_t N, int I, int64_t S,
+                              int d, cudaStream_t st) {
+    if (table_dtype == LFFN_F32)
+        return launch_scatter_typed<float>(idx, w, tables, peers, rows_per_owner, slab, N, I, S, d, st);
+    if (table_dtype == LFFN_BF16)
+        return launch_scatter_typed<__nv_bfloat16>(idx, w, tables, peers, rows_per_owner, slab, N, I, S, d, st);
+    set_error("gather_fwd_scatter: unknown table dtype %d", table_dtype);
+    return LFFN_ERR_INVALID_ARG;
 }
 
 // FULLV: the column tile is exactly VPL*32 vectors wide, so no lane needs a column predicate

@@ -184,3 +184,75 @@ class ShardedTableAdamW:
 
     def zero_grad(self):
         self.tables.grad = None
+
+
+class PeerOutput:
+    """Output buffers of all ranks, each mapped into every process (torch symmetric memory: CUDA peer mappings
+    over NVLink), plus the device array of their addresses that lffn_gather_fwd_scatter takes.
+    mode "add" (default): every rank owns [N/world, d] fp32 and partial rows are added in place with vector
+    reductions (as fast as the NCCL path; summation order across ranks not fixed).
+    mode "store": every rank owns a staging buffer [world, N/world, d] fp32; rank r stores its partial rows into
+    slab r of the owner's buffer and the owner sums the slabs in rank order (deterministic, but measured about
+    twice slower: fine-grained peer stores).
+    Allocate once and reuse across steps."""
+
+    def __init__(self, rows_per_rank, d, device, group=None, mode="add"):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        assert mode in ("store", "add")
+        self.mode = mode
+        self.group = dist.group.WORLD if group is None else group
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.rows, self.d = rows_per_rank, d
+        shape = (self.world, rows_per_rank, d) if mode == "store" else (rows_per_rank, d)
+        self.local = symm_mem.empty(shape, dtype=torch.float32, device=device)
+        self.handle = symm_mem.rendezvous(self.local, self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.ptr_array = torch.tensor(ptrs, dtype=torch.int64, device=device)
+
+    def _rank_barrier(self):
+        torch.cuda.current_stream().synchronize()
+        dist.barrier(self.group)
+
+    def reset(self, bias=None):
+        """Before a step.  "add": the owner writes the initial value (zeros or the bias) of its rows.  Both
+        modes end with a rank barrier: no peer may write into a buffer its owner is still reading or initialising."""
+        if self.mode == "add":
+            if bias is None:
+                self.local.zero_()
+            else:
+                self.local.copy_(bias.to(torch.float32)[None].expand_as(self.local))
+        self._rank_barrier()
+
+    def finish(self, bias=None):
+        """After every rank's kernel has finished all partial rows have landed; returns this rank's [N/world, d]."""
+        self._rank_barrier()
+        if self.mode == "add":
+            return self.local
+        out = self.local.sum(0)
+        if bias is not None:
+            out += bias.to(out.dtype)
+        return out
+
+
+def lookup_forward_table_sharded_fused(x, desc, tables_local, t_begin, t_count, peers, bias=None):
+    """The table-sharded forward with the exchange step of the reduce-scatter fused into the gather kernel: each
+    rank's gather sends its partial rows straight to the owner's buffer through peer-mapped memory over NVLink
+    (plain stores into its slab, or in-place vector reductions), so the [N, d] partial sums are never written to
+    or read from this GPU's HBM and no NCCL collective moves data.  Token n is owned by rank n // (N / world).
+    Returns this rank's [N/world, d] fp32 rows."""
+    from . import _lib as L
+
+    N = x.shape[0]
+    if N != peers.rows * peers.world:
+        raise ValueError(f"N = {N} tokens but the peer buffers hold {peers.rows} x {peers.world} rows")
+    peers.reset(bias)
+    idx, w, _ = ops.hash_fwd(x, desc, t_begin=t_begin, t_count=t_count)
+    tables_local = tables_local if tables_local.is_contiguous() else tables_local.contiguous()
+    S, d = tables_local.shape
+    slab = peers.rank if peers.mode == "store" else -1
+    with torch.cuda.device(x.device):
+        L.check(L.lib().lffn_gather_fwd_scatter(L.ptr(idx), L.ptr(w), L.ptr(tables_local),
+                                                L.dtype_code(tables_local.dtype), L.ptr(peers.ptr_array), peers.world,
+                                                peers.rows, slab, N, idx.shape[1], S, d, L.stream_ptr(x.device)))
+    return peers.finish(bias if peers.mode == "store" else None)

@@ -59,3 +59,60 @@ def test_table_sharded_forward_two_gpus():
     for rank, err, shape in res:
         assert shape == (2048, 512)
         assert err < 1e-6  # fp32 partial sums added in another order than the single fmaf chain
+
+
+def _fused_worker(rank, world, port, q):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from lookupffn_b200 import ops, sharded
+
+        dev = torch.device("cuda", rank)
+        N, d_in, D, T, k, d_out = 4096, 768, 1024, 96, 8, 512
+        R = -(-T * k // D)
+        g = torch.Generator(device=dev).manual_seed(5)
+        x = torch.randn(N, d_in, generator=g, device=dev).to(torch.bfloat16)
+        signs = (2 * torch.randint(0, 2, (R, 2, D, 1, 1), generator=g, device=dev) - 1).float()
+        tables = (0.02 * torch.randn(T << k, d_out, generator=g, device=dev)).to(torch.bfloat16)
+        bias = torch.randn(d_out, generator=g, device=dev)
+        desc = ops.make_hash_desc(d_in, signs, None, T, k, had_scale=1 / 32, mix_a=1.0, mix_b=0.0)
+        idx, w, _ = ops.hash_fwd(x, desc)
+        y_full = ops.weighted_vector_gather_add(idx, tables, w, bias=bias, out_dtype=torch.float32)
+        tb, tc = sharded.table_range(T, rank, world)
+        errs = []
+        local = tables[tb << k:(tb + tc) << k].contiguous()
+        lo = rank * (N // world)
+        for mode in ("store", "add"):
+            peers = sharded.PeerOutput(N // world, d_out, dev, mode=mode)
+            for _ in range(2):  # twice: the buffers are reused
+                y_loc = sharded.lookup_forward_table_sharded_fused(x, desc, local, tb, tc, peers, bias=bias)
+                errs.append(float((y_loc - y_full[lo:lo + N // world]).abs().max() / y_full.abs().max()))
+        q.put((rank, max(errs), tuple(y_loc.shape)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_gather_reduce_scatter_two_gpus():
+    """Gather + reduce-scatter in one kernel through peer-mapped output buffers vs the single-GPU forward."""
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29750 + os.getpid() % 200
+    procs = [ctx.Process(target=_fused_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, err, shape in res:
+        assert shape == (2048, 512)
+        assert err < 1e-6
