@@ -660,3 +660,37 @@ def test_sliced_index_lists_are_bit_exact(dev):
     tabn = t2n(tab)
     np.testing.assert_array_equal(t2n(y), O.gather(idx, w, tabn, bias=bias))
     assert rel_err(t2n(dw), O.gather_bwd_weights(idx, dy, tabn)) < 1e-4
+
+
+def test_layer_fwd_host_buffers_match_device_path(dev):
+    """lffn_layer_fwd_host: pinned host x in, pinned host y out, chunked over internal streams; must equal the
+    device-buffer path bit for bit, including a ragged last chunk and a second call that reuses the workspace."""
+    import ctypes as C
+
+    from lookupffn_b200 import _lib as L
+    from lookupffn_b200 import ops
+
+    lib = L.lib()
+    g = torch.Generator(device=dev).manual_seed(8)
+    N, d_in, D, T, k, d_out = 1000, 768, 1024, 96, 8, 768
+    R = -(-T * k // D)
+    x = torch.randn(N, d_in, generator=g, device=dev).to(torch.bfloat16)
+    tables = (0.02 * torch.randn(T << k, d_out, generator=g, device=dev)).to(torch.bfloat16)
+    signs = (2 * torch.randint(0, 2, (R, 2, D, 1, 1), generator=g, device=dev) - 1).float()
+    bias = torch.randn(d_out, generator=g, device=dev)
+    desc = ops.make_hash_desc(d_in, signs, None, T, k, had_scale=1 / 32, mix_a=1.0, mix_b=0.0)
+    y_dev = ops.layer_fwd(x, desc, tables, bias=bias)
+    chunk = 192  # 1000 = 5 * 192 + 40
+    nbytes = lib.lffn_layer_fwd_host_ws_bytes(C.byref(desc), L.BF16, L.BF16, d_out, chunk)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    x_host = x.cpu().pin_memory()
+    for _ in range(2):
+        y_host = torch.zeros(N, d_out, dtype=torch.bfloat16).pin_memory()
+        with torch.cuda.device(dev):
+            L.check(lib.lffn_layer_fwd_host(C.byref(desc), L.ptr(x_host), L.BF16, N, L.ptr(tables), L.BF16, d_out,
+                                            L.ptr(bias), L.ptr(y_host), L.BF16, L.ptr(ws), nbytes, chunk, L.stream_ptr(dev)))
+        assert torch.equal(y_host.view(torch.int16), y_dev.cpu().view(torch.int16))
+    # a workspace that is too small is refused with the needed size in the message
+    rc = lib.lffn_layer_fwd_host(C.byref(desc), L.ptr(x_host), L.BF16, N, L.ptr(tables), L.BF16, d_out, L.ptr(bias),
+                                 L.ptr(y_host), L.BF16, L.ptr(ws), nbytes // 2, chunk, L.stream_ptr(dev))
+    assert rc == -5 and b"workspace" in lib.lffn_last_error_string()
