@@ -65,11 +65,14 @@ __device__ __forceinline__ void fwht_pass(float *Y, int D, int lo, float scale, 
 template <int NW = HB_THREADS / 32>
 __device__ __forceinline__ void fwht_tile(float *Y, int D, float scale, int warp, int lane) {
     int bits = 31 - __clz(D);
+    // up to 5 bits (radix 32) per pass, split evenly: 10 bits = 5 + 5, 9 = 5 + 4
     while (bits > 0) {
-        const int nb = bits >= 4 ? 4 : bits;
+        const int left = (bits + 4) / 5;
+        const int nb = (bits + left - 1) / left;
         const int lo = bits - nb;
         const float sc = lo == 0 ? scale : 1.f;
-        if (nb == 4) fwht_pass<16, NW>(Y, D, lo, sc, warp, lane);
+        if (nb == 5) fwht_pass<32, NW>(Y, D, lo, sc, warp, lane);
+        else if (nb == 4) fwht_pass<16, NW>(Y, D, lo, sc, warp, lane);
         else if (nb == 3) fwht_pass<8, NW>(Y, D, lo, sc, warp, lane);
         else if (nb == 2) fwht_pass<4, NW>(Y, D, lo, sc, warp, lane);
         else fwht_pass<2, NW>(Y, D, lo, sc, warp, lane);
