@@ -8,7 +8,8 @@ sees all N tokens, computes the partial sum over its tables in fp32 and the part
 by a reduce-scatter(sum) over tokens, chunk by chunk so that the collective of chunk c overlaps the
 kernels of chunk c+1 (NCCL runs on its own stream).  After the call rank g holds N/world rows; the
 rows it owns are returned with it.  The reference has no counterpart (it is data-parallel only,
-main.py:40-47); the partition follows BASELINE.json config 5.
+main.py:40-47); the partition is the one of the benchmark's table-sharded sweep (1 GB of tables split by T
+over 8 GPUs, every GPU seeing all 262,144 tokens).
 """
 import torch
 import torch.distributed as dist

@@ -1,7 +1,7 @@
 """Generate tests/golden/lookupffn_golden.npz by running the REFERENCE's own code.
 
-Run in a container that has the reference checkout (default /root/reference,
-override with LFFN_REFERENCE_ROOT) after `python oracle/build.py`:
+Run in a container that has the reference checkout (its location is taken from LFFN_REFERENCE_ROOT when set)
+after `python oracle/build.py`:
 
     python tests/golden/make_golden.py
 

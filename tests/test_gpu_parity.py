@@ -694,3 +694,42 @@ def test_layer_fwd_host_buffers_match_device_path(dev):
     rc = lib.lffn_layer_fwd_host(C.byref(desc), L.ptr(x_host), L.BF16, N, L.ptr(tables), L.BF16, d_out, L.ptr(bias),
                                  L.ptr(y_host), L.BF16, L.ptr(ws), nbytes // 2, chunk, L.stream_ptr(dev))
     assert rc == -5 and b"workspace" in lib.lffn_last_error_string()
+
+
+def test_full_size_training_gather_adjoint_identities(dev):
+    """Benchmark config 4 at full size (N=16384, T=512, k=8, m=9 candidates, d=768, fp32): the forward and the
+    two gradients are tied by size-independent identities, since y is linear in the weights and in the tables:
+        <y, dy> = sum_{n,i} w[n,i] * dw[n,i] = <dtables, tables>,
+    and the sorted table gradient must reproduce bit for bit on a second run."""
+    from lookupffn_b200 import ops
+
+    N, T, k, d = 16384, 512, 8, 768
+    m, rows = k + 1, 1 << k
+    g = torch.Generator(device=dev).manual_seed(6)
+    x = torch.randn(N, d, generator=g, device=dev)
+    signs = (2 * torch.randint(0, 2, (4, 2, 1024, 1, 1), generator=g, device=dev) - 1).float()
+    tables = 0.02 * torch.randn(T * rows, d, generator=g, device=dev)
+    dy = torch.randn(N, d, generator=g, device=dev)
+    desc = ops.make_hash_desc(d, signs, None, T, k, had_scale=1 / 32, mix_a=1.0, mix_b=0.0,
+                              weight_mode=O.WEIGHT_SOFT_FLIP, tau=0.5)
+    idx, w, _ = ops.hash_fwd(x, desc)
+    assert idx.shape == (N, T * m)
+    # the k+1 candidates of a table are the hard code and its k single-bit flips; their weights sum to <= 1
+    cand = (idx.view(N, T, m) - (torch.arange(T, device=dev, dtype=torch.int32) * rows)[None, :, None])
+    flips = cand[:, :, 1:] ^ cand[:, :, :1]
+    assert bool(((flips & (flips - 1)) == 0).all()) and bool((flips > 0).all())
+    assert float(w.view(N, T, m).sum(-1).max()) <= 1.0 + 1e-5
+    y = ops.weighted_vector_gather_add(idx, tables, w)
+    dw = ops.indexed_inner_product(idx, dy, tables)
+    dt = ops.weighted_vector_scatter_add(idx, dy, w, T * rows, structure=(T, m, rows))
+    dt2 = ops.weighted_vector_scatter_add(idx, dy, w, T * rows, structure=(T, m, rows))
+    assert torch.equal(dt, dt2)
+    a = float((y.double() * dy.double()).sum())
+    b = float((w.double() * dw.double()).sum())
+    c = float((dt.double() * tables.double()).sum())
+    scale = float((y.double().abs() * dy.double().abs()).sum())
+    assert abs(a - b) < 1e-5 * scale and abs(a - c) < 1e-5 * scale
+    # a sample of tokens against the oracle
+    sel = torch.arange(0, N, N // 16, device=dev)
+    y_ref = O.gather(t2n(idx[sel]), t2n(w[sel]), t2n(tables))
+    np.testing.assert_array_equal(t2n(y[sel]), y_ref)
