@@ -72,6 +72,8 @@ def hash_fwd(x, desc, t_begin=0, t_count=None, want_z=False, want_codes=True):
     """x [N, d_in] -> (idx int32 [N, t_count*m] with table offsets, w fp32 [N, t_count*m], z or None).
     Reference: Hashing.forward (lookup.py:64-77) + the offsets of LookupFFN.gather (lookup.py:126)."""
     L.require_cuda(x)
+    if x.dtype == torch.float16:  # the reference trains under fp16 autocast; the kernels read fp32 or bf16
+        x = x.float()
     x = _contig(x)
     N = x.shape[0]
     t_count = desc.T - t_begin if t_count is None else t_count

@@ -103,10 +103,15 @@ class TableShardedLookupFFN(nn.Module):
     (every rank constructs or loads the same one) and keeps only its own slice of `tables`;
     LayerNorm, projection and bias stay replicated."""
 
-    def __init__(self, full, group=None, chunk_tokens=32768):
+    def __init__(self, full, group=None, chunk_tokens=32768, exchange="auto"):
+        """exchange: "nccl" (chunked reduce-scatter), "fused" (peer reductions from the gather kernel) or "auto":
+        fused when this rank gathers at least 128 rows per token -- enough work to hide the peer traffic
+        (measured at 8 GPUs: 256 tables per rank 18.1 vs 23.5 ms, 16 tables per rank 10.5 vs 5.4 ms)."""
         super().__init__()
         self.group = group
         self.chunk_tokens = chunk_tokens
+        self.exchange = exchange
+        self._peers = None
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         self.t_begin, self.t_count = table_range(full.num_table, rank, world)
         self.LayerNorm = full.LayerNorm
@@ -125,6 +130,22 @@ class TableShardedLookupFFN(nn.Module):
         u = self.LayerNorm(hidden_states)
         N = u.shape[0]
         flat = self.tables.reshape(self.t_count * self.table_size, self.output_size)
+        world = dist.get_world_size(self.group)
+        fused = self.exchange == "fused" or (self.exchange == "auto" and world > 1 and N % world == 0
+                                             and self.t_count * self.hash.candidates >= 128)
+        if fused:
+            if self._peers is None or self._peers.rows != N // world:
+                self._peers = PeerOutput(N // world, self.output_size, u.device, group=self.group)
+            peers = self._peers
+            peers.reset(self.bias)
+            idx, w = self.hash(u, t_begin=self.t_begin, t_count=self.t_count)
+            from . import _lib as L
+            with torch.cuda.device(u.device):
+                L.check(L.lib().lffn_gather_fwd_scatter(L.ptr(idx), L.ptr(w), L.ptr(flat), L.dtype_code(flat.dtype),
+                                                        L.ptr(peers.ptr_array), world, peers.rows, -1, N, idx.shape[1],
+                                                        flat.shape[0], self.output_size, L.stream_ptr(u.device)))
+            rank = dist.get_rank(self.group)
+            return peers.finish().clone(), torch.arange(rank * peers.rows, (rank + 1) * peers.rows)
 
         def partial(start, size):
             idx, w = self.hash(u[start:start + size], t_begin=self.t_begin, t_count=self.t_count)

@@ -116,3 +116,56 @@ def test_fused_gather_reduce_scatter_two_gpus():
     for rank, err, shape in res:
         assert shape == (2048, 512)
         assert err < 1e-6
+
+
+def _module_worker(rank, world, port, q):
+    from argparse import Namespace
+
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from lookupffn_b200 import LookupFFN, sharded
+
+        dev = torch.device("cuda", rank)
+        torch.manual_seed(0)  # the same module on every rank
+        cfg = Namespace(hidden_size=512, ffn_num_table=256, ffn_table_size=256, layer_norm_eps=1e-5,
+                        projection_type="bh4", block_size=64)
+        full = LookupFFN(cfg, 512).to(dev).eval()
+        x = torch.randn(2048, 512, device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+        with torch.no_grad():
+            y_full = full(x)
+        errs = {}
+        for mode in ("nccl", "fused", "auto"):
+            mod = sharded.TableShardedLookupFFN(full, chunk_tokens=512, exchange=mode)
+            y_loc, owned = mod(x)
+            errs[mode] = float((y_loc - y_full[owned.to(dev)]).abs().max() / y_full.abs().max())
+        q.put((rank, errs, mod.t_count))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_table_sharded_module_two_gpus():
+    """TableShardedLookupFFN (reference BH4 projection, tables split by T) with each exchange mode vs the whole
+    module on one GPU."""
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29650 + os.getpid() % 90
+    procs = [ctx.Process(target=_module_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, errs, t_count in res:
+        assert t_count == 128
+        assert all(e < 1e-6 for e in errs.values()), errs
