@@ -222,7 +222,10 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
 template <typename TableT, typename OutT, int VPL, bool FULLV>
 static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, void *out, int64_t N, int I, int64_t S,
                       int d, int col0, const float *bias, const int2 *seg, cudaStream_t st) {
-    constexpr int U = (VPL <= 3) ? LFFN_GATHER_U_NARROW : (VPL <= 6 ? LFFN_GATHER_U_MEDIUM : LFFN_GATHER_U_WIDE);
+    // rows in flight per warp; 2 KB bf16 rows (VPL = 4) measured best with 3 (config-5 shape: 2.41 -> 2.14 ms)
+    constexpr int U = (VPL <= 3) ? LFFN_GATHER_U_NARROW
+                      : (VPL == 4 && sizeof(TableT) == 2) ? 3
+                      : (VPL <= 6 ? LFFN_GATHER_U_MEDIUM : LFFN_GATHER_U_WIDE);
     constexpr int THREADS = LFFN_GATHER_THREADS;
     auto kern = gather_fwd_kernel<TableT, OutT, VPL, U, FULLV>;
     int per_sm = 0;
@@ -263,7 +266,10 @@ template <typename TableT, int VPL, bool FULLV>
 static int launch_scatter_f(const int32_t *idx, const float *w, const void *tables, float *const *peers,
                             long long rows_per_owner, int slab, int64_t N, int I, int64_t S, int d, int col0,
                             cudaStream_t st) {
-    constexpr int U = (VPL <= 3) ? LFFN_GATHER_U_NARROW : (VPL <= 6 ? LFFN_GATHER_U_MEDIUM : LFFN_GATHER_U_WIDE);
+    // rows in flight per warp; 2 KB bf16 rows (VPL = 4) measured best with 3 (config-5 shape: 2.41 -> 2.14 ms)
+    constexpr int U = (VPL <= 3) ? LFFN_GATHER_U_NARROW
+                      : (VPL == 4 && sizeof(TableT) == 2) ? 3
+                      : (VPL <= 6 ? LFFN_GATHER_U_MEDIUM : LFFN_GATHER_U_WIDE);
     constexpr int THREADS = LFFN_GATHER_THREADS;
     auto kern = gather_fwd_kernel<TableT, float, VPL, U, FULLV, true>;
     int per_sm = 0;
