@@ -702,6 +702,7 @@ def main():
     ap.add_argument("--rs", default="nccl", choices=["nccl", "fused", "fused-store"],
                     help="--shard tables: combine partial sums with NCCL reduce-scatter, or inside the gather kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-encoder", action="store_true", help="skip the short config-2 encoder run appended at N=1")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on a small case)")
     ap.add_argument("--no-e2e", action="store_true", help="device path only, short report (for ncu captures)")
     args = ap.parse_args()
@@ -740,6 +741,13 @@ def main():
     if out is not None:
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_path(args, 15.0)
+        if world == 1 and args.workload == "c3" and not args.tokens and not args.no_encoder:
+            # the second half of the headline metric: RoBERTa-small encoder inference (config 2), a short run
+            enc_args = argparse.Namespace(**vars(args))
+            enc_args.steps, enc_args.warmup = 10, 3
+            enc = run_encoder(enc_args, rank, world, local)
+            out["roberta_small_encoder"] = {"value": enc["value"], "unit": enc["unit"], "ms_per_step": enc["ms_per_step"],
+                                            "e2e": enc["e2e"]["value"], "steps": 10, "config": enc["config"]["workload"]}
         print(json.dumps(out), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
