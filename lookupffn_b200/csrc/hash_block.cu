@@ -129,15 +129,42 @@ __device__ __forceinline__ void tile_end_rotation(float *Y, const float *carry, 
     long long t_end = c_hi / k;
     if (t_end > a.t_begin + a.t_count) t_end = a.t_begin + a.t_count;
     if (lane < mt && a.idx_out != nullptr) {
-        for (long long t = t_first + warp; t < t_end; t += THREADS / 32) {
+        auto emit = [&](long long t, int wm, int32_t *io, float *wo) {
             const int local0 = (int)(t * k - c_lo);
             auto get = [&](int j) -> float {
                 const int e = local0 + j;
                 return e >= 0 ? Y[e * HB_MP + lane] : carry[(HB_CARRY + e) * HB_MP + lane];
             };
-            const long long o = (n0 + lane) * out_pitch + (t - a.t_begin) * m;
-            emit_table(get, k, a.bit_order, a.weight_mode, a.tau, (int32_t)((t - a.t_begin) << k), false, 0,
-                       a.idx_out + o, a.w_out + o);
+            emit_table(get, k, a.bit_order, wm, a.tau, (int32_t)((t - a.t_begin) << k), false, 0, io, wo);
+        };
+        const bool vec4 = m == 1 && (out_pitch & 3) == 0 && ((reinterpret_cast<uintptr_t>(a.idx_out) & 15u) == 0) &&
+                          ((reinterpret_cast<uintptr_t>(a.w_out) & 15u) == 0);
+        if (vec4) {
+            // m == 1 rules out the soft-flip mode: naming the two remaining modes lets the compiler drop that branch
+            const int wm = a.weight_mode == LFFN_WEIGHT_ONES ? LFFN_WEIGHT_ONES : LFFN_WEIGHT_SCORE;
+            // a warp takes four consecutive tables at a time and each lane (token) writes their codes and weights
+            // with one 16-byte store each
+            const long long q_first = (t_first - a.t_begin) >> 2, q_end = (t_end - a.t_begin + 3) >> 2;
+            for (long long q = q_first + warp; q < q_end; q += THREADS / 32) {
+                const long long tb = a.t_begin + q * 4;
+                const long long o = (n0 + lane) * out_pitch + q * 4;
+                if (tb >= t_first && tb + 4 <= t_end) {
+                    int32_t ci[4];
+                    float cw[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) emit(tb + u, wm, ci + u, cw + u);
+                    *reinterpret_cast<int4 *>(a.idx_out + o) = make_int4(ci[0], ci[1], ci[2], ci[3]);
+                    *reinterpret_cast<float4 *>(a.w_out + o) = make_float4(cw[0], cw[1], cw[2], cw[3]);
+                } else {
+                    for (int u = 0; u < 4; u++)
+                        if (tb + u >= t_first && tb + u < t_end) emit(tb + u, wm, a.idx_out + o + u, a.w_out + o + u);
+                }
+            }
+        } else {
+            for (long long t = t_first + warp; t < t_end; t += THREADS / 32) {
+                const long long o = (n0 + lane) * out_pitch + (t - a.t_begin) * m;
+                emit(t, a.weight_mode, a.idx_out + o, a.w_out + o);
+            }
         }
     }
 }
@@ -263,15 +290,14 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) my_tiles++;
     const long long total_chunks = my_tiles * chunks_per_tile;
 
-    // global chunk counter -> source of that chunk (the weights do not depend on the tile)
+    // Chunks are consumed in the order (tile, rotation, stage, pass, row slice); the weights do not depend on the
+    // tile.  The position of the next chunk to fetch is advanced incrementally (no divisions in the loop).
+    int nx_r = a.r_lo, nx_s = 0, nx_p = 0, nx_h = 0;
+    long long nx_left = total_chunks;
     auto issue_chunk = [&](long long gc) {
-        if (gc >= total_chunks) return;
-        const long long in_tile = gc % chunks_per_tile;
-        const int r = a.r_lo + (int)(in_tile / (a.S * cps));
-        const int rem = (int)(in_tile % (a.S * cps));
-        const int s = rem / cps, c = rem % cps;
-        const int p = c / (64 / CR), h = c % (64 / CR);
-        const float *src = a.w + (((long long)r * a.S + s) * NB + NBLK * p) * 4096 + h * CR * 64;
+        if (nx_left <= 0) return;
+        nx_left--;
+        const float *src = a.w + (((long long)nx_r * a.S + nx_s) * NB + NBLK * nx_p) * 4096 + nx_h * CR * 64;
         float *dst = Wb + (gc & 1) * HF_CHUNK_FLOATS;
 #pragma unroll
         for (int j = 0; j < 2048 / THREADS; j++) {
@@ -281,6 +307,16 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                        src + (long long)g * 4096 + il * 64 + o4 * 4);
         }
         cp_async_commit();
+        if (++nx_h == 64 / CR) {
+            nx_h = 0;
+            if (++nx_p == D / PC) {
+                nx_p = 0;
+                if (++nx_s == a.S) {
+                    nx_s = 0;
+                    if (++nx_r > a.r_hi) nx_r = a.r_lo;
+                }
+            }
+        }
     };
 
     long long gc = 0;
