@@ -85,45 +85,69 @@ __device__ __forceinline__ void fwht_tile(float *Y, int D, float scale, int warp
 // Start of a rotation: keep the last coordinates of the previous rotation (for a table that straddles the
 // boundary), then load the tile transposed and zero-padded.  The caller synchronises afterwards.
 template <typename XT, int THREADS>
-__device__ __forceinline__ void tile_begin_rotation(float *Y, float *carry, const HashArgs &a, long long n0, int mt, int D) {
+__device__ __forceinline__ void tile_load(float *dst, const HashArgs &a, long long n0, int mt, int D) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    __syncthreads();
-    for (int i = tid; i < HB_CARRY * HB_M; i += THREADS) {
-        const int e = i / HB_M, mm = i % HB_M;
-        carry[e * HB_MP + mm] = Y[(D - HB_CARRY + e) * HB_MP + mm];
-    }
-    __syncthreads();
     for (int mm = warp; mm < HB_M; mm += THREADS / 32) {
         const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
         for (int e = lane; e < D; e += 32)
-            Y[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+            dst[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
     }
 }
 
+__device__ __forceinline__ void tile_save_carry(const float *Y, float *carry, int D, int threads) {
+    for (int i = threadIdx.x; i < HB_CARRY * HB_M; i += threads) {
+        const int e = i / HB_M, mm = i % HB_M;
+        carry[e * HB_MP + mm] = Y[(D - HB_CARRY + e) * HB_MP + mm];
+    }
+}
+
+template <typename XT, int THREADS>
+__device__ __forceinline__ void tile_begin_rotation(float *Y, float *carry, const HashArgs &a, long long n0, int mt, int D) {
+    __syncthreads();
+    tile_save_carry(Y, carry, D, THREADS);
+    __syncthreads();
+    tile_load<XT, THREADS>(Y, a, n0, mt, D);
+}
+
 // End of a rotation: z = fl(fl(mix_a * y) + fl(mix_b * u)) + bias in place, then codes and weights of the
-// tables that end inside this rotation (lane = token, warps stride over tables).
+// tables that end inside this rotation (lane = token, warps stride over tables).  Xs, when not null, is a copy of
+// the input tile in the layout of Y: u comes from there instead of global memory, and when no table straddles a
+// rotation boundary and z itself is not wanted the mix is folded into the code/weight step (Y is not rewritten).
 template <typename XT, int THREADS>
 __device__ __forceinline__ void tile_end_rotation(float *Y, const float *carry, const HashArgs &a, long long n0, int mt,
-                                                  int D, int r) {
+                                                  int D, int r, const float *Xs = nullptr) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = a.k;
     const int m = a.weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
     const long long g_lo = (long long)a.t_begin * k, g_hi = (long long)(a.t_begin + a.t_count) * k;
     const long long out_pitch = (long long)a.t_count * m;
     const long long c_lo = (long long)r * D, c_hi = c_lo + D;
-    for (int mm = warp; mm < HB_M; mm += THREADS / 32) {
-        const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
-        for (int e = lane; e < D; e += 32) {
-            const float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+    const bool fused = Xs != nullptr && a.z_out == nullptr && D % k == 0;
+    if (Xs != nullptr && !fused) {
+        for (int e = warp; e < D; e += THREADS / 32) {  // lane = token
             const long long g = c_lo + e;
-            float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + mm]), __fmul_rn(a.mix_b, u));
+            float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + lane]), __fmul_rn(a.mix_b, Xs[e * HB_MP + lane]));
             if (a.bias != nullptr && g < (long long)a.T * k) z = __fadd_rn(z, __ldg(a.bias + g));
-            Y[e * HB_MP + mm] = z;
-            if (a.z_out != nullptr && mm < mt && g >= g_lo && g < g_hi)
-                a.z_out[(n0 + mm) * (g_hi - g_lo) + (g - g_lo)] = z;
+            Y[e * HB_MP + lane] = z;
+            if (a.z_out != nullptr && lane < mt && g >= g_lo && g < g_hi)
+                a.z_out[(n0 + lane) * (g_hi - g_lo) + (g - g_lo)] = z;
         }
+        __syncthreads();
+    } else if (!fused) {
+        for (int mm = warp; mm < HB_M; mm += THREADS / 32) {
+            const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
+            for (int e = lane; e < D; e += 32) {
+                const float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+                const long long g = c_lo + e;
+                float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + mm]), __fmul_rn(a.mix_b, u));
+                if (a.bias != nullptr && g < (long long)a.T * k) z = __fadd_rn(z, __ldg(a.bias + g));
+                Y[e * HB_MP + mm] = z;
+                if (a.z_out != nullptr && mm < mt && g >= g_lo && g < g_hi)
+                    a.z_out[(n0 + mm) * (g_hi - g_lo) + (g - g_lo)] = z;
+            }
+        }
+        __syncthreads();
     }
-    __syncthreads();
     long long t_first = c_lo / k;
     if (t_first < a.t_begin) t_first = a.t_begin;
     long long t_end = c_hi / k;
@@ -133,6 +157,11 @@ __device__ __forceinline__ void tile_end_rotation(float *Y, const float *carry, 
             const int local0 = (int)(t * k - c_lo);
             auto get = [&](int j) -> float {
                 const int e = local0 + j;
+                if (fused) {  // no straddling table here: e >= 0
+                    float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + lane]), __fmul_rn(a.mix_b, Xs[e * HB_MP + lane]));
+                    if (a.bias != nullptr) z = __fadd_rn(z, __ldg(a.bias + c_lo + e));
+                    return z;
+                }
                 return e >= 0 ? Y[e * HB_MP + lane] : carry[(HB_CARRY + e) * HB_MP + lane];
             };
             emit_table(get, k, a.bit_order, wm, a.tau, (int32_t)((t - a.t_begin) << k), false, 0, io, wo);
@@ -269,7 +298,10 @@ constexpr int HF_CHUNK_FLOATS = 4 * 32 * 64;  // 4 blocks x 32 rows x 64 outputs
 
 // THREADS = columns per pass (one 8 x 4 item per thread): 256 threads work on 4 blocks x 32-row chunks, 512 threads
 // on 8 blocks x 16-row chunks; the chunk is 32 KB either way.
-template <typename XT, int THREADS>
+// X0: shared memory has room for a second [D][HB_MP] array (D <= 512): the input tile is loaded once per tile and
+// kept there; the first stage of every rotation reads it directly and the mix at the end of a rotation takes u
+// from it, instead of eight passes over the tile's rows in global memory per tile.
+template <typename XT, int THREADS, bool X0>
 __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     constexpr int PC = THREADS;            // columns per pass
     constexpr int CR = 8192 / PC;          // input rows per chunk
@@ -280,19 +312,23 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     float *Y = smem;                              // [D][HB_MP]
     float *Wb = Y + (size_t)D * HB_MP;            // 2 x HF_CHUNK_FLOATS
     float *carry = Wb + 2 * HF_CHUNK_FLOATS;      // [HB_CARRY][HB_MP]
+    float *Xs = X0 ? carry + HB_CARRY * HB_MP : nullptr;  // [D][HB_MP]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int NB = D / 64;
     const int cps = (D / PC) * (64 / CR);            // chunks per stage: passes x row slices
     const int nrot = a.r_hi - a.r_lo + 1;
-    const long long chunks_per_tile = (long long)nrot * a.S * cps;
     const long long ntiles = (a.N + HB_M - 1) / HB_M;
-    long long my_tiles = 0;
-    for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) my_tiles++;
-    const long long total_chunks = my_tiles * chunks_per_tile;
+    // Work units are (tile, rotation) pairs, tile-major, cut into gridDim.x contiguous ranges of nearly equal length:
+    // rotations are independent, so with 512 tiles x 4 rotations on 148 CTAs every CTA gets 13 or 14 units instead of
+    // 3 or 4 whole tiles.  When a table can straddle two rotations (k does not divide D) a range holds whole tiles.
+    const long long per = (D % a.k == 0) ? 1 : nrot;
+    const long long groups = ntiles * nrot / per;
+    const long long u_begin = groups * blockIdx.x / gridDim.x * per, u_end = groups * (blockIdx.x + 1) / gridDim.x * per;
+    const long long total_chunks = (u_end - u_begin) * a.S * cps;
 
     // Chunks are consumed in the order (tile, rotation, stage, pass, row slice); the weights do not depend on the
     // tile.  The position of the next chunk to fetch is advanced incrementally (no divisions in the loop).
-    int nx_r = a.r_lo, nx_s = 0, nx_p = 0, nx_h = 0;
+    int nx_r = a.r_lo + (int)(u_begin % nrot), nx_s = 0, nx_p = 0, nx_h = 0;
     long long nx_left = total_chunks;
     auto issue_chunk = [&](long long gc) {
         if (nx_left <= 0) return;
@@ -321,55 +357,72 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
 
     long long gc = 0;
     issue_chunk(0);
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    long long tile = u_begin / nrot;
+    int r = a.r_lo + (int)(u_begin % nrot);
+    for (long long u = u_begin; u < u_end; u++) {
         const long long n0 = tile * HB_M;
         const int mt = (int)min((long long)HB_M, a.N - n0);
-        for (int r = a.r_lo; r <= a.r_hi; r++) {
-            tile_begin_rotation<XT, THREADS>(Y, carry, a, n0, mt, D);
-            for (int s = 0; s < a.S; s++) {
-                const int cq = tid % (PC / 4), tq = tid / (PC / 4);   // PC/4 column quads x 4 token octets
-                const int g = cq >> 4, o4 = cq & 15;
-                for (int p = 0; p < D / PC; p++) {
-                    const int col0 = p * PC;
-                    unsigned long long acc[4][4];               // [token pair][column]
-#pragma unroll
-                    for (int pp = 0; pp < 4; pp++)
-#pragma unroll
-                        for (int q = 0; q < 4; q++) acc[pp][q] = 0ull;
-                    for (int h = 0; h < 64 / CR; h++) {
-                        cp_async_wait_all();
-                        __syncthreads();           // chunk gc landed for everyone; buffer (gc+1)&1 is free; Y is loaded
-                        issue_chunk(gc + 1);
-                        const float *wb = Wb + (gc & 1) * HF_CHUNK_FLOATS + g * (CR * 64);
-                        const float *yb = Y + (size_t)(col0 + g * 64 + h * CR) * HB_MP + tq * 8;
-#pragma unroll 8
-                        for (int il = 0; il < CR; il++) {
-                            const ulonglong2 x0 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP);
-                            const ulonglong2 x1 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP + 4);
-                            const float4 w4 = *reinterpret_cast<const float4 *>(wb + il * 64 + ((o4 ^ (il & 15)) << 2));
-                            const unsigned long long wq[4] = {dup2(w4.x), dup2(w4.y), dup2(w4.z), dup2(w4.w)};
-#pragma unroll
-                            for (int q = 0; q < 4; q++) {
-                                ffma2(acc[0][q], x0.x, wq[q]);
-                                ffma2(acc[1][q], x0.y, wq[q]);
-                                ffma2(acc[2][q], x1.x, wq[q]);
-                                ffma2(acc[3][q], x1.y, wq[q]);
-                            }
-                        }
-                        gc++;
-                    }
-                    __syncthreads();  // every thread finished reading this pass's 256 input columns
-                    float *yo = Y + (size_t)(col0 + cq * 4) * HB_MP + tq * 8;
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        *reinterpret_cast<ulonglong2 *>(yo + q * HB_MP) = make_ulonglong2(acc[0][q], acc[1][q]);
-                        *reinterpret_cast<ulonglong2 *>(yo + q * HB_MP + 4) = make_ulonglong2(acc[2][q], acc[3][q]);
-                    }
-                }
+        const bool first_of_tile = u == u_begin || r == a.r_lo;
+        if constexpr (X0) {
+            if (first_of_tile) {
+                __syncthreads();  // the previous unit has finished reading Xs
+                tile_load<XT, THREADS>(Xs, a, n0, mt, D);
+            } else if (D % a.k != 0) {
                 __syncthreads();
-                fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
+                tile_save_carry(Y, carry, D, THREADS);
             }
-            tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r);
+            // the barrier that opens the first pass orders both against the multiply-add loop
+        } else {
+            tile_begin_rotation<XT, THREADS>(Y, carry, a, n0, mt, D);
+        }
+        for (int s = 0; s < a.S; s++) {
+            const float *ysrc = (X0 && s == 0) ? Xs : Y;
+            const int cq = tid % (PC / 4), tq = tid / (PC / 4);   // PC/4 column quads x 4 token octets
+            const int g = cq >> 4, o4 = cq & 15;
+            for (int p = 0; p < D / PC; p++) {
+                const int col0 = p * PC;
+                unsigned long long acc[4][4];               // [token pair][column]
+#pragma unroll
+                for (int pp = 0; pp < 4; pp++)
+#pragma unroll
+                    for (int q = 0; q < 4; q++) acc[pp][q] = 0ull;
+                for (int h = 0; h < 64 / CR; h++) {
+                    cp_async_wait_all();
+                    __syncthreads();           // chunk gc landed for everyone; buffer (gc+1)&1 is free; Y is loaded
+                    issue_chunk(gc + 1);
+                    const float *wb = Wb + (gc & 1) * HF_CHUNK_FLOATS + g * (CR * 64);
+                    const float *yb = ysrc + (size_t)(col0 + g * 64 + h * CR) * HB_MP + tq * 8;
+#pragma unroll 16
+                    for (int il = 0; il < CR; il++) {
+                        const ulonglong2 x0 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP);
+                        const ulonglong2 x1 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP + 4);
+                        const float4 w4 = *reinterpret_cast<const float4 *>(wb + il * 64 + ((o4 ^ (il & 15)) << 2));
+                        const unsigned long long wq[4] = {dup2(w4.x), dup2(w4.y), dup2(w4.z), dup2(w4.w)};
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            ffma2(acc[0][q], x0.x, wq[q]);
+                            ffma2(acc[1][q], x0.y, wq[q]);
+                            ffma2(acc[2][q], x1.x, wq[q]);
+                            ffma2(acc[3][q], x1.y, wq[q]);
+                        }
+                    }
+                    gc++;
+                }
+                __syncthreads();  // every thread finished reading this pass's 256 input columns
+                float *yo = Y + (size_t)(col0 + cq * 4) * HB_MP + tq * 8;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    *reinterpret_cast<ulonglong2 *>(yo + q * HB_MP) = make_ulonglong2(acc[0][q], acc[1][q]);
+                    *reinterpret_cast<ulonglong2 *>(yo + q * HB_MP + 4) = make_ulonglong2(acc[2][q], acc[3][q]);
+                }
+            }
+            __syncthreads();
+            fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
+        }
+        tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r, Xs);
+        if (++r > a.r_hi) {
+            r = a.r_lo;
+            tile++;
         }
     }
     cp_async_wait_all();
@@ -393,19 +446,29 @@ int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, c
         static_assert(2 * HF_CHUNK_FLOATS == HB_WFLOATS, "same shared-memory footprint as the generic kernel");
         static const bool narrow_only = [] { const char *e = getenv("LFFN_BLOCK64_NARROW"); return e && e[0] == '1'; }();
         const bool wide = a.D % 512 == 0 && !narrow_only;   // 512 threads: 16 warps per SM instead of 8
+        // the kernel splits (tile, rotation) units, or whole tiles when k does not divide D, evenly over the grid
+        const long long nrot = a.r_hi - a.r_lo + 1;
+        const long long groups = a.D % a.k == 0 ? ntiles * nrot : ntiles;
+        grid = num_sms();
+        if (grid > groups) grid = groups;
+        if (grid < 1) grid = 1;
         const int threads = wide ? 512 : 256;
+        const size_t smem_x0 = smem + (size_t)a.D * HB_MP * sizeof(float);  // + the resident copy of the input tile
+        const bool x0 = smem_x0 <= 227 * 1024;
+        const size_t smem_k = x0 ? smem_x0 : smem;
+        void (*kern)(HashArgs) = nullptr;
         if (x_dtype == LFFN_F32) {
-            auto kern = wide ? hash_block64_kernel<float, 512> : hash_block64_kernel<float, 256>;
-            LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<(unsigned)grid, threads, smem, st>>>(a);
+            kern = wide ? (x0 ? hash_block64_kernel<float, 512, true> : hash_block64_kernel<float, 512, false>)
+                        : (x0 ? hash_block64_kernel<float, 256, true> : hash_block64_kernel<float, 256, false>);
         } else if (x_dtype == LFFN_BF16) {
-            auto kern = wide ? hash_block64_kernel<__nv_bfloat16, 512> : hash_block64_kernel<__nv_bfloat16, 256>;
-            LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<(unsigned)grid, threads, smem, st>>>(a);
+            kern = wide ? (x0 ? hash_block64_kernel<__nv_bfloat16, 512, true> : hash_block64_kernel<__nv_bfloat16, 512, false>)
+                        : (x0 ? hash_block64_kernel<__nv_bfloat16, 256, true> : hash_block64_kernel<__nv_bfloat16, 256, false>);
         } else {
             set_error("hash_fwd: unknown x dtype %d", x_dtype);
             return LFFN_ERR_INVALID_ARG;
         }
+        LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k));
+        kern<<<(unsigned)grid, threads, smem_k, st>>>(a);
         LFFN_CHECK_CUDA(cudaGetLastError());
         return LFFN_OK;
     }
