@@ -52,6 +52,7 @@ extern "C" {
 /* bits of the device status word (lffn_device_status) */
 #define LFFN_STATUS_INDEX_RANGE 1u /* a gather/scatter index was outside [0, S); the row was skipped */
 #define LFFN_STATUS_STRUCTURE 2u   /* an index left its table's row range in the sorted backward     */
+#define LFFN_STATUS_TIMEOUT 4u     /* a bounded wait inside a kernel ran out; that launch's outputs are incomplete */
 
 typedef void *lffn_stream_t;
 

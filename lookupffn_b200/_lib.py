@@ -15,7 +15,7 @@ LIB_PATH = os.environ.get("LFFN_LIBRARY_PATH") or os.path.join(_HERE, "liblookup
 F32, BF16 = 0, 1
 MSB_FIRST, LSB_FIRST = 0, 1
 WEIGHT_SCORE, WEIGHT_ONES, WEIGHT_SOFT_FLIP = 0, 1, 2
-STATUS_INDEX_RANGE, STATUS_STRUCTURE = 1, 2
+STATUS_INDEX_RANGE, STATUS_STRUCTURE, STATUS_TIMEOUT = 1, 2, 4
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 ERR_NAMES = {-1: "INVALID_ARG", -2: "UNSUPPORTED", -3: "CUDA", -4: "INDEX_RANGE", -5: "SCRATCH"}

@@ -273,18 +273,53 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, i
 
 // ---- fast path: 64 x 64 blocks, weights stored [block][i][o] ------------------------------------------
 // Same tile layout and arithmetic as hash_block_kernel; what changes is how the weights travel and how the
-// multiply-adds are issued.  Weights stream through two 32 KB shared buffers in chunks of (4 blocks) x (32
-// input rows) x (64 outputs), fetched with 16-byte cp.async one chunk ahead of the arithmetic -- across
-// passes, stages and rotations, so the Hadamard passes hide the next stage's first chunk -- and land
-// already in the swizzled [i][o] layout.  The 8 x 4 register tile is held as 16 packed pairs and updated
-// with fma.rn.f32x2 (two IEEE fp32 fused multiply-adds per instruction): 16 packed FMAs + 4 register moves
-// per input coordinate instead of 32 scalar FMAs.  Each output is still one fmaf chain over i ascending.
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
-    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+// multiply-adds are issued.  Weights stream through two 32 KB shared buffers in chunks of (NBLK blocks) x (CR
+// input rows) x (64 outputs).  A chunk is NBLK contiguous pieces of global memory, so one thread fetches it with
+// NBLK bulk copies (cp.async.bulk, the TMA unit) that signal a "full" mbarrier by byte count; every warp reports on
+// an "empty" mbarrier when it has finished with a chunk, and the next fetch into that buffer waits for the 16
+// reports.  The fetch runs one chunk ahead of the arithmetic across passes, stages and rotations, so the Hadamard
+// passes hide the next stage's first chunk, and there is no CTA-wide barrier inside the multiply-add loop: the
+// columns a warp overwrites after a pass are read only by that same warp (two blocks x one token octet).
+// The 8 x 4 register tile is held as 16 packed pairs and updated with fma.rn.f32x2 (two IEEE fp32 fused
+// multiply-adds per instruction).  Each output is still one fmaf chain over i ascending.
+//
+// Every mbarrier wait is a bounded poll: when the bound is hit the thread sets LFFN_STATUS_TIMEOUT in the device
+// status word and leaves the kernel (the outputs of that launch are then incomplete).
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+constexpr int MBAR_POLL_LIMIT = 1 << 22;  // polls of a few tens of ns each: gives up after about 0.1 - 0.2 s
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity) {
+    const unsigned addr = smem_u32(bar);
+    for (int it = 0; it < MBAR_POLL_LIMIT; it++) {
+        unsigned done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// global -> shared bulk copy (16-byte aligned addresses, size a multiple of 16) that adds its byte count to `bar`
+__device__ __forceinline__ void bulk_copy_g2s(void *smem_dst, const void *gmem_src, unsigned bytes, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(__cvta_generic_to_global(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 __device__ __forceinline__ unsigned long long dup2(float w) {
     unsigned long long r;
     asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(w));
@@ -295,6 +330,7 @@ __device__ __forceinline__ void ffma2(unsigned long long &acc, unsigned long lon
 }
 
 constexpr int HF_CHUNK_FLOATS = 4 * 32 * 64;  // 4 blocks x 32 rows x 64 outputs
+constexpr int HF_BAR_FLOATS = 8;               // four mbarriers behind the carry rows
 
 // THREADS = columns per pass (one 8 x 4 item per thread): 256 threads work on 4 blocks x 32-row chunks, 512 threads
 // on 8 blocks x 16-row chunks; the chunk is 32 KB either way.
@@ -312,7 +348,9 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     float *Y = smem;                              // [D][HB_MP]
     float *Wb = Y + (size_t)D * HB_MP;            // 2 x HF_CHUNK_FLOATS
     float *carry = Wb + 2 * HF_CHUNK_FLOATS;      // [HB_CARRY][HB_MP]
-    float *Xs = X0 ? carry + HB_CARRY * HB_MP : nullptr;  // [D][HB_MP]
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(carry + HB_CARRY * HB_MP);
+    unsigned long long *full = bars, *empty = bars + 2;    // one pair per weight buffer
+    float *Xs = X0 ? carry + HB_CARRY * HB_MP + HF_BAR_FLOATS : nullptr;  // [D][HB_MP]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int NB = D / 64;
     const int cps = (D / PC) * (64 / CR);            // chunks per stage: passes x row slices
@@ -326,23 +364,31 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     const long long u_begin = groups * blockIdx.x / gridDim.x * per, u_end = groups * (blockIdx.x + 1) / gridDim.x * per;
     const long long total_chunks = (u_end - u_begin) * a.S * cps;
 
+    if (tid == 0) {
+        mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
+        mbar_init(&empty[0], NW);
+        mbar_init(&empty[1], NW);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
     // Chunks are consumed in the order (tile, rotation, stage, pass, row slice); the weights do not depend on the
-    // tile.  The position of the next chunk to fetch is advanced incrementally (no divisions in the loop).
+    // tile.  Thread 0 fetches: the position of the next chunk is advanced incrementally (no divisions in the loop).
+    // Chunk c lives in buffer c & 1 and is the (c >> 1)-th use of that buffer's barriers.
     int nx_r = a.r_lo + (int)(u_begin % nrot), nx_s = 0, nx_p = 0, nx_h = 0;
     long long nx_left = total_chunks;
-    auto issue_chunk = [&](long long gc) {
-        if (nx_left <= 0) return;
+    auto issue_chunk = [&](long long c) -> bool {
+        if (nx_left <= 0) return true;
         nx_left--;
+        const int b = (int)(c & 1);
+        // the buffer's previous chunk, c - 2, must have been reported finished by every warp
+        if (c >= 2 && !mbar_wait(&empty[b], (unsigned)(((c - 2) >> 1) & 1))) return false;
         const float *src = a.w + (((long long)nx_r * a.S + nx_s) * NB + NBLK * nx_p) * 4096 + nx_h * CR * 64;
-        float *dst = Wb + (gc & 1) * HF_CHUNK_FLOATS;
+        float *dst = Wb + b * HF_CHUNK_FLOATS;
+        mbar_arrive_expect_tx(&full[b], HF_CHUNK_FLOATS * sizeof(float));
 #pragma unroll
-        for (int j = 0; j < 2048 / THREADS; j++) {
-            const int q = tid + THREADS * j;             // 16-byte piece 0..2047
-            const int g = q / (CR * 16), rm = q % (CR * 16), il = rm >> 4, o4 = rm & 15;
-            cp_async16(dst + g * (CR * 64) + il * 64 + ((o4 ^ (il & 15)) << 2),
-                       src + (long long)g * 4096 + il * 64 + o4 * 4);
-        }
-        cp_async_commit();
+        for (int g = 0; g < NBLK; g++) bulk_copy_g2s(dst + g * (CR * 64), src + (long long)g * 4096, CR * 64 * sizeof(float), &full[b]);
         if (++nx_h == 64 / CR) {
             nx_h = 0;
             if (++nx_p == D / PC) {
@@ -353,10 +399,14 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                 }
             }
         }
+        return true;
+    };
+    auto give_up = [&]() {
+        if (a.status != nullptr) atomicOr(a.status, LFFN_STATUS_TIMEOUT);
     };
 
     long long gc = 0;
-    issue_chunk(0);
+    if (tid == 0) issue_chunk(0);  // the first use of a buffer waits for nothing
     long long tile = u_begin / nrot;
     int r = a.r_lo + (int)(u_begin % nrot);
     for (long long u = u_begin; u < u_end; u++) {
@@ -371,10 +421,10 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                 __syncthreads();
                 tile_save_carry(Y, carry, D, THREADS);
             }
-            // the barrier that opens the first pass orders both against the multiply-add loop
         } else {
             tile_begin_rotation<XT, THREADS>(Y, carry, a, n0, mt, D);
         }
+        __syncthreads();  // the tile (and the carry rows) are in place
         for (int s = 0; s < a.S; s++) {
             const float *ysrc = (X0 && s == 0) ? Xs : Y;
             const int cq = tid % (PC / 4), tq = tid / (PC / 4);   // PC/4 column quads x 4 token octets
@@ -387,16 +437,26 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
 #pragma unroll
                     for (int q = 0; q < 4; q++) acc[pp][q] = 0ull;
                 for (int h = 0; h < 64 / CR; h++) {
-                    cp_async_wait_all();
-                    __syncthreads();           // chunk gc landed for everyone; buffer (gc+1)&1 is free; Y is loaded
-                    issue_chunk(gc + 1);
+                    if (warp == 0) {  // thread 0 fetches the next chunk; on a timeout its whole warp leaves
+                        int ok = 1;
+                        if (lane == 0) ok = issue_chunk(gc + 1) ? 1 : 0;
+                        ok = __shfl_sync(FULL, ok, 0);
+                        if (!ok) {
+                            give_up();
+                            return;
+                        }
+                    }
+                    if (!mbar_wait(&full[gc & 1], (unsigned)((gc >> 1) & 1))) {  // chunk gc has landed
+                        give_up();
+                        return;
+                    }
                     const float *wb = Wb + (gc & 1) * HF_CHUNK_FLOATS + g * (CR * 64);
                     const float *yb = ysrc + (size_t)(col0 + g * 64 + h * CR) * HB_MP + tq * 8;
 #pragma unroll 16
                     for (int il = 0; il < CR; il++) {
                         const ulonglong2 x0 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP);
                         const ulonglong2 x1 = *reinterpret_cast<const ulonglong2 *>(yb + il * HB_MP + 4);
-                        const float4 w4 = *reinterpret_cast<const float4 *>(wb + il * 64 + ((o4 ^ (il & 15)) << 2));
+                        const float4 w4 = *reinterpret_cast<const float4 *>(wb + il * 64 + (o4 << 2));
                         const unsigned long long wq[4] = {dup2(w4.x), dup2(w4.y), dup2(w4.z), dup2(w4.w)};
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
@@ -406,9 +466,12 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                             ffma2(acc[3][q], x1.y, wq[q]);
                         }
                     }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[gc & 1]);  // this warp is done with the buffer
                     gc++;
                 }
-                __syncthreads();  // every thread finished reading this pass's 256 input columns
+                // the 64 input columns of a block x 8 tokens are read by one half-warp, the one that overwrites them
+                __syncwarp();
                 float *yo = Y + (size_t)(col0 + cq * 4) * HB_MP + tq * 8;
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
@@ -425,7 +488,6 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
             tile++;
         }
     }
-    cp_async_wait_all();
 }
 
 int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, cudaStream_t st) {
@@ -453,9 +515,10 @@ int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, c
         if (grid > groups) grid = groups;
         if (grid < 1) grid = 1;
         const int threads = wide ? 512 : 256;
-        const size_t smem_x0 = smem + (size_t)a.D * HB_MP * sizeof(float);  // + the resident copy of the input tile
+        const size_t smem_b = smem + HF_BAR_FLOATS * sizeof(float);              // + the four mbarriers
+        const size_t smem_x0 = smem_b + (size_t)a.D * HB_MP * sizeof(float);  // + the resident copy of the input tile
         const bool x0 = smem_x0 <= 227 * 1024;
-        const size_t smem_k = x0 ? smem_x0 : smem;
+        const size_t smem_k = x0 ? smem_x0 : smem_b;
         void (*kern)(HashArgs) = nullptr;
         if (x_dtype == LFFN_F32) {
             kern = wide ? (x0 ? hash_block64_kernel<float, 512, true> : hash_block64_kernel<float, 512, false>)

@@ -20,7 +20,13 @@ struct HashArgs {
     int32_t *idx_out;  // may be null together with w_out: only z_out is produced
     float *w_out;
     float *z_out;
+    uint32_t *status;  // device status word (may be null)
 };
+
+// e^x for x <= 0 as one multiply and one ex2.approx.  The result is only ever used as 1 + e^x: its error (about two
+// ulp of e^x, plus |x| * 2^-24 relative from rounding x * log2(e), which matters only where e^x is tiny) moves
+// 1 + e^x by no more than the two-ulp bound of the library expf does, at a quarter of the instructions.
+__device__ __forceinline__ float exp_nonpos(float x) { return __expf(x); }
 
 // ---- codes and weights of one table from its k coordinates ------------------------------------
 // `get(j)` returns coordinate j of the table.  Writes m = 1 or k+1 (idx, w) pairs.
@@ -35,7 +41,7 @@ __device__ __forceinline__ void emit_table(Get get, int k, int bit_order, int we
             if (!have_code && z > 0.f) code |= 1 << j;
             const float a = fabsf(z);
             num = __fadd_rn(num, a);
-            den = __fmul_rn(den, __fadd_rn(1.f, expf(__fmul_rn(-2.f, a))));
+            den = __fmul_rn(den, __fadd_rn(1.f, exp_nonpos(__fmul_rn(-2.f, a))));
         }
         if (have_code) code = code_lsb;
         if (bit_order == LFFN_BIT_MSB_FIRST) code = (int32_t)(__brev((unsigned)code) >> (32 - k));
@@ -58,7 +64,7 @@ __device__ __forceinline__ void emit_table(Get get, int k, int bit_order, int we
             if (j < k) {
                 const float z = get(j);
                 if (!have_code && z > 0.f) code |= 1 << j;
-                s[j] = __fdiv_rn(1.f, __fadd_rn(1.f, expf(__fdiv_rn(-fabsf(z), tau))));
+                s[j] = __fdiv_rn(1.f, __fadd_rn(1.f, exp_nonpos(__fdiv_rn(-fabsf(z), tau))));
             }
         }
         if (have_code) code = code_lsb;
@@ -97,7 +103,7 @@ __device__ __forceinline__ void emit_table_regs(const float (&z)[8], int sub, in
         for (int j = 0; j < K; j++) {
             const float a = fabsf(zz[j]);
             num = __fadd_rn(num, a);
-            den = __fmul_rn(den, __fadd_rn(1.f, expf(__fmul_rn(-2.f, a))));
+            den = __fmul_rn(den, __fadd_rn(1.f, exp_nonpos(__fmul_rn(-2.f, a))));
         }
         if (bit_order == LFFN_BIT_MSB_FIRST) code = (int32_t)(__brev((unsigned)code) >> (32 - K));
         io[0] = code + offset;
@@ -109,7 +115,7 @@ __device__ __forceinline__ void emit_table_regs(const float (&z)[8], int sub, in
     } else {
         float s[K];
 #pragma unroll
-        for (int j = 0; j < K; j++) s[j] = __fdiv_rn(1.f, __fadd_rn(1.f, expf(__fdiv_rn(-fabsf(zz[j]), tau))));
+        for (int j = 0; j < K; j++) s[j] = __fdiv_rn(1.f, __fadd_rn(1.f, exp_nonpos(__fdiv_rn(-fabsf(zz[j]), tau))));
 #pragma unroll
         for (int c = 0; c <= K; c++) {
             float p = 1.f;

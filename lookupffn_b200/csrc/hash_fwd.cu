@@ -540,6 +540,7 @@ int launch_hash_fwd(const lffn_hash_desc &h, const void *x, int x_dtype, int64_t
     a.idx_out = idx_out;
     a.w_out = w_out;
     a.z_out = z_out;
+    a.status = status_word();
     if (h.BS == 1) {
         if (x_dtype == LFFN_F32) return launch_hash_diag_t<float>(a, st);
         if (x_dtype == LFFN_BF16) return launch_hash_diag_t<__nv_bfloat16>(a, st);
