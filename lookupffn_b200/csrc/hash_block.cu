@@ -330,7 +330,11 @@ __device__ __forceinline__ void ffma2(unsigned long long &acc, unsigned long lon
 }
 
 constexpr int HF_CHUNK_FLOATS = 4 * 32 * 64;  // 4 blocks x 32 rows x 64 outputs
-constexpr int HF_BAR_FLOATS = 8;               // four mbarriers behind the carry rows
+#ifndef LFFN_HB_NBUF
+#define LFFN_HB_NBUF 2
+#endif
+constexpr int HF_NBUF = LFFN_HB_NBUF;          // weight buffers in the ring (2 or 4), 64 KB together
+constexpr int HF_BAR_FLOATS = 4 * HF_NBUF;     // a full and an empty mbarrier per buffer, behind the carry rows
 
 // THREADS = columns per pass (one 8 x 4 item per thread): 256 threads work on 4 blocks x 32-row chunks, 512 threads
 // on 8 blocks x 16-row chunks; the chunk is 32 KB either way.
@@ -340,7 +344,8 @@ constexpr int HF_BAR_FLOATS = 8;               // four mbarriers behind the carr
 template <typename XT, int THREADS, bool X0>
 __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     constexpr int PC = THREADS;            // columns per pass
-    constexpr int CR = 8192 / PC;          // input rows per chunk
+    constexpr int CHUNK = 2 * HF_CHUNK_FLOATS / HF_NBUF;  // floats per weight buffer
+    constexpr int CR = CHUNK / PC;         // input rows per chunk
     constexpr int NBLK = PC / 64;          // blocks per pass
     constexpr int NW = THREADS / 32;
     extern __shared__ __align__(16) float smem[];
@@ -349,7 +354,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     float *Wb = Y + (size_t)D * HB_MP;            // 2 x HF_CHUNK_FLOATS
     float *carry = Wb + 2 * HF_CHUNK_FLOATS;      // [HB_CARRY][HB_MP]
     unsigned long long *bars = reinterpret_cast<unsigned long long *>(carry + HB_CARRY * HB_MP);
-    unsigned long long *full = bars, *empty = bars + 2;    // one pair per weight buffer
+    unsigned long long *full = bars, *empty = bars + HF_NBUF;  // one pair per weight buffer
     float *Xs = X0 ? carry + HB_CARRY * HB_MP + HF_BAR_FLOATS : nullptr;  // [D][HB_MP]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int NB = D / 64;
@@ -365,30 +370,24 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     const long long total_chunks = (u_end - u_begin) * a.S * cps;
 
     if (tid == 0) {
-        mbar_init(&full[0], 1);
-        mbar_init(&full[1], 1);
-        mbar_init(&empty[0], NW);
-        mbar_init(&empty[1], NW);
+#pragma unroll
+        for (int b = 0; b < HF_NBUF; b++) {
+            mbar_init(&full[b], 1);
+            mbar_init(&empty[b], NW);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
     // Chunks are consumed in the order (tile, rotation, stage, pass, row slice); the weights do not depend on the
-    // tile.  Thread 0 fetches: the position of the next chunk is advanced incrementally (no divisions in the loop).
-    // Chunk c lives in buffer c & 1 and is the (c >> 1)-th use of that buffer's barriers.
+    // tile.  Every thread advances the position of the next chunk (incrementally, no divisions in the loop); chunk c
+    // is fetched by lane 0 of warp c % NW, so the wait for the buffer to be free -- for the slowest warp to finish
+    // chunk c - HF_NBUF -- falls on a different warp each time instead of making one warp the straggler.
+    // Chunk c lives in buffer c % HF_NBUF and is the (c / HF_NBUF)-th use of that buffer's barriers; the fetch
+    // runs HF_NBUF - 1 chunks ahead of the arithmetic.
     int nx_r = a.r_lo + (int)(u_begin % nrot), nx_s = 0, nx_p = 0, nx_h = 0;
-    long long nx_left = total_chunks;
-    auto issue_chunk = [&](long long c) -> bool {
-        if (nx_left <= 0) return true;
-        nx_left--;
-        const int b = (int)(c & 1);
-        // the buffer's previous chunk, c - 2, must have been reported finished by every warp
-        if (c >= 2 && !mbar_wait(&empty[b], (unsigned)(((c - 2) >> 1) & 1))) return false;
+    auto next_chunk_src = [&]() -> const float * {
         const float *src = a.w + (((long long)nx_r * a.S + nx_s) * NB + NBLK * nx_p) * 4096 + nx_h * CR * 64;
-        float *dst = Wb + b * HF_CHUNK_FLOATS;
-        mbar_arrive_expect_tx(&full[b], HF_CHUNK_FLOATS * sizeof(float));
-#pragma unroll
-        for (int g = 0; g < NBLK; g++) bulk_copy_g2s(dst + g * (CR * 64), src + (long long)g * 4096, CR * 64 * sizeof(float), &full[b]);
         if (++nx_h == 64 / CR) {
             nx_h = 0;
             if (++nx_p == D / PC) {
@@ -399,14 +398,34 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                 }
             }
         }
+        return src;
+    };
+    auto fetch_chunk = [&](long long c, const float *src) -> bool {  // one thread
+        const int b = (int)(c % HF_NBUF);
+        // the buffer's previous chunk, c - HF_NBUF, must have been reported finished by every warp
+        if (c >= HF_NBUF && !mbar_wait(&empty[b], (unsigned)(((c - HF_NBUF) / HF_NBUF) & 1))) return false;
+        float *dst = Wb + b * CHUNK;
+        mbar_arrive_expect_tx(&full[b], CHUNK * sizeof(float));
+#pragma unroll
+        for (int g = 0; g < NBLK; g++) bulk_copy_g2s(dst + g * (CR * 64), src + (long long)g * 4096, CR * 64 * sizeof(float), &full[b]);
         return true;
+    };
+    // all threads call this once per chunk, in chunk order; false = the fetching warp timed out and must leave
+    auto issue_chunk = [&](long long c) -> bool {
+        if (c >= total_chunks) return true;
+        const float *src = next_chunk_src();
+        if (warp != (int)(c % NW)) return true;
+        int ok = 1;
+        if (lane == 0) ok = fetch_chunk(c, src) ? 1 : 0;
+        return __shfl_sync(FULL, ok, 0) != 0;
     };
     auto give_up = [&]() {
         if (a.status != nullptr) atomicOr(a.status, LFFN_STATUS_TIMEOUT);
     };
 
     long long gc = 0;
-    if (tid == 0) issue_chunk(0);  // the first use of a buffer waits for nothing
+#pragma unroll
+    for (int c = 0; c < HF_NBUF - 1; c++) issue_chunk(c);  // the first use of a buffer waits for nothing
     long long tile = u_begin / nrot;
     int r = a.r_lo + (int)(u_begin % nrot);
     for (long long u = u_begin; u < u_end; u++) {
@@ -437,20 +456,16 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
 #pragma unroll
                     for (int q = 0; q < 4; q++) acc[pp][q] = 0ull;
                 for (int h = 0; h < 64 / CR; h++) {
-                    if (warp == 0) {  // thread 0 fetches the next chunk; on a timeout its whole warp leaves
-                        int ok = 1;
-                        if (lane == 0) ok = issue_chunk(gc + 1) ? 1 : 0;
-                        ok = __shfl_sync(FULL, ok, 0);
-                        if (!ok) {
-                            give_up();
-                            return;
-                        }
-                    }
-                    if (!mbar_wait(&full[gc & 1], (unsigned)((gc >> 1) & 1))) {  // chunk gc has landed
+                    if (!issue_chunk(gc + HF_NBUF - 1)) {
                         give_up();
                         return;
                     }
-                    const float *wb = Wb + (gc & 1) * HF_CHUNK_FLOATS + g * (CR * 64);
+                    const int buf = (int)(gc % HF_NBUF);
+                    if (!mbar_wait(&full[buf], (unsigned)((gc / HF_NBUF) & 1))) {  // chunk gc has landed
+                        give_up();
+                        return;
+                    }
+                    const float *wb = Wb + buf * CHUNK + g * (CR * 64);
                     const float *yb = ysrc + (size_t)(col0 + g * 64 + h * CR) * HB_MP + tq * 8;
 #pragma unroll 16
                     for (int il = 0; il < CR; il++) {
@@ -467,7 +482,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                         }
                     }
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty[gc & 1]);  // this warp is done with the buffer
+                    if (lane == 0) mbar_arrive(&empty[buf]);  // this warp is done with the buffer
                     gc++;
                 }
                 // the 64 input columns of a block x 8 tokens are read by one half-warp, the one that overwrites them
