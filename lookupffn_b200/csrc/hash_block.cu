@@ -21,6 +21,24 @@
 
 namespace lffn {
 
+// Optional phase clocks (compile with -DLFFN_HB_PHASE_CLOCKS, see lookupffn_b200/phase_clocks.py): thread 0 of
+// every CTA adds the clock64 cycles between consecutive marks to a per-phase counter.  Off by default.
+#ifdef LFFN_HB_PHASE_CLOCKS
+__device__ unsigned long long g_hb_phase[8];
+__device__ long long g_hb_last[1024];
+__device__ __forceinline__ void hb_mark(int phase) {  // phase < 0: start the clock only
+    if (threadIdx.x == 0) {
+        const long long now = clock64();
+        if (phase >= 0) atomicAdd(&g_hb_phase[phase], (unsigned long long)(now - g_hb_last[blockIdx.x & 1023]));
+        g_hb_last[blockIdx.x & 1023] = now;
+    }
+}
+#define HB_MARK(phase) hb_mark(phase)
+#else
+#define HB_MARK(phase)
+#endif
+enum { HB_PH_TILE = 0, HB_PH_FMA = 1, HB_PH_HADAMARD = 2, HB_PH_MIX = 3, HB_PH_CODES = 4, HB_PH_CHUNK_WAIT = 5, HB_PH_WRITEBACK = 6 };
+
 constexpr int HB_M = 32;        // tokens per tile
 constexpr int HB_MP = 36;       // padded tokens per coordinate row
 constexpr int HB_THREADS = 256;
@@ -148,6 +166,7 @@ __device__ __forceinline__ void tile_end_rotation(float *Y, const float *carry, 
         }
         __syncthreads();
     }
+    HB_MARK(HB_PH_MIX);
     long long t_first = c_lo / k;
     if (t_first < a.t_begin) t_first = a.t_begin;
     long long t_end = c_hi / k;
@@ -424,6 +443,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     };
 
     long long gc = 0;
+    HB_MARK(-1);
 #pragma unroll
     for (int c = 0; c < HF_NBUF - 1; c++) issue_chunk(c);  // the first use of a buffer waits for nothing
     long long tile = u_begin / nrot;
@@ -444,6 +464,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
             tile_begin_rotation<XT, THREADS>(Y, carry, a, n0, mt, D);
         }
         __syncthreads();  // the tile (and the carry rows) are in place
+        HB_MARK(HB_PH_TILE);
         for (int s = 0; s < a.S; s++) {
             const float *ysrc = (X0 && s == 0) ? Xs : Y;
             const int cq = tid % (PC / 4), tq = tid / (PC / 4);   // PC/4 column quads x 4 token octets
@@ -456,6 +477,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
 #pragma unroll
                     for (int q = 0; q < 4; q++) acc[pp][q] = 0ull;
                 for (int h = 0; h < 64 / CR; h++) {
+                    HB_MARK(HB_PH_FMA);
                     if (!issue_chunk(gc + HF_NBUF - 1)) {
                         give_up();
                         return;
@@ -465,6 +487,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                         give_up();
                         return;
                     }
+                    HB_MARK(HB_PH_CHUNK_WAIT);
                     const float *wb = Wb + buf * CHUNK + g * (CR * 64);
                     const float *yb = ysrc + (size_t)(col0 + g * 64 + h * CR) * HB_MP + tq * 8;
 #pragma unroll 16
@@ -485,6 +508,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                     if (lane == 0) mbar_arrive(&empty[buf]);  // this warp is done with the buffer
                     gc++;
                 }
+                HB_MARK(HB_PH_FMA);
                 // the 64 input columns of a block x 8 tokens are read by one half-warp, the one that overwrites them
                 __syncwarp();
                 float *yo = Y + (size_t)(col0 + cq * 4) * HB_MP + tq * 8;
@@ -495,9 +519,15 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                 }
             }
             __syncthreads();
+            HB_MARK(HB_PH_WRITEBACK);
             fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
+            HB_MARK(HB_PH_HADAMARD);
         }
         tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r, Xs);
+#ifdef LFFN_HB_PHASE_CLOCKS
+        __syncthreads();
+#endif
+        HB_MARK(HB_PH_CODES);
         if (++r > a.r_hi) {
             r = a.r_lo;
             tile++;
@@ -567,3 +597,15 @@ int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, c
 }
 
 }  // namespace lffn
+
+#ifdef LFFN_HB_PHASE_CLOCKS
+// Reads (and optionally clears) the phase counters of hash_block64_kernel: cycles summed over CTAs, indexed by HB_PH_*.
+extern "C" int lffn_debug_hash_block_phases(unsigned long long *out8, int reset) {
+    if (out8 != nullptr && cudaMemcpyFromSymbol(out8, lffn::g_hb_phase, 8 * sizeof(unsigned long long)) != cudaSuccess) return -3;
+    if (reset) {
+        const unsigned long long zero[8] = {0};
+        if (cudaMemcpyToSymbol(lffn::g_hb_phase, zero, sizeof(zero)) != cudaSuccess) return -3;
+    }
+    return 0;
+}
+#endif
