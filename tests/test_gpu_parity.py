@@ -130,6 +130,45 @@ def test_hash_fwd_matches_oracle(dev, case, transpose_w):
     np.testing.assert_array_equal(t2n(w_s), t2n(wgt)[:, tb * m:(tb + tc) * m])
 
 
+BLOCK64_CASES = [
+    # N, d_in, D, T, k, weight_mode: the 64 x 64 fast kernel without z_out, many work units per CTA
+    (6500, 512, 512, 192, 8, O.WEIGHT_SCORE),      # input tile resident, mix folded into the code step, 3 rotations
+    (5000, 500, 512, 150, 6, O.WEIGHT_SCORE),      # k does not divide D: carry rows, whole tiles per CTA
+    (300, 256, 256, 100, 8, O.WEIGHT_ONES),        # 256-thread variant, 4 rotations
+    (4200, 768, 1024, 256, 8, O.WEIGHT_SCORE),     # D = 1024: no resident tile, two passes per stage
+    (700, 512, 512, 24, 8, O.WEIGHT_SOFT_FLIP),    # k + 1 candidates per table (scalar stores)
+]
+
+
+@pytest.mark.parametrize("case", BLOCK64_CASES, ids=[f"b{i}" for i in range(len(BLOCK64_CASES))])
+def test_hash_block64_without_z_matches_oracle(dev, case):
+    """The paths of the 64 x 64 kernel that only run when z itself is not asked for, on enough tokens that every
+    CTA walks several (tile, rotation) units and its weight-chunk ring wraps many times."""
+    from lookupffn_b200 import _lib, ops
+
+    N, d_in, D, T, k, wm = case
+    rng = np.random.RandomState(N + T)
+    R = max(1, -(-T * k // D))
+    w = make_proj(rng, D, 64, 4, R, signs=False)
+    bias = (0.05 * rng.randn(T * k)).astype(np.float32)
+    x = rng.randn(N, d_in).astype(np.float32)
+    z_ref = O.project(x, w, T * k, transpose_w=True, had_scale=1.0, mix_a=0.7, mix_b=0.3, bias=bias)
+    idx_ref, w_ref = O.code_weights(z_ref, T, k, bit_order=O.MSB_FIRST, weight_mode=wm, tau=0.5)
+    desc = ops.make_hash_desc(d_in, torch.from_numpy(w).to(dev), torch.from_numpy(bias).to(dev), T, k, transpose_w=True,
+                              mix_a=0.7, mix_b=0.3, weight_mode=wm, tau=0.5)
+    xd = torch.from_numpy(x).to(dev)
+    idx, wgt, _ = ops.hash_fwd(xd, desc)
+    np.testing.assert_array_equal(t2n(idx), idx_ref)
+    assert rel_err(t2n(wgt), w_ref) < 1e-5
+    # a table sub-range starting inside a rotation
+    m = k + 1 if wm == O.WEIGHT_SOFT_FLIP else 1
+    tb, tc = T // 3 + 1, T - T // 3 - 2
+    idx_s, w_s, _ = ops.hash_fwd(xd, desc, t_begin=tb, t_count=tc)
+    np.testing.assert_array_equal(t2n(idx_s), idx_ref[:, tb * m:(tb + tc) * m] - tb * (1 << k))
+    np.testing.assert_array_equal(t2n(w_s), t2n(wgt)[:, tb * m:(tb + tc) * m])
+    assert _lib.device_status(dev) & _lib.STATUS_TIMEOUT == 0
+
+
 def test_hash_bf16_input(dev):
     from lookupffn_b200 import ops
 
