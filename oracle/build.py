@@ -11,7 +11,10 @@ Outputs
   oracle/liblffn_oracle.so   C restatement (oracle/lffn_oracle.c)
   oracle/_ref/ccs_cpu*.so          reference compute_code_score extension, unmodified source
   oracle/_ref/gather_add_cpu*.so   reference CPU gather extension, unmodified source
-The reference sources are compiled where they lie; nothing is copied.
+  oracle/_ref/gather_add*.so       reference CUDA gather extension (fp32 / fp16 kernels), unmodified source, sm_100a
+  oracle/_ref/fast_hadamard_transform_kernel*.so   reference CUDA Hadamard extension, unmodified source, sm_100a
+The reference sources are compiled where they lie; nothing is copied.  The two CUDA modules are the GPU comparator:
+tests check the library's kernels against them on the GPU, the benchmark times them beside its own.
 """
 import argparse
 import os
@@ -59,6 +62,21 @@ def ref_module_path(name):
     return os.path.join(REF_OUT, name + suffix)
 
 
+def load_ref_module(name):
+    """Import one of the modules built into oracle/_ref (None when it has not been built)."""
+    import importlib.util
+
+    path = ref_module_path(name)
+    if not os.path.exists(path):
+        return None
+    import torch  # noqa: F401  (the extension modules link against libtorch)
+
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def build_ref(force=False, verbose=True):
     """Compile the reference's two CPU extensions (pybind11 + ATen modules) with one
     g++ command each.  Returns the list built, or [] when the reference tree is absent."""
@@ -92,6 +110,73 @@ def build_ref(force=False, verbose=True):
     return built
 
 
+REF_CUDA_EXTENSIONS = {
+    # module name -> (directory relative to prenorm_lookup/, sources)
+    "gather_add": (os.path.join("gather", "cuda", "extension"),
+                   ["gather_kernel_fp16.cu", "gather_fp16.cu", "gather_kernel_fp32.cu", "gather_fp32.cu",
+                    "torch_extension.cpp"]),
+    "fast_hadamard_transform_kernel": (os.path.join("bh4", "fast_hadamard_transform", "extension"),
+                                       ["cuda_kernel.cu", "cuda_launch.cu", "torch_extension.cpp"]),
+}
+
+
+def build_ref_cuda(force=False, verbose=True):
+    """Compile the reference's CUDA extensions for sm_100a: one nvcc / g++ command per source file (the same files
+    its own torch.utils.cpp_extension.load call lists), one link step per module.  Objects go to oracle/_ref/obj."""
+    if not os.path.isdir(REF_LOOKUP):
+        return []
+    from concurrent.futures import ThreadPoolExecutor
+
+    import torch
+    from torch.utils import cpp_extension
+
+    objdir = os.path.join(REF_OUT, "obj")
+    os.makedirs(objdir, exist_ok=True)
+    inc = []
+    for p in cpp_extension.include_paths("cuda"):
+        inc += ["-isystem", p]
+    inc += ["-isystem", sysconfig.get_paths()["include"]]
+    libdir = os.path.join(os.path.dirname(torch.__file__), "lib")
+    abi = f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    jobs, plan = [], {}
+    for name, (rel, files) in REF_CUDA_EXTENSIONS.items():
+        srcs = [os.path.join(REF_LOOKUP, rel, f) for f in files]
+        out = ref_module_path(name)
+        if not force and _newer(out, srcs):
+            plan[name] = (out, None)
+            continue
+        objs = []
+        for src in srcs:
+            obj = os.path.join(objdir, name + "_" + os.path.basename(src) + ".o")
+            defs = [f"-DTORCH_EXTENSION_NAME={name}", "-DTORCH_API_INCLUDE_EXTENSION_H", abi]
+            if src.endswith(".cu"):
+                cmd = (["nvcc", "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-w",
+                        "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC"] + defs + inc + ["-c", src, "-o", obj])
+            else:
+                cmd = (["g++", "-std=c++17", "-O3", "-fPIC", "-w"] + defs + inc
+                       + ["-isystem", os.path.join(cuda_home, "include"), "-c", src, "-o", obj])
+            jobs.append(cmd)
+            objs.append(obj)
+        plan[name] = (out, objs)
+
+    def run(cmd):
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        list(pool.map(run, jobs))
+    built = []
+    for name, (out, objs) in plan.items():
+        if objs is not None:
+            run(["g++", "-shared"] + objs + ["-o", out, f"-L{libdir}", f"-Wl,-rpath,{libdir}",
+                                             f"-L{os.path.join(cuda_home, 'lib64')}", "-ltorch_python", "-ltorch",
+                                             "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", "-lcudart"])
+        built.append(out)
+    return built
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--no-ref", action="store_true")
@@ -101,6 +186,8 @@ def main():
     if not a.no_ref:
         got = build_ref(force=a.force)
         print("reference CPU extensions:", got if got else "reference tree not present, skipped")
+        got = build_ref_cuda(force=a.force)
+        print("reference CUDA extensions:", got if got else "reference tree not present, skipped")
 
 
 if __name__ == "__main__":
