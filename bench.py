@@ -474,6 +474,45 @@ def run_train_gather(args, rank, world, local):
         elapsed_ms = float(t[0])
     if rank != 0:
         return None
+    comparator = None
+    if world == 1 and not args.no_cpu_baseline:
+        # baseline leg: the reference's own fp32 CUDA kernels (oracle/_ref, unmodified, sm_100a) on the same tensors
+        from oracle import build as obuild
+
+        gat = obuild.load_ref_module("gather_add")
+        if gat is not None:
+            def once(fn):
+                fn()  # warm-up
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1)
+
+            ry, rdw, rdt = torch.zeros_like(y), torch.zeros_like(dw), torch.zeros_like(dt)
+            ref_ms = {
+                "gather_fwd": once(lambda: gat.weighted_vector_gather_add_fp32(idx, tables, w, ry)),
+                "grad_weights": once(lambda: gat.indexed_inner_product_fp32(idx, dy, tables, rdw)),
+            }
+            rdt.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gat.weighted_vector_scatter_add_fp32(idx, dy, w, rdt)  # one launch, into zeros: its result is checked
+            e1.record()
+            torch.cuda.synchronize()
+            ref_ms["grad_tables_atomics"] = e0.elapsed_time(e1)
+
+            def rel(a, b):
+                return float((a - b).abs().max() / b.abs().max())
+
+            comparator = {"kernels": "reference weighted_vector_gather_add / indexed_inner_product / "
+                                     "weighted_vector_scatter_add fp32 (gather/cuda/extension, unmodified, sm_100a)",
+                          "ms": ref_ms, "ms_total": sum(ref_ms.values()),
+                          "ours_ms_total": per["gather_fwd"] + per["grad_weights"] + per["grad_tables_sorted"],
+                          "max_abs_diff_over_max_abs": {"y": rel(y, ry), "dw": rel(dw, rdw), "dtables": rel(dt, rdt)}}
+            del ry, rdw, rdt
     logical = N * I * d * 4
     return {
         "metric": "lookupffn_gather_forward_backward_throughput", "value": world * N * args.steps / (elapsed_ms * 1e-3),
@@ -486,6 +525,7 @@ def run_train_gather(args, rank, world, local):
         "kernels_ms": per,
         "algorithmic_GBps": {n: logical / (per[n] * 1e-3) / 1e9 for n in names[1:]},
         "gpu_launches": 5 * args.steps, "clocks": clocks, "device_status": L.device_status(device),
+        "gpu_comparator": comparator,
     }
 
 
