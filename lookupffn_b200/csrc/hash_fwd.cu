@@ -185,21 +185,6 @@ __device__ __forceinline__ void fwht_vec8(float (&v)[NV][8], const float (&sgn)[
             }
         }
     }
-#ifdef LFFN_VEC8_ROLLED_LANE_STAGES
-    const int lane_id = threadIdx.x & 31;
-#pragma unroll 1
-    for (int s = 16; s >= 1; s >>= 1) {
-        const float sg = (lane_id & s) ? -1.f : 1.f;
-#pragma unroll
-        for (int i = 0; i < NV; i++) {
-#pragma unroll
-            for (int q = 0; q < 8; q++) {
-                const float p = __shfl_xor_sync(FULL, v[i][q], s);
-                v[i][q] = __fmaf_rn(v[i][q], sg, p);
-            }
-        }
-    }
-#else
 #pragma unroll
     for (int b = 0; b < 5; b++) {
         const int s = 16 >> b;
@@ -212,7 +197,6 @@ __device__ __forceinline__ void fwht_vec8(float (&v)[NV][8], const float (&sgn)[
             }
         }
     }
-#endif
 #pragma unroll
     for (int s = 4; s >= 1; s >>= 1) {
 #pragma unroll
