@@ -152,17 +152,22 @@ int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int3
  * token n goes to the rank that owns it, n / rows_per_owner, through out_ptrs, a DEVICE array of n_owners fp32
  * buffer addresses, one per rank, all mapped into this process (peer / symmetric memory over NVLink; the local
  * one included).
- *   slab < 0:  buffers are [rows_per_owner, d]; the row is ADDED in place (fp32 vector reductions).  They must
+ *   slab < 0:  buffers are [rows_per_owner, d]; the row is ADDED in place: the warp parks its fp32 row in shared
+ *              memory and one bulk reduction (cp.reduce.async.bulk, f32 add) carries it to the owner.  They must
  *              hold their initial value (zeros or the bias) on every rank before any rank starts; the order of
  *              summation across ranks is not fixed.
  *   slab >= 0: buffers are [n_owners, rows_per_owner, d]; the row is STORED (plain 16-byte stores) into slab
  *              `slab` (the caller's rank).  The owner then sums its slabs in rank order: deterministic.
+ * first_owner in [0, n_owners): the call walks the tokens starting with those of this owner and wraps around.
+ * Ranks that run at the same time should pass different values ((rank + 1) % n_owners): then at any moment every
+ * rank sends to a different owner and all NVLink ports are busy, instead of all ranks converging on one owner.
+ * The result does not depend on it.
  * Either way a buffer is complete once every rank's call has finished: the caller synchronises the ranks on the
  * host; the kernel itself never waits on a peer.
  */
 int lffn_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype,
-                            float *const *out_ptrs, int32_t n_owners, int64_t rows_per_owner, int32_t slab, int64_t N,
-                            int32_t I, int64_t S, int32_t d, lffn_stream_t stream);
+                            float *const *out_ptrs, int32_t n_owners, int64_t rows_per_owner, int32_t slab,
+                            int32_t first_owner, int64_t N, int32_t I, int64_t S, int32_t d, lffn_stream_t stream);
 
 /*
  * dw[n, i] = <dy[n, :], tables[idx[n, i], :]>: replaces gather_add.indexed_inner_product_fp32/_fp16

@@ -51,7 +51,7 @@ _SIGNATURES = {
     "lffn_gather_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64,
                                   C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "lffn_gather_fwd_scatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
-                                          C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_int64, C.c_int32,
+                                          C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_int64, C.c_int32,
                                           C.c_void_p]),
     "lffn_gather_bwd_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64,
                                           C.c_int32, C.c_int64, C.c_int32, C.c_void_p]),

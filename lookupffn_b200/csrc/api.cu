@@ -175,8 +175,8 @@ int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int3
 }
 
 int lffn_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype,
-                            float *const *out_ptrs, int32_t n_owners, int64_t rows_per_owner, int32_t slab, int64_t N,
-                            int32_t I, int64_t S, int32_t d, lffn_stream_t stream) {
+                            float *const *out_ptrs, int32_t n_owners, int64_t rows_per_owner, int32_t slab,
+                            int32_t first_owner, int64_t N, int32_t I, int64_t S, int32_t d, lffn_stream_t stream) {
     int rc = check_gather(N, I, S, d, table_dtype);
     if (rc != LFFN_OK) return rc;
     LFFN_REQUIRE(n_owners >= 1 && rows_per_owner >= 1 && (int64_t)n_owners * rows_per_owner >= N, LFFN_ERR_INVALID_ARG,
@@ -187,7 +187,9 @@ int lffn_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tabl
                  LFFN_ERR_INVALID_ARG, "gather_fwd_scatter: NULL buffer");
     LFFN_REQUIRE(aligned16(tables), LFFN_ERR_INVALID_ARG, "gather_fwd_scatter: tables must be 16-byte aligned");
     LFFN_REQUIRE(slab < n_owners, LFFN_ERR_INVALID_ARG, "gather_fwd_scatter: slab %d outside [0, %d)", slab, n_owners);
-    return launch_gather_fwd_scatter(idx, w, tables, table_dtype, out_ptrs, rows_per_owner, slab, N, I, S, d,
+    LFFN_REQUIRE(first_owner >= 0 && first_owner < n_owners, LFFN_ERR_INVALID_ARG,
+                 "gather_fwd_scatter: first_owner %d outside [0, %d)", first_owner, n_owners);
+    return launch_gather_fwd_scatter(idx, w, tables, table_dtype, out_ptrs, rows_per_owner, slab, first_owner, N, I, S, d,
                                      static_cast<cudaStream_t>(stream));
 }
 

@@ -39,7 +39,8 @@ uint32_t *status_word();  // device pointer to this device's status word (alloca
 int launch_gather_fwd(const int32_t *idx, const float *w, const void *tables, int table_dtype, void *out,
                       int out_dtype, int64_t N, int I, int64_t S, int d, const float *bias, cudaStream_t st);
 int launch_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tables, int table_dtype,
-                              float *const *peers, long long rows_per_owner, int slab, int64_t N, int I, int64_t S,
+                              float *const *peers, long long rows_per_owner, int slab, int first_owner, int64_t N,
+                              int I, int64_t S,
                               int d, cudaStream_t st);
 int launch_hash_fwd(const lffn_hash_desc &h, const void *x, int x_dtype, int64_t N, int t_begin, int t_count,
                     int32_t *idx_out, float *w_out, float *z_out, cudaStream_t st);

@@ -16,6 +16,8 @@
 // resident warps sweep i = 0..I-1 at about the same pace, so at any time the rows being read
 // come from a narrow band of tables, which keeps them L2-resident across the concurrently
 // processed tokens even when the whole table set exceeds L2.
+#include <cstdlib>
+
 #include "common.cuh"
 
 // Tuning constants (overridable at compile time): rows in flight per warp for narrow / medium /
@@ -38,6 +40,9 @@
 
 namespace lffn {
 
+// internal value of the kernel's `slab` argument: add mode carried out with one bulk reduction per row
+constexpr int LFFN_SLAB_BULK_ADD = -2;
+
 // 16-byte vector reduction into global memory, which may be another GPU's memory mapped over NVLink
 __device__ __forceinline__ void red_add_v4_f32(float *p, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
@@ -54,7 +59,7 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
                                                          const float *__restrict__ bias, const int2 *__restrict__ seg,
                                                          int i0, int icnt, int resume, int finish, uint32_t *status,
                                                          float *const *__restrict__ peers, long long rows_per_owner,
-                                                         int slab) {
+                                                         int slab, long long rot) {
     // i0/icnt: the slice of each token's index list this launch consumes; resume: start from the fp32 partial
     // sums already in `out`; finish: last slice, add the bias and convert (see launch_vpl_f on why lists are sliced)
     constexpr int EPV = Elem<TableT>::PER_VEC;
@@ -67,7 +72,10 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
     const uint4 *tv = reinterpret_cast<const uint4 *>(tables) + col0;
     bool bad = false;
 
-    for (long long n = warp0; n < N; n += nwarps) {
+    for (long long ni = warp0; ni < N; ni += nwarps) {
+        // SCATTER: tokens are taken in rotated order (start at token `rot`), so that ranks running this kernel at
+        // the same time, each with its own rotation, send to different owners at any moment
+        const long long n = SCATTER ? (ni + rot >= N ? ni + rot - N : ni + rot) : ni;
         float acc[VPL][EPV];
 #pragma unroll
         for (int v = 0; v < VPL; v++)
@@ -164,6 +172,36 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
             // `slab` of the owner's [n_ranks, rows_per_owner, d] staging buffer (the owner sums the slabs afterwards)
             const long long row = (slab < 0 ? 0 : (long long)slab * rows_per_owner) + n % rows_per_owner;
             float *prow = peers[n / rows_per_owner] + row * d + (long long)col0 * EPV;
+            if (slab == LFFN_SLAB_BULK_ADD) {
+                // One bulk reduction per row instead of 16-byte ones: the warp parks its fp32 row in shared memory
+                // and lane 0 hands it to the TMA unit, which adds it into the owner's row (cp.reduce.async.bulk,
+                // f32 add) as one transfer of up to 8 KB -- far fewer, larger packets on NVLink.
+                extern __shared__ __align__(16) float stage_all[];
+                float *stage = stage_all + (threadIdx.x >> 5) * (VPL * 32 * EPV);
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous row left smem
+                __syncwarp();
+#pragma unroll
+                for (int v = 0; v < VPL; v++) {
+                    const int c = lane + 32 * v;
+                    if (c < nvec) {
+#pragma unroll
+                        for (int q = 0; q < EPV / 4; q++)
+                            *reinterpret_cast<float4 *>(stage + c * EPV + 4 * q) =
+                                make_float4(acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2], acc[v][4 * q + 3]);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    const unsigned bytes = (unsigned)(nvec * EPV * sizeof(float));
+                    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(
+                                     __cvta_generic_to_global(prow)),
+                                 "r"((unsigned)__cvta_generic_to_shared(stage)), "r"(bytes)
+                                 : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                continue;
+            }
 #pragma unroll
             for (int v = 0; v < VPL; v++) {
                 const int c = lane + 32 * v;
@@ -216,6 +254,10 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
             }
         }
     }
+    if constexpr (SCATTER) {
+        // the bulk reductions of this thread have left shared memory and completed before the CTA exits
+        if (slab == LFFN_SLAB_BULK_ADD && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
     if (bad) atomicOr(status, LFFN_STATUS_INDEX_RANGE);
 }
 
@@ -255,7 +297,7 @@ static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, 
         const int icnt = I - i0 < per ? I - i0 : per;
         kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, w, static_cast<const TableT *>(tables), static_cast<OutT *>(out), N,
                                                  I, S, d, col0, bias, seg, i0, icnt, i0 > 0 ? 1 : 0,
-                                                 i0 + icnt >= I ? 1 : 0, status, nullptr, 0, -1);
+                                                 i0 + icnt >= I ? 1 : 0, status, nullptr, 0, -1, 0);
         LFFN_CHECK_CUDA(cudaGetLastError());
         if (I == 0) break;
     }
@@ -264,7 +306,7 @@ static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, 
 
 template <typename TableT, int VPL, bool FULLV>
 static int launch_scatter_f(const int32_t *idx, const float *w, const void *tables, float *const *peers,
-                            long long rows_per_owner, int slab, int64_t N, int I, int64_t S, int d, int col0,
+                            long long rows_per_owner, int slab, long long rot, int64_t N, int I, int64_t S, int d, int col0,
                             cudaStream_t st) {
     // rows in flight per warp; 2 KB bf16 rows (VPL = 4) measured best with 3 (config-5 shape: 2.41 -> 2.14 ms)
     constexpr int U = (VPL <= 3) ? LFFN_GATHER_U_NARROW
@@ -281,15 +323,25 @@ static int launch_scatter_f(const int32_t *idx, const float *w, const void *tabl
     if (grid < 1) grid = 1;
     uint32_t *status = status_word();
     LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
-    kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, w, static_cast<const TableT *>(tables), nullptr, N, I, S, d, col0, nullptr,
-                                             nullptr, 0, I, 0, 1, status, peers, rows_per_owner, slab);
+    // add mode: one bulk reduction per row (default) or 16-byte vector reductions (LFFN_SCATTER_VECTOR_RED=1)
+    static const bool vector_red = [] { const char *e = getenv("LFFN_SCATTER_VECTOR_RED"); return e && e[0] == '1'; }();
+    const int slab_k = (slab < 0 && !vector_red) ? LFFN_SLAB_BULK_ADD : slab;
+    const size_t smem = slab_k == LFFN_SLAB_BULK_ADD ? (size_t)(THREADS / 32) * VPL * 32 * Elem<TableT>::PER_VEC * sizeof(float) : 0;
+    if (smem > 48 * 1024) LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem));
+    if (per_sm < 1) per_sm = 1;
+    grid = (long long)num_sms() * per_sm;
+    if (grid > want) grid = want;
+    if (grid < 1) grid = 1;
+    kern<<<(unsigned)grid, THREADS, smem, st>>>(idx, w, static_cast<const TableT *>(tables), nullptr, N, I, S, d, col0, nullptr,
+                                                nullptr, 0, I, 0, 1, status, peers, rows_per_owner, slab_k, rot);
     LFFN_CHECK_CUDA(cudaGetLastError());
     return LFFN_OK;
 }
 
 template <typename TableT>
 static int launch_scatter_typed(const int32_t *idx, const float *w, const void *tables, float *const *peers,
-                                long long rows_per_owner, int slab, int64_t N, int I, int64_t S, int d, cudaStream_t st) {
+                                long long rows_per_owner, int slab, long long rot, int64_t N, int I, int64_t S, int d, cudaStream_t st) {
     constexpr int EPV = Elem<TableT>::PER_VEC;
     const int row_vecs = d / EPV;
     constexpr int MAXV = 8;
@@ -299,8 +351,8 @@ static int launch_scatter_typed(const int32_t *idx, const float *w, const void *
         const bool full = nvec == vpl * 32;
         int rc;
 #define LFFN_SCATTER_CASE(V)                                                                                              \
-    rc = full ? launch_scatter_f<TableT, V, true>(idx, w, tables, peers, rows_per_owner, slab, N, I, S, d, col0, st)      \
-              : launch_scatter_f<TableT, V, false>(idx, w, tables, peers, rows_per_owner, slab, N, I, S, d, col0, st)
+    rc = full ? launch_scatter_f<TableT, V, true>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st)      \
+              : launch_scatter_f<TableT, V, false>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st)
         switch (vpl) {
             case 1: LFFN_SCATTER_CASE(1); break;
             case 2: LFFN_SCATTER_CASE(2); break;
@@ -317,12 +369,13 @@ static int launch_scatter_typed(const int32_t *idx, const float *w, const void *
 }
 
 int launch_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tables, int table_dtype,
-                              float *const *peers, long long rows_per_owner, int slab, int64_t N, int I, int64_t S,
-                              int d, cudaStream_t st) {
+                              float *const *peers, long long rows_per_owner, int slab, int first_owner, int64_t N, int I,
+                              int64_t S, int d, cudaStream_t st) {
+    const long long rot = N > 0 ? ((long long)first_owner * rows_per_owner) % N : 0;
     if (table_dtype == LFFN_F32)
-        return launch_scatter_typed<float>(idx, w, tables, peers, rows_per_owner, slab, N, I, S, d, st);
+        return launch_scatter_typed<float>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, st);
     if (table_dtype == LFFN_BF16)
-        return launch_scatter_typed<__nv_bfloat16>(idx, w, tables, peers, rows_per_owner, slab, N, I, S, d, st);
+        return launch_scatter_typed<__nv_bfloat16>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, st);
     set_error("gather_fwd_scatter: unknown table dtype %d", table_dtype);
     return LFFN_ERR_INVALID_ARG;
 }

@@ -142,8 +142,9 @@ class TableShardedLookupFFN(nn.Module):
             from . import _lib as L
             with torch.cuda.device(u.device):
                 L.check(L.lib().lffn_gather_fwd_scatter(L.ptr(idx), L.ptr(w), L.ptr(flat), L.dtype_code(flat.dtype),
-                                                        L.ptr(peers.ptr_array), world, peers.rows, -1, N, idx.shape[1],
-                                                        flat.shape[0], self.output_size, L.stream_ptr(u.device)))
+                                                        L.ptr(peers.ptr_array), world, peers.rows, -1,
+                                                        (peers.rank + 1) % world, N, idx.shape[1], flat.shape[0],
+                                                        self.output_size, L.stream_ptr(u.device)))
             rank = dist.get_rank(self.group)
             return peers.finish().clone(), torch.arange(rank * peers.rows, (rank + 1) * peers.rows)
 
@@ -260,7 +261,7 @@ class PeerOutput:
 def lookup_forward_table_sharded_fused(x, desc, tables_local, t_begin, t_count, peers, bias=None):
     """The table-sharded forward with the exchange step of the reduce-scatter fused into the gather kernel: each
     rank's gather sends its partial rows straight to the owner's buffer through peer-mapped memory over NVLink
-    (plain stores into its slab, or in-place vector reductions), so the [N, d] partial sums are never written to
+    (plain stores into its slab, or one in-place bulk reduction per row), so the [N, d] partial sums are never written to
     or read from this GPU's HBM and no NCCL collective moves data.  Token n is owned by rank n // (N / world).
     Returns this rank's [N/world, d] fp32 rows."""
     from . import _lib as L
@@ -276,5 +277,6 @@ def lookup_forward_table_sharded_fused(x, desc, tables_local, t_begin, t_count, 
     with torch.cuda.device(x.device):
         L.check(L.lib().lffn_gather_fwd_scatter(L.ptr(idx), L.ptr(w), L.ptr(tables_local),
                                                 L.dtype_code(tables_local.dtype), L.ptr(peers.ptr_array), peers.world,
-                                                peers.rows, slab, N, idx.shape[1], S, d, L.stream_ptr(x.device)))
+                                                peers.rows, slab, (peers.rank + 1) % peers.world, N, idx.shape[1], S, d,
+                                                L.stream_ptr(x.device)))
     return peers.finish(bias if peers.mode == "store" else None)
