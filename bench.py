@@ -404,7 +404,7 @@ def run_table_sharded(args, rank, world, local):
 
 
 def run_train_gather(args, rank, world, local):
-    """BASELINE config 4: training-mode weighted gather-add, forward and backward, fp32: N=16384 tokens, d=768,
+    """Benchmark configuration 4: training-mode weighted gather-add, forward and backward, fp32: N=16384 tokens, d=768,
     T=512, k=8, m=k+1 soft-flip candidates per (token, table) (tau=0.5), upstream gradient dy ~ N(0,1).
     One step = candidates/weights (hash kernel) + gather forward + gradient of the weights + gradient of the
     tables (sorted, deterministic)."""
@@ -581,7 +581,7 @@ def encoder_gpu_comparator(model, step, B, S, cfg, device):
 
 
 def run_encoder(args, rank, world, local):
-    """BASELINE config 2: RoBERTa-small prenorm encoder inference with every FFN a LookupFFN (4 layers, hidden
+    """Benchmark configuration 2: RoBERTa-small prenorm encoder inference with every FFN a LookupFFN (4 layers, hidden
     512, 8 heads, seq 512, batch 32 per GPU, T=256, k=8, fp32 tables, reference BH4 projection).  seq/s."""
     from argparse import Namespace
 

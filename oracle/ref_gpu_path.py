@@ -1,6 +1,6 @@
 """The reference's GPU evaluation of a LookupFFN layer, restated around the reference's own CUDA kernels.
 
-TEST / BASELINE INFRASTRUCTURE: used by tests and by the benchmark's baseline leg as the GPU comparator; the
+TEST AND COMPARATOR INFRASTRUCTURE: used by tests and by the benchmark's baseline leg as the GPU comparator; the
 product never calls it.
 
 The reference's Python cannot travel to the GPU machine, its compiled CUDA extensions (oracle/_ref) can.  This
