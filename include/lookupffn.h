@@ -92,8 +92,18 @@ typedef struct lffn_hash_desc {
 int lffn_version(void);
 const char *lffn_last_error_string(void);
 
-/* Reads and clears the status word of the current device (synchronises `stream`). */
+/* Reads and clears the status word of the current device with one atomic exchange on `stream`, then
+ * synchronises `stream`.  A flag raised concurrently by a kernel on another stream is never lost: it is either in
+ * this value or in the next one. */
 int lffn_device_status(uint32_t *status_out, lffn_stream_t stream);
+
+/*
+ * Self-test of the kernels' bounded waits (no reference counterpart).  Launches one tiny kernel whose only wait is
+ * on a barrier nobody will ever signal, with `poll_limit` polls (1 .. 2^20); the wait gives up, the kernel sets
+ * LFFN_STATUS_TIMEOUT in the device status word and ends normally.  Shows that a wait that runs out surfaces as a
+ * status bit and leaves the device usable.  No memory is touched and nothing else is in flight.
+ */
+int lffn_selftest_bounded_wait(int32_t poll_limit, lffn_stream_t stream);
 
 /*
  * Walsh-Hadamard transform of each row, out = x H_D * scale.  Replaces
@@ -152,10 +162,12 @@ int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int3
  * token n goes to the rank that owns it, n / rows_per_owner, through out_ptrs, a DEVICE array of n_owners fp32
  * buffer addresses, one per rank, all mapped into this process (peer / symmetric memory over NVLink; the local
  * one included).
- *   slab < 0:  buffers are [rows_per_owner, d]; the row is ADDED in place: the warp parks its fp32 row in shared
- *              memory and one bulk reduction (cp.reduce.async.bulk, f32 add) carries it to the owner.  They must
- *              hold their initial value (zeros or the bias) on every rank before any rank starts; the order of
- *              summation across ranks is not fixed.
+ *   slab = -1: buffers are [rows_per_owner, d]; the row is ADDED in place: the warp parks its fp32 row in shared
+ *              memory and one bulk reduction (cp.reduce.async.bulk, f32 add) carries it to the owner.  The buffers
+ *              must hold their initial value (zeros or the bias) on every rank before any rank starts; the order
+ *              of summation across ranks is not fixed.
+ *   slab = -2: the same in-place add, carried out with 16-byte vector reductions (red.global.add.v4.f32): many
+ *              small packets instead of one large one (slower over NVLink; kept for comparison).
  *   slab >= 0: buffers are [n_owners, rows_per_owner, d]; the row is STORED (plain 16-byte stores) into slab
  *              `slab` (the caller's rank).  The owner then sums its slabs in rank order: deterministic.
  * first_owner in [0, n_owners): the call walks the tokens starting with those of this owner and wraps around.
@@ -201,15 +213,19 @@ int lffn_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const floa
 /*
  * The sorted table gradient for callers that are not allowed to allocate device memory.  (No counterpart in
  * the reference: its scatter-add needs no scratch.)  Such callers exist: a plugin running inside a host
- * whose memory pool is fixed at start-up, code on a stream that is being captured, a real-time loop that
- * must not take the allocator's lock.  They cannot hand lffn_gather_bwd_tables_sorted its scratch buffer, so
+ * that took all device memory into its own pool at start-up (cudaMalloc fails there, or is forbidden), a
+ * real-time loop that must not take the allocator's lock.  They cannot hand lffn_gather_bwd_tables_sorted its scratch buffer, so
  * this variant sorts into an array compiled into the library, LFFN_STATIC_SCRATCH_BYTES (32 MiB) long; every
  * GPU that loads the library holds those bytes until the process exits.  Same arguments and bit-identical
  * result.  It calls no cudaMalloc/cudaFree and no allocating library routine.
  *   - Limit: lffn_gather_bwd_tables_sorted_scratch_bytes(N, T, m, rows) <= LFFN_STATIC_SCRATCH_BYTES, about
  *     N*T*m <= 4.1 million entries; larger problems return LFFN_ERR_SCRATCH with the sizes in the message.
- *   - The first call on each device looks up the array's device address (one runtime query, no
- *     allocation); make that first call outside any stream capture.
+ *   - The array's 32 MiB are reserved on a device when the CUDA runtime loads the library's code there, which
+ *     (with the runtime's default lazy loading) happens at the first use on that device, not when the shared
+ *     library is opened: a host with a fixed pool sees free device memory drop by the size of the library image
+ *     on that first use.  The first call of this function on a device also looks up the array's device address
+ *     (one runtime query).  So make one warm-up call per device at start-up, outside any stream capture; every
+ *     later call allocates nothing and leaves free device memory unchanged.
  *   - All calls on a device share the one array and find the previous call's bytes in it.  Nothing needs
  *     clearing (every word a call reads it has written first), but two calls whose kernels overlap on the
  *     GPU (different streams, or two host threads) race on it: serialise them.

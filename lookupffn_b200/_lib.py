@@ -41,6 +41,7 @@ _SIGNATURES = {
     "lffn_version": (C.c_int, []),
     "lffn_last_error_string": (C.c_char_p, []),
     "lffn_device_status": (C.c_int, [C.POINTER(C.c_uint32), C.c_void_p]),
+    "lffn_selftest_bounded_wait": (C.c_int, [C.c_int32, C.c_void_p]),
     "lffn_fwht": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]),
     "lffn_hash_fwd": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -1,5 +1,6 @@
 // extern "C" entry points of liblookupffn.so (declared in include/lookupffn.h): argument checks,
 // error strings, the device status word, and the two whole-layer drivers.
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -23,32 +24,57 @@ int cuda_fail(cudaError_t e, const char *what) {
 
 constexpr int MAX_DEV = 64;
 
+// Per-device caches are atomics: two host threads that meet on the first call both compute the same value and
+// either store wins.
 int num_sms() {
-    static int cache[MAX_DEV] = {0};
+    static std::atomic<int> cache[MAX_DEV];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return 148;
-    if (cache[dev] == 0) {
-        int n = 0;
+    int n = cache[dev].load(std::memory_order_acquire);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cache[dev] = n;
+        cache[dev].store(n, std::memory_order_release);
     }
-    return cache[dev];
+    return n;
 }
 
 // The status word is a __device__ variable (one per device that loads the library), not an
 // allocation: kernels OR flags into it, lffn_device_status reads and clears it.
 __device__ uint32_t g_status_word = 0;
+// lffn_device_status takes the word with one atomic exchange and parks the value in one of these slots for the
+// copy to the host; concurrent readers get different slots.
+constexpr int STATUS_SLOTS = 64;
+__device__ uint32_t g_status_slots[STATUS_SLOTS];
+
+__global__ void status_take_kernel(uint32_t *slot) { *slot = atomicExch(&g_status_word, 0u); }
 
 uint32_t *status_word() {
-    static uint32_t *cache[MAX_DEV] = {nullptr};
+    static std::atomic<uint32_t *> cache[MAX_DEV];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return nullptr;
-    if (cache[dev] == nullptr) {
+    uint32_t *w = cache[dev].load(std::memory_order_acquire);
+    if (w == nullptr) {
         void *p = nullptr;
         if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
-        cache[dev] = static_cast<uint32_t *>(p);
+        w = static_cast<uint32_t *>(p);
+        cache[dev].store(w, std::memory_order_release);
     }
-    return cache[dev];
+    return w;
+}
+
+static uint32_t *status_slot() {
+    static std::atomic<uint32_t *> base[MAX_DEV];
+    static std::atomic<unsigned> next{0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return nullptr;
+    uint32_t *b = base[dev].load(std::memory_order_acquire);
+    if (b == nullptr) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_slots) != cudaSuccess) return nullptr;
+        b = static_cast<uint32_t *>(p);
+        base[dev].store(b, std::memory_order_release);
+    }
+    return b + next.fetch_add(1, std::memory_order_relaxed) % STATUS_SLOTS;
 }
 
 static int check_hash_desc(const lffn_hash_desc *h, int t_begin, int t_count) {
@@ -101,12 +127,21 @@ const char *lffn_last_error_string(void) { return g_err; }
 int lffn_device_status(uint32_t *status_out, lffn_stream_t stream) {
     LFFN_REQUIRE(status_out != nullptr, LFFN_ERR_INVALID_ARG, "status_out is NULL");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    uint32_t *dev = status_word();
-    LFFN_REQUIRE(dev != nullptr, LFFN_ERR_CUDA, "no CUDA device");
-    LFFN_CHECK_CUDA(cudaMemcpyAsync(status_out, dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
-    LFFN_CHECK_CUDA(cudaMemsetAsync(dev, 0, sizeof(uint32_t), st));
+    uint32_t *slot = status_slot();
+    LFFN_REQUIRE(slot != nullptr, LFFN_ERR_CUDA, "no CUDA device");
+    // read and clear in one atomic exchange: a flag that a kernel on another stream raises meanwhile is either in
+    // this value or still in the word for the next reader, never lost
+    status_take_kernel<<<1, 1, 0, st>>>(slot);
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    LFFN_CHECK_CUDA(cudaMemcpyAsync(status_out, slot, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
     LFFN_CHECK_CUDA(cudaStreamSynchronize(st));
     return LFFN_OK;
+}
+
+int lffn_selftest_bounded_wait(int32_t poll_limit, lffn_stream_t stream) {
+    LFFN_REQUIRE(poll_limit >= 1 && poll_limit <= (1 << 20), LFFN_ERR_INVALID_ARG,
+                 "selftest_bounded_wait: poll_limit %d outside [1, 2^20]", poll_limit);
+    return launch_bounded_wait_selftest(poll_limit, static_cast<cudaStream_t>(stream));
 }
 
 int lffn_fwht(const void *x, void *out, int64_t N, int32_t D, int32_t dtype, float scale, lffn_stream_t stream) {
@@ -186,7 +221,8 @@ int lffn_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tabl
     LFFN_REQUIRE(tables != nullptr && out_ptrs != nullptr && (I == 0 || (idx != nullptr && w != nullptr)),
                  LFFN_ERR_INVALID_ARG, "gather_fwd_scatter: NULL buffer");
     LFFN_REQUIRE(aligned16(tables), LFFN_ERR_INVALID_ARG, "gather_fwd_scatter: tables must be 16-byte aligned");
-    LFFN_REQUIRE(slab < n_owners, LFFN_ERR_INVALID_ARG, "gather_fwd_scatter: slab %d outside [0, %d)", slab, n_owners);
+    LFFN_REQUIRE(slab >= -2 && slab < n_owners, LFFN_ERR_INVALID_ARG,
+                 "gather_fwd_scatter: slab %d is neither an add mode (-1, -2) nor a slab in [0, %d)", slab, n_owners);
     LFFN_REQUIRE(first_owner >= 0 && first_owner < n_owners, LFFN_ERR_INVALID_ARG,
                  "gather_fwd_scatter: first_owner %d outside [0, %d)", first_owner, n_owners);
     return launch_gather_fwd_scatter(idx, w, tables, table_dtype, out_ptrs, rows_per_owner, slab, first_owner, N, I, S, d,
@@ -274,24 +310,44 @@ int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t 
                  lffn_layer_fwd_host_ws_bytes(desc, x_dtype, out_dtype, d_out, chunk_tokens), ws_bytes);
     if (N == 0) return LFFN_OK;
 
+    // The lanes of a device are created once and shared by all calls on that device, so one host-buffer call runs
+    // at a time per device (calls on different devices do not wait for each other).
     struct Lanes {
         cudaStream_t s[HOST_LANES] = {};
         cudaEvent_t done[HOST_LANES] = {};
         cudaEvent_t start = nullptr;
+        bool ready = false;
+        void destroy() {
+            for (int i = 0; i < HOST_LANES; i++) {
+                if (done[i]) cudaEventDestroy(done[i]);
+                if (s[i]) cudaStreamDestroy(s[i]);
+                done[i] = nullptr;
+                s[i] = nullptr;
+            }
+            if (start) cudaEventDestroy(start);
+            start = nullptr;
+        }
     };
     static Lanes lanes[MAX_DEV];
-    static std::mutex mu;
+    static std::mutex mu[MAX_DEV];
     int dev = 0;
     LFFN_CHECK_CUDA(cudaGetDevice(&dev));
     LFFN_REQUIRE(dev >= 0 && dev < MAX_DEV, LFFN_ERR_UNSUPPORTED, "device ordinal %d", dev);
-    std::lock_guard<std::mutex> lock(mu);  // one host-buffer call at a time per process: the lanes are shared
+    std::lock_guard<std::mutex> lock(mu[dev]);
     Lanes &L = lanes[dev];
-    if (L.s[0] == nullptr) {
-        for (int i = 0; i < HOST_LANES; i++) {
-            LFFN_CHECK_CUDA(cudaStreamCreateWithFlags(&L.s[i], cudaStreamNonBlocking));
-            LFFN_CHECK_CUDA(cudaEventCreateWithFlags(&L.done[i], cudaEventDisableTiming));
+    if (!L.ready) {  // built in a local and published only when every stream and event exists
+        Lanes fresh;
+        cudaError_t e = cudaEventCreateWithFlags(&fresh.start, cudaEventDisableTiming);
+        for (int i = 0; i < HOST_LANES && e == cudaSuccess; i++) {
+            e = cudaStreamCreateWithFlags(&fresh.s[i], cudaStreamNonBlocking);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&fresh.done[i], cudaEventDisableTiming);
         }
-        LFFN_CHECK_CUDA(cudaEventCreateWithFlags(&L.start, cudaEventDisableTiming));
+        if (e != cudaSuccess) {
+            fresh.destroy();
+            return cuda_fail(e, "creating the streams of lffn_layer_fwd_host");
+        }
+        L = fresh;
+        L.ready = true;
     }
     cudaStream_t user = static_cast<cudaStream_t>(stream);
     LFFN_CHECK_CUDA(cudaEventRecord(L.start, user));
@@ -300,7 +356,21 @@ int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t 
     const size_t ob = up256((size_t)chunk_tokens * d_out * esize(out_dtype));
     const size_t ib = up256((size_t)chunk_tokens * desc->T * m * 4);
     const size_t per_lane = xb + ob + 2 * ib;
-    for (int i = 0; i < HOST_LANES; i++) LFFN_CHECK_CUDA(cudaStreamWaitEvent(L.s[i], L.start, 0));
+    // From the first enqueue on, an error must not return while copies into out_host may still be in flight:
+    // every exit below goes through `finish`, which waits for all lanes.
+    auto finish = [&](int code) -> int {
+        for (int i = 0; i < HOST_LANES; i++) {
+            const cudaError_t e = cudaStreamSynchronize(L.s[i]);
+            if (e != cudaSuccess && code == LFFN_OK) code = cuda_fail(e, "cudaStreamSynchronize(lane)");
+        }
+        return code;
+    };
+#define LFFN_HOST_CUDA(expr)                                          \
+    do {                                                              \
+        cudaError_t _e = (expr);                                      \
+        if (_e != cudaSuccess) return finish(cuda_fail(_e, #expr));   \
+    } while (0)
+    for (int i = 0; i < HOST_LANES; i++) LFFN_HOST_CUDA(cudaStreamWaitEvent(L.s[i], L.start, 0));
     int64_t c = 0;
     for (int64_t n0 = 0; n0 < N; n0 += chunk_tokens, c++) {
         const int lane = (int)(c % HOST_LANES);
@@ -312,16 +382,17 @@ int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t 
         float *ww = reinterpret_cast<float *>(base + xb + ob + ib);
         const char *xs = static_cast<const char *>(x_host) + (size_t)n0 * desc->d_in * esize(x_dtype);
         char *os = static_cast<char *>(out_host) + (size_t)n0 * d_out * esize(out_dtype);
-        LFFN_CHECK_CUDA(cudaMemcpyAsync(xd, xs, (size_t)nt * desc->d_in * esize(x_dtype), cudaMemcpyHostToDevice, L.s[lane]));
+        LFFN_HOST_CUDA(cudaMemcpyAsync(xd, xs, (size_t)nt * desc->d_in * esize(x_dtype), cudaMemcpyHostToDevice, L.s[lane]));
         rc = lffn_layer_fwd(desc, xd, x_dtype, nt, 0, desc->T, tables, table_dtype, d_out, bias, od, out_dtype, iw, ww,
                             L.s[lane]);
-        if (rc != LFFN_OK) return rc;
-        LFFN_CHECK_CUDA(cudaMemcpyAsync(os, od, (size_t)nt * d_out * esize(out_dtype), cudaMemcpyDeviceToHost, L.s[lane]));
+        if (rc != LFFN_OK) return finish(rc);
+        LFFN_HOST_CUDA(cudaMemcpyAsync(os, od, (size_t)nt * d_out * esize(out_dtype), cudaMemcpyDeviceToHost, L.s[lane]));
     }
     for (int i = 0; i < HOST_LANES; i++) {
-        LFFN_CHECK_CUDA(cudaEventRecord(L.done[i], L.s[i]));
-        LFFN_CHECK_CUDA(cudaStreamWaitEvent(user, L.done[i], 0));
+        LFFN_HOST_CUDA(cudaEventRecord(L.done[i], L.s[i]));
+        LFFN_HOST_CUDA(cudaStreamWaitEvent(user, L.done[i], 0));
     }
+#undef LFFN_HOST_CUDA
     LFFN_CHECK_CUDA(cudaStreamSynchronize(user));
     return LFFN_OK;
 }

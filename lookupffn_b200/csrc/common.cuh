@@ -48,6 +48,7 @@ int launch_code_weights(const float *z, int64_t N, int T, int k, int bit_order, 
                         int add_offsets, int32_t *idx_out, float *w_out, cudaStream_t st);
 int launch_code_weights_bwd(const float *z, const float *dw, int64_t N, int T, int k, int weight_mode, float tau,
                             float *dz, cudaStream_t st);
+int launch_bounded_wait_selftest(int poll_limit, cudaStream_t st);
 int launch_fwht(const void *x, void *out, int64_t N, int D, int dtype, float scale, cudaStream_t st);
 int launch_gather_bwd_weights(const int32_t *idx, const float *dy, const void *tables, int table_dtype, float *dw,
                               int64_t N, int I, int64_t S, int d, cudaStream_t st);

@@ -16,8 +16,6 @@
 // resident warps sweep i = 0..I-1 at about the same pace, so at any time the rows being read
 // come from a narrow band of tables, which keeps them L2-resident across the concurrently
 // processed tokens even when the whole table set exceeds L2.
-#include <cstdlib>
-
 #include "common.cuh"
 
 // Tuning constants (overridable at compile time): rows in flight per warp for narrow / medium /
@@ -40,8 +38,9 @@
 
 namespace lffn {
 
-// internal value of the kernel's `slab` argument: add mode carried out with one bulk reduction per row
-constexpr int LFFN_SLAB_BULK_ADD = -2;
+// values of `slab` below zero select how a row is added into the owner's buffer (lffn_gather_fwd_scatter):
+constexpr int LFFN_SLAB_BULK_ADD = -1;    // one bulk reduction per row
+constexpr int LFFN_SLAB_VECTOR_ADD = -2;  // 16-byte vector reductions
 
 // 16-byte vector reduction into global memory, which may be another GPU's memory mapped over NVLink
 __device__ __forceinline__ void red_add_v4_f32(float *p, float a, float b, float c, float d) {
@@ -323,9 +322,7 @@ static int launch_scatter_f(const int32_t *idx, const float *w, const void *tabl
     if (grid < 1) grid = 1;
     uint32_t *status = status_word();
     LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
-    // add mode: one bulk reduction per row (default) or 16-byte vector reductions (LFFN_SCATTER_VECTOR_RED=1)
-    static const bool vector_red = [] { const char *e = getenv("LFFN_SCATTER_VECTOR_RED"); return e && e[0] == '1'; }();
-    const int slab_k = (slab < 0 && !vector_red) ? LFFN_SLAB_BULK_ADD : slab;
+    const int slab_k = slab;
     const size_t smem = slab_k == LFFN_SLAB_BULK_ADD ? (size_t)(THREADS / 32) * VPL * 32 * Elem<TableT>::PER_VEC * sizeof(float) : 0;
     if (smem > 48 * 1024) LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem));

@@ -14,14 +14,12 @@
 // Weights of 256 output columns (PC/BS blocks) are staged per pass into shared memory as
 // Ws[g][i][o] with a 16-byte XOR swizzle, from either global layout ([o][i] or [i][o]).
 // No tensor cores: sign bits must reproduce the fp32 fmaf chain.
-#include <cstdlib>
-
 #include "common.cuh"
 #include "hash_common.cuh"
 
 namespace lffn {
 
-// Optional phase clocks (compile with -DLFFN_HB_PHASE_CLOCKS, see lookupffn_b200/phase_clocks.py): thread 0 of
+// Optional phase clocks (compile with -DLFFN_HB_PHASE_CLOCKS; a profiling build, never the shipped one): thread 0 of
 // every CTA adds the clock64 cycles between consecutive marks to a per-phase counter.  Off by default.
 #ifdef LFFN_HB_PHASE_CLOCKS
 __device__ unsigned long long g_hb_phase[8];
@@ -315,9 +313,9 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 constexpr int MBAR_POLL_LIMIT = 1 << 22;  // polls of a few tens of ns each: gives up after about 0.1 - 0.2 s
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity) {
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity, int limit = MBAR_POLL_LIMIT) {
     const unsigned addr = smem_u32(bar);
-    for (int it = 0; it < MBAR_POLL_LIMIT; it++) {
+    for (int it = 0; it < limit; it++) {
         unsigned done;
         asm volatile(
             "{\n"
@@ -438,8 +436,14 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
         if (lane == 0) ok = fetch_chunk(c, src) ? 1 : 0;
         return __shfl_sync(FULL, ok, 0) != 0;
     };
-    auto give_up = [&]() {
+    // A thread that gives up first waits (bounded again) for the chunks [from, to) that have been requested but not
+    // consumed, so that it does not leave while a bulk copy it issued is still writing into this CTA's shared
+    // memory: shared memory is released only when the last thread has left, and every issuer waits for its own copy
+    // either in the normal flow or here.
+    auto give_up = [&](long long from, long long to) {
         if (a.status != nullptr) atomicOr(a.status, LFFN_STATUS_TIMEOUT);
+        for (long long c = from; c < to && c < total_chunks; c++)
+            mbar_wait(&full[c % HF_NBUF], (unsigned)((c / HF_NBUF) & 1));
     };
 
     long long gc = 0;
@@ -478,13 +482,13 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                     for (int q = 0; q < 4; q++) acc[pp][q] = 0ull;
                 for (int h = 0; h < 64 / CR; h++) {
                     HB_MARK(HB_PH_FMA);
-                    if (!issue_chunk(gc + HF_NBUF - 1)) {
-                        give_up();
+                    if (!issue_chunk(gc + HF_NBUF - 1)) {  // that chunk was not requested; the ones before it were
+                        give_up(gc, gc + HF_NBUF - 1);
                         return;
                     }
                     const int buf = (int)(gc % HF_NBUF);
                     if (!mbar_wait(&full[buf], (unsigned)((gc / HF_NBUF) & 1))) {  // chunk gc has landed
-                        give_up();
+                        give_up(gc, gc + HF_NBUF);
                         return;
                     }
                     HB_MARK(HB_PH_CHUNK_WAIT);
@@ -535,6 +539,26 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     }
 }
 
+// Self-test of the bounded wait: one thread waits on an mbarrier that nobody will ever arrive on (no copy is in
+// flight, nothing else runs), with a small poll limit.  The wait must run out, set LFFN_STATUS_TIMEOUT and return,
+// leaving the context usable.
+__global__ void bounded_wait_selftest_kernel(int poll_limit, uint32_t *status) {
+    __shared__ unsigned long long bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait(&bar, 0u, poll_limit)) atomicOr(status, LFFN_STATUS_TIMEOUT);
+    }
+}
+
+int launch_bounded_wait_selftest(int poll_limit, cudaStream_t st) {
+    uint32_t *status = status_word();
+    LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
+    bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(poll_limit, status);
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return LFFN_OK;
+}
+
 int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, cudaStream_t st) {
     if (BS < 4 || BS > 128 || (BS & (BS - 1)) != 0 || a.D % BS != 0) {
         set_error("hash_fwd: block size %d unsupported (1, or a power of two in [4, 128] dividing D)", BS);
@@ -551,8 +575,7 @@ int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, c
     if (grid < 1) grid = 1;
     if (BS == 64 && transpose_w && a.D % 256 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0) {
         static_assert(2 * HF_CHUNK_FLOATS == HB_WFLOATS, "same shared-memory footprint as the generic kernel");
-        static const bool narrow_only = [] { const char *e = getenv("LFFN_BLOCK64_NARROW"); return e && e[0] == '1'; }();
-        const bool wide = a.D % 512 == 0 && !narrow_only;   // 512 threads: 16 warps per SM instead of 8
+        const bool wide = a.D % 512 == 0;   // 512 threads: 16 warps per SM instead of 8
         // the kernel splits (tile, rotation) units, or whole tiles when k does not divide D, evenly over the grid
         const long long nrot = a.r_hi - a.r_lo + 1;
         const long long groups = a.D % a.k == 0 ? ntiles * nrot : ntiles;

@@ -47,6 +47,7 @@ class BH4(nn.Module):
             torch.randn(self.num_repeat, self.num_stages, self.num_block, self.block_size, self.block_size) / coeff)
         self.bias = nn.Parameter(torch.zeros(self.out_dim))
         self.had_scale = 1.0
+        self.register_load_state_dict_post_hook(lambda module, _keys: module.refresh_kernel_weight())
 
     def extra_repr(self):
         return (f"in_dim={self.in_dim}, out_dim={self.out_dim}, block_size={self.block_size}, "
@@ -58,16 +59,22 @@ class BH4(nn.Module):
 
     def kernel_weight(self):
         """(weight tensor, transpose_w flag) to hand to the hash kernel.  The 64 x 64 fast path streams the
-        blocks in [i][o] order, so for that shape a transposed copy of the parameter is kept and refreshed
-        whenever the parameter changes (optimizer step, load_state_dict, .to())."""
+        blocks in [i][o] order, so for that shape a transposed copy of the parameter is kept.  It is refreshed when
+        the parameter's storage or version counter changes (optimizer step, .to()), after load_state_dict, and on
+        every call while the module is in training mode.  An in-place write through `weight.data` in eval mode
+        does not move the version counter: call refresh_kernel_weight() after one."""
         w = self.weight.detach()
         if self.block_size != 64 or self.padded_in_dim % 256 != 0:
             return w.contiguous(), False
         key = (w.data_ptr(), w._version, w.device)
-        if getattr(self, "_wt_key", None) != key:
+        if self.training or getattr(self, "_wt_key", None) != key:
             self._wt = w.transpose(-1, -2).contiguous()
             self._wt_key = key
         return self._wt, True
+
+    def refresh_kernel_weight(self):
+        """Drop the cached transposed weights; the next forward rebuilds them from the parameter."""
+        self._wt_key = None
 
     def forward(self, xs):
         """The projection alone, z [..., out_dim] (reference BH4.forward)."""

@@ -13,6 +13,9 @@ from ._lib import (BF16, F32, LSB_FIRST, MSB_FIRST, WEIGHT_ONES, WEIGHT_SCORE, W
                    LookupFFNError)
 
 
+SORTED_MAX_ROWS = 16384  # rows per table the sorted table-gradient kernel keeps counters for (csrc/gather_bwd.cu)
+
+
 def _contig(t):
     return t if t.is_contiguous() else t.contiguous()
 
@@ -289,7 +292,9 @@ def weighted_vector_scatter_add(indexes, source, weights, output_size, structure
     """outputs[indexes[b, i]] += weights[b, i] * source[b]; outputs fp32 [output_size, d].
     Reference: weighted_vector_scatter_add (gather/cuda/kernel.py:124-173).
     structure=(T, m, rows) declares the layer's index structure (entry (b, t*m+c) lies in table t of
-    `rows` rows) and selects the deterministic sorted kernel; None accepts any index list."""
+    `rows` rows) and selects the deterministic sorted kernel; None accepts any index list.  Shapes the sorted
+    kernel does not cover (more than SORTED_MAX_ROWS rows per table, or 2^31 entries and more) go to the
+    general kernel, as the reference's scatter-add handles any table size."""
     L.require_cuda(indexes, source, weights)
     assert indexes.dtype == torch.int32 and source.dtype == torch.float32 and weights.dtype == torch.float32
     indexes, source, weights = _contig(indexes), _contig(source), _contig(weights)
@@ -298,12 +303,15 @@ def weighted_vector_scatter_add(indexes, source, weights, output_size, structure
     out = torch.empty((output_size, d), dtype=torch.float32, device=source.device)
     lib = L.lib()
     with torch.cuda.device(source.device):
+        if structure is not None:
+            T, m, rows = structure
+            assert T * m == I and T * rows == output_size
+            if rows > SORTED_MAX_ROWS or N * I >= 2 ** 31:
+                structure = None
         if structure is None:
             L.check(lib.lffn_gather_bwd_tables(L.ptr(indexes), L.ptr(weights), L.ptr(source), L.ptr(out), N, I,
                                                output_size, d, L.stream_ptr(source.device)))
         else:
-            T, m, rows = structure
-            assert T * m == I and T * rows == output_size
             nbytes = lib.lffn_gather_bwd_tables_sorted_scratch_bytes(N, T, m, rows)
             scratch = torch.empty(nbytes, dtype=torch.uint8, device=source.device)
             L.check(lib.lffn_gather_bwd_tables_sorted(L.ptr(indexes), L.ptr(weights), L.ptr(source), L.ptr(out), N, T,

@@ -25,7 +25,8 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liblffn_oracle.so")
 REF_OUT = os.path.join(HERE, "_ref")
-REF_ROOT = os.environ.get("LFFN_REFERENCE_ROOT", "/root/reference")
+# where the reference checkout lives: LFFN_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REF_ROOT = os.environ.get("LFFN_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 REF_LOOKUP = os.path.join(REF_ROOT, "src", "roberta", "models", "prenorm_lookup")
 
 # AVX2+FMA rather than -march=native: the library is built on one machine and

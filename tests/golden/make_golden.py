@@ -36,7 +36,8 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("LFFN_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: LFFN_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REF = os.environ.get("LFFN_REFERENCE_ROOT") or os.path.join(os.path.dirname(REPO), "reference")
 OUT = os.path.join(HERE, "lookupffn_golden.npz")
 
 sys.path.insert(0, REPO)

@@ -1,12 +1,17 @@
 """The allocation-free table-gradient entry point, lffn_gather_bwd_tables_sorted_static.
 
-Some callers of this library may not allocate device memory while they run (a plugin inside a host with a
-fixed memory pool, code on a stream under capture, a latency-critical loop), so they cannot provide the
-scratch buffer the sorted table gradient sorts into.  For them the library carries a 32 MiB array of its
-own.  This test calls the entry point through the C ABI twice in a row on different inputs and requires
-each result to be bit-identical to the regular entry point's (the regular one is itself checked bit for bit
-against the CPU oracle in test_gpu_parity.py).  The second call finds the first call's leftovers in the shared
-array, which must not matter.  The file is named to be collected last.
+Some callers of this library may not allocate device memory while they run: a plugin inside a host that took
+all GPU memory into its own pool at start-up (cudaMalloc fails there, or is forbidden), a latency-critical loop
+that must not take the allocator's lock.  They cannot provide the scratch buffer the sorted table gradient sorts
+into, so the library carries a 32 MiB array of its own for them.  This test calls the entry point through the
+C ABI twice in a row on different inputs and requires each result to be bit-identical to the regular entry
+point's (the regular one is itself checked bit for bit against the CPU oracle in test_gpu_parity.py).  The
+second call finds the first call's leftovers in the shared array, which must not matter.
+
+"Allocates nothing" is checked with cudaMemGetInfo (free bytes of the device), not with torch's own counters,
+which see only torch's caching allocator: after one warm-up call -- the first use on a device is when the CUDA
+runtime loads the library's code and reserves the built-in array -- the two calls must leave the free bytes of
+the device unchanged.  The file is named to be collected last.
 """
 import ctypes as C
 
@@ -32,12 +37,14 @@ def test_static_scratch_entry_point_matches_regular_one_twice():
     assert torch.cuda.is_available()
     dev = torch.device("cuda:0")
     lib = L.lib()
+    shapes = [(3000, 24, 1, 256, 512), (700, 6, 9, 256, 768)]
     with torch.cuda.device(dev):
         sp = L.stream_ptr(dev)
-        for seed, (N, T, m, rows, d) in enumerate([(3000, 24, 1, 256, 512), (700, 6, 9, 256, 768)]):
+        # everything the calls under test touch is allocated first; the regular entry point gives the expected bits
+        cases = []
+        for seed, (N, T, m, rows, d) in enumerate(shapes):
             idx, w, dy = _inputs(seed, N, T, m, rows, d, dev)
             S = T * rows
-            # every output buffer is allocated before the call under test; the call itself allocates nothing
             ref = torch.empty(S, d, device=dev)
             out = torch.full((S, d), float("nan"), device=dev)
             nbytes = lib.lffn_gather_bwd_tables_sorted_scratch_bytes(N, T, m, rows)
@@ -45,13 +52,32 @@ def test_static_scratch_entry_point_matches_regular_one_twice():
             scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
             L.check(lib.lffn_gather_bwd_tables_sorted(L.ptr(idx), L.ptr(w), L.ptr(dy), L.ptr(ref), N, T, m, rows, d,
                                                       L.ptr(scratch), nbytes, sp))
-            torch.cuda.synchronize()
-            before = torch.cuda.memory_allocated(dev)
+            cases.append((idx, w, dy, ref, out, (N, T, m, rows, d)))
+
+        def call(case):
+            idx, w, dy, _, out, (N, T, m, rows, d) = case
             L.check(lib.lffn_gather_bwd_tables_sorted_static(L.ptr(idx), L.ptr(w), L.ptr(dy), L.ptr(out), N, T, m,
                                                              rows, d, sp))
+
+        call(cases[0])  # warm-up: the first use on the device loads the code and looks up the array's address
+        torch.cuda.synchronize()
+        cases[0][4].fill_(float("nan"))
+        torch.cuda.synchronize()
+        # Free bytes of the device as the driver reports them.  Another process on the same GPU could move the
+        # number, so a changed reading is re-taken (up to three rounds); an allocation by the calls themselves
+        # would change it every time.
+        unchanged = False
+        for _ in range(3):
+            free_before = torch.cuda.mem_get_info(dev)[0]
+            for case in cases:
+                call(case)
             torch.cuda.synchronize()
-            assert torch.cuda.memory_allocated(dev) == before
-            assert torch.equal(out, ref), f"call {seed}: static-scratch result differs from the regular entry point"
+            if torch.cuda.mem_get_info(dev)[0] == free_before:
+                unchanged = True
+                break
+        assert unchanged, "free device memory changed across the allocation-free calls"
+        for i, (_, _, _, ref, out, _) in enumerate(cases):
+            assert torch.equal(out, ref), f"call {i}: static-scratch result differs from the regular entry point"
             assert float(out.abs().sum()) > 0
         assert L.device_status(dev) == 0
 
