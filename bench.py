@@ -41,11 +41,12 @@ WORKLOADS = {
     "c5k10": dict(N=262144, d_in=1024, d_out=1024, T=64, k=10, dtype="bf16", weight_mode="score", bit_order="msb"),
     "c5k12": dict(N=262144, d_in=1024, d_out=1024, T=16, k=12, dtype="bf16", weight_mode="score", bit_order="msb"),
 }
-# DRAM bytes per gather launch from one ncu capture (dram__bytes_read.sum + dram__bytes_write.sum).
-# c3: captured at 16384 tokens (1.513 GB: tables re-fetched once per wave of resident warps, plus
-# idx/w/y) and scaled by 4 to the 65536-token launch, traffic being proportional to the waves of
-# tokens; see profiles/gather_fwd_c3.md.
-NCU_TRAFFIC_BYTES = {"c3": 4 * 1.5135e9}
+# Counters of the gather kernel from one ncu capture of this binary's kernel (dram__bytes_read.sum +
+# dram__bytes_write.sum, lts__t_sector_hit_rate.pct), per launch.  c3: captured on a 16384-token launch and
+# scaled by 4 to the 65536-token launch, DRAM traffic being proportional to the waves of tokens (the tables are
+# re-fetched once per wave of resident warps).  `commit` is the source revision the capture was taken from.
+NCU_PROFILE = {"c3": {"traffic_bytes_per_launch": 4 * 1.5135e9, "l2_hit_rate": 0.77, "commit": "0b851ed",
+                      "capture": "ncu --set full, 16384-token launch of the same kernel, traffic x 4"}}
 
 
 def padded_dim(d):
@@ -124,6 +125,74 @@ def physical_gpu_index(local):
     return local
 
 
+# ---- host placement ---------------------------------------------------------------------------------
+def _parse_cpulist(text):
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def gpu_numa_node(local):
+    """NUMA node and local CPU list of GPU `local` from sysfs (read-only), or (None, set())."""
+    try:
+        p = torch.cuda.get_device_properties(local)
+        bus = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        base = f"/sys/bus/pci/devices/{bus}"
+        node = int(open(base + "/numa_node").read())
+        cpus = _parse_cpulist(open(base + "/local_cpulist").read())
+        return (node if node >= 0 else None), cpus
+    except Exception:
+        return None, set()
+
+
+def bind_rank_to_gpu(local, world):
+    """Process placement only (no GPU or driver setting): this rank's threads go to a share of the CPUs that are
+    local to its GPU, disjoint from the other ranks' shares, and its future host allocations prefer the GPU's NUMA
+    node (set_mempolicy, MPOL_PREFERRED).  Returns what was done, for the JSON line."""
+    info = {"gpu_numa_node": None, "cpus": None, "mempolicy": "unchanged"}
+    try:
+        allowed = sorted(os.sched_getaffinity(0))
+        nodes = [gpu_numa_node(i) for i in range(torch.cuda.device_count())][:max(world, local + 1)]
+        node, near = nodes[local]
+        info["gpu_numa_node"] = node
+        pool = sorted(set(allowed) & near) or allowed
+        sharers = [i for i, (nd, nr) in enumerate(nodes) if (sorted(set(allowed) & nr) or allowed) == pool]
+        pos, cnt = sharers.index(local), len(sharers)
+        per = max(1, len(pool) // cnt)
+        mine = pool[pos * per:(pos + 1) * per] or pool
+        os.sched_setaffinity(0, mine)
+        torch.set_num_threads(max(1, min(len(mine), 4)))
+        info["cpus"] = f"{mine[0]}-{mine[-1]} ({len(mine)} of {len(allowed)} allowed)"
+        if node is not None:
+            libc = C.CDLL(None, use_errno=True)
+            mask = (C.c_ulong * 16)()
+            mask[node // 64] = 1 << (node % 64)
+            rc = libc.syscall(238, 1, mask, C.c_ulong(16 * 64))  # x86-64 set_mempolicy(MPOL_PREFERRED, mask, maxnode)
+            info["mempolicy"] = f"preferred node {node}" if rc == 0 else f"set_mempolicy errno {C.get_errno()}"
+    except Exception as e:  # placement is an optimisation; the run goes on without it
+        info["error"] = repr(e)
+    return info
+
+
+def pinned_like(t):
+    """Page-locked host tensor of t's shape and dtype.  Allocated with the process's own allocator (so that the
+    NUMA preference set above applies on first touch) and then registered with the CUDA runtime."""
+    h = torch.empty(t.shape, dtype=t.dtype)
+    h.view(torch.int16 if h.element_size() == 2 else h.dtype).zero_()  # first touch, under the NUMA preference
+    rc = torch.cuda.cudart().cudaHostRegister(h.data_ptr(), h.numel() * h.element_size(), 0)
+    if int(rc) != 0:
+        return torch.empty(t.shape, dtype=t.dtype).pin_memory()
+    _REGISTERED.append(h)  # stays registered, and alive, until the process ends
+    return h
+
+
+_REGISTERED = []
+
+
 # ---- synthetic workload ----------------------------------------------------------------------------
 def make_inputs(w, device, seed):
     """Seeded synthetic stand-ins for the pre-training activations and trained tables: x ~ N(0,1),
@@ -164,6 +233,7 @@ def run_ours(args, rank, world, local):
         w["N"] = args.tokens
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    placement = bind_rank_to_gpu(local, world)
     lib = L.lib()
     x, tables, signs, bias, D, R = make_inputs(w, device, rank)
     N, T, k = w["N"], w["T"], w["k"]
@@ -233,6 +303,20 @@ def run_ours(args, rank, world, local):
     l2_resident_ms = ev_l2[0].elapsed_time(ev_l2[1]) / 3
     del idx_l2, y_l2
 
+    # Hardware ceiling of that access pattern: plain coalesced 16-byte reads of a 32 MiB buffer that stays in L2,
+    # issued by the gather's grid with the gather's number of loads in flight (lffn_probe_read).  Outside the timed
+    # region.  One launch reads about as many bytes as the gather launch does.
+    probe_bytes = min(32 << 20, tables.numel() * tables.element_size()) // 16 * 16
+    reps = max(8, int(algorithmic_bytes_per_token(w) * N // probe_bytes))
+    sink = torch.zeros(1, dtype=torch.int32, device=device)
+    L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, 4, L.ptr(sink), sp))
+    ev_p = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev_p[0].record(stream)
+    L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, reps, L.ptr(sink), sp))
+    ev_p[1].record(stream)
+    torch.cuda.synchronize()
+    l2_read_peak = probe_bytes * reps / (ev_p[0].elapsed_time(ev_p[1]) * 1e-3) / 1e9  # GB/s
+
     if args.no_e2e:  # profiling runs: device path only
         if rank == 0:
             print(json.dumps({"workload": args.workload, "N": N, "hash_ms": hash_ms, "gather_ms": gather_ms,
@@ -244,9 +328,39 @@ def run_ours(args, rank, world, local):
     chunk = args.e2e_chunk
     ws_bytes = lib.lffn_layer_fwd_host_ws_bytes(C.byref(desc), dcode, dcode, w["d_out"], chunk)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
-    x_host = torch.empty(x.shape, dtype=dt).pin_memory()
+    x_host = pinned_like(x)
     x_host.copy_(x)
-    y_host = torch.empty(y.shape, dtype=dt).pin_memory()
+    y_host = pinned_like(y)
+
+    # What the host side allows with no kernels at all: the step's x going in and a y coming out, both whole, on
+    # two streams at once, all ranks at the same time.  The end-to-end number cannot beat this, nor the device path.
+    cs_in, cs_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    x_tmp = torch.empty_like(x)
+
+    def copy_step():
+        with torch.cuda.stream(cs_in):
+            x_tmp.copy_(x_host, non_blocking=True)
+        with torch.cuda.stream(cs_out):
+            y_host.copy_(y, non_blocking=True)
+
+    copy_steps = max(5, min(args.steps, 30))
+    for _ in range(3):
+        copy_step()
+    torch.cuda.synchronize()
+    barrier()
+    ev_c = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev_c[0].record(stream)
+    cs_in.wait_stream(stream)
+    cs_out.wait_stream(stream)
+    for _ in range(copy_steps):
+        copy_step()
+    stream.wait_stream(cs_in)
+    stream.wait_stream(cs_out)
+    ev_c[1].record(stream)
+    torch.cuda.synchronize()
+    copy_s = ev_c[0].elapsed_time(ev_c[1]) * 1e-3 / copy_steps
+    barrier()
+    del x_tmp
 
     def e2e_step():
         L.check(lib.lffn_layer_fwd_host(C.byref(desc), L.ptr(x_host), dcode, N, L.ptr(tables), dcode, w["d_out"],
@@ -259,17 +373,23 @@ def run_ours(args, rank, world, local):
                               y.cpu().view(torch.int16) if dt == torch.bfloat16 else y.cpu()))
     barrier()
     torch.cuda.synchronize()
-    t0 = time.perf_counter()
+    ev_e = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev_e[0].record(stream)
     for _ in range(args.steps):
-        e2e_step()  # synchronous: returns when y_host is complete
+        e2e_step()  # synchronous: returns when y_host is complete; its copies and kernels are ordered after `stream`
+    ev_e[1].record(stream)
     torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = ev_e[0].elapsed_time(ev_e[1]) * 1e-3
     barrier()
 
     if world > 1:
-        t = torch.tensor([elapsed_ms, e2e_s, gather_ms, hash_ms], dtype=torch.float64, device=device)
+        t = torch.tensor([elapsed_ms, e2e_s, gather_ms, hash_ms, copy_s], dtype=torch.float64, device=device)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        elapsed_ms, e2e_s, gather_ms, hash_ms = (float(v) for v in t.tolist())
+        elapsed_ms, e2e_s, gather_ms, hash_ms, copy_s = (float(v) for v in t.tolist())
+        placements = [None] * world
+        torch.distributed.all_gather_object(placements, placement)
+    else:
+        placements = [placement]
 
     if rank != 0:
         return None
@@ -284,44 +404,58 @@ def run_ours(args, rank, world, local):
     peak, peak_kind = load_peaks()
     achieved = alg * N / (gather_ms * 1e-3) / 1e9
     chunks = -(-N // chunk)
+    prof = NCU_PROFILE.get(args.workload) if not args.tokens else None
+    traffic = prof["traffic_bytes_per_launch"] if prof else None
+    value = world * N * args.steps / (elapsed_ms * 1e-3)
+    e2e_value = world * N * args.steps / e2e_s
+    copy_ceiling = world * N / copy_s
+    ceiling = min(copy_ceiling, value)
     out = {
-        "metric": "lookupffn_layer_forward_throughput", "value": world * N * args.steps / (elapsed_ms * 1e-3),
+        "metric": "lookupffn_layer_forward_throughput", "value": value,
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": w["dtype"], "data": "synthetic",
         "config": layer_config(args, w, world),
         "kernels_ms": {"hash_fwd": hash_ms, "gather_fwd": gather_ms},
-        "roofline": {"bound": "hbm", "kernel": "gather_fwd_kernel", "achieved": achieved, "peak": peak,
+        # `achieved` counts every gathered row once per use (algorithmic bytes), so `frac` above 1 is not an HBM
+        # fraction: each table row is used N / 2^k times per launch and most uses are served from L2.  What limits
+        # the kernel is L2 read bandwidth; the DRAM side is `traffic` (ncu) over the same time.
+        "roofline": {"bound": "hbm", "limiter": "l2 read bandwidth", "kernel": "gather_fwd_kernel",
+                     "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
-                     "algorithmic_bytes_per_token": alg, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                     # frac > 1: most rows are served from L2 (see traffic).  The same launch with all indices
-                     # folded into an L2-resident band of 32 tables gives the kernel's ceiling without DRAM:
+                     "algorithmic_bytes_per_token": alg, "traffic": traffic,
+                     "traffic_capture": {k: prof[k] for k in ("capture", "commit")} if prof else None,
+                     "dram_achieved": traffic / (gather_ms * 1e-3) / 1e9 if traffic else None,
+                     "dram_frac": traffic / (gather_ms * 1e-3) / 1e9 / peak if traffic else None,
+                     "l2_hit_rate": prof["l2_hit_rate"] if prof else None,
+                     "l2_read_peak": l2_read_peak, "frac_of_l2_read_peak": achieved / l2_read_peak,
+                     "l2_read_peak_source": "lffn_probe_read: 16-byte loads of an L2-resident 32 MiB buffer by the "
+                                            "gather's grid, measured in this run",
+                     # the same launch with all indices folded into an L2-resident band of 32 tables:
                      "l2_resident_launch_ms": l2_resident_ms, "frac_of_l2_resident_launch": l2_resident_ms / gather_ms},
-        "e2e": {"value": world * N * args.steps / e2e_s, "unit": "tokens/s",
+        "e2e": {"value": e2e_value, "unit": "tokens/s",
                 "h2d_bytes_per_step": N * w["d_in"] * eb, "d2h_bytes_per_step": N * w["d_out"] * eb,
                 "api": "lffn_layer_fwd_host (pinned host x -> pinned host y)", "chunk_tokens": chunk,
-                "matches_device_path": e2e_ok},
+                "matches_device_path": e2e_ok,
+                # the same bytes copied both ways at once with no kernels, all ranks together (max over ranks)
+                "host_copy_ceiling": {"value": copy_ceiling, "unit": "tokens/s", "ms_per_step": copy_s * 1e3,
+                                      "GBps_per_direction_per_gpu": N * w["d_in"] * eb / copy_s / 1e9},
+                "ceiling": ceiling, "frac_of_ceiling": e2e_value / ceiling,
+                "placement": placements},
         "gpu_launches": 2 * args.steps + 2 * chunks * args.steps,
         "clocks": clocks, "device_status": status, "parity_sample": parity, "gpu_comparator": comparator,
     }
     return out
 
 
-def run_table_sharded(args, rank, world, local):
-    """Config-5 style: every rank sees all N tokens, owns T_per_gpu tables (the whole layer has
-    T_per_gpu * world), partial sums are reduce-scattered over NVLink chunk by chunk."""
-    from lookupffn_b200 import _lib as L
-    from lookupffn_b200 import ops, sharded
+def table_sharded_setup(w, rank, world, device):
+    """Inputs of the table-sharded mode (benchmark configuration 5): every rank sees all N tokens (identical x),
+    owns T_per_gpu tables of a layer with T_per_gpu * world tables."""
+    from lookupffn_b200 import ops
 
-    w = dict(WORKLOADS[args.workload])
-    if args.tokens:
-        w["N"] = args.tokens
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
     N, k, d_in, d_out = w["N"], w["k"], w["d_in"], w["d_out"]
     t_count = w["T"]
     T = t_count * world
-    t_begin = rank * t_count
     dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
     D = padded_dim(d_in)
     R = max(1, -(-T * k // D))
@@ -332,55 +466,120 @@ def run_table_sharded(args, rank, world, local):
     tables = (0.02 * torch.randn(t_count << k, d_out, generator=gt, device=device)).to(dt)
     bias = torch.zeros(d_out, device=device)
     desc = ops.make_hash_desc(d_in, signs, None, T, k, had_scale=float(1.0 / np.sqrt(D)), mix_a=1.0, mix_b=0.0)
-    chunk = args.rs_chunk
+    return dict(x=x, tables=tables, bias=bias, desc=desc, t_begin=rank * t_count, t_count=t_count, T=T, dt=dt)
 
-    peers = None
-    if args.rs != "nccl":
-        peers = sharded.PeerOutput(N // world, d_out, device, mode="add" if args.rs == "fused" else "store")
+
+def table_sharded_step_fn(S, rs, chunk, world, device):
+    """One step of the table-sharded forward with exchange `rs`: "nccl" (chunked NCCL reduce-scatter), "fused" (one
+    bulk reduction per row from the gather kernel into the owner's buffer over NVLink), "fused-store" (peer stores
+    into slabs), or "none" (no exchange: the rank's partial sums stay local -- the one-GPU pace of the same shape)."""
+    from lookupffn_b200 import ops, sharded
+
+    x, tables, bias, desc = S["x"], S["tables"], S["bias"], S["desc"]
+    if rs == "none":
+        def step():
+            idx, wg, _ = ops.hash_fwd(x, desc, t_begin=S["t_begin"], t_count=S["t_count"])
+            return ops.weighted_vector_gather_add(idx, tables, wg, out_dtype=torch.float32)
+        return step, None
+    if rs == "nccl":
+        def step():
+            return sharded.lookup_forward_table_sharded(x, desc, tables, S["t_begin"], S["t_count"], bias=bias,
+                                                        chunk_tokens=chunk, out_dtype=torch.float32)[0]
+        return step, None
+    peers = sharded.PeerOutput(x.shape[0] // world, tables.shape[1], device, mode="add" if rs == "fused" else "store")
 
     def step():
-        if peers is not None:  # gather and reduce-scatter in one kernel over peer-mapped buffers
-            return sharded.lookup_forward_table_sharded_fused(x, desc, tables, t_begin, t_count, peers, bias=bias)
-        return sharded.lookup_forward_table_sharded(x, desc, tables, t_begin, t_count, bias=bias,
-                                                    chunk_tokens=chunk, out_dtype=torch.float32)[0]
+        return sharded.lookup_forward_table_sharded_fused(x, desc, tables, S["t_begin"], S["t_count"], peers, bias=bias)
+    return step, peers
 
-    for _ in range(args.warmup):
-        step()
+
+def time_steps(step, steps, warmup, device, world):
+    """CUDA-event time per step in ms, max over ranks, bracketed by barriers and synchronisation."""
+    for _ in range(warmup):
+        y = step()
     torch.cuda.synchronize()
-    sampler = ClockSampler(physical_gpu_index(local))
-    torch.distributed.barrier()
+    if world > 1:
+        torch.distributed.barrier()
     torch.cuda.synchronize()
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         y = step()
     e1.record()
     torch.cuda.synchronize()
-    torch.distributed.barrier()
+    if world > 1:
+        torch.distributed.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=device)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t[0]), y
+
+
+def table_sharded_record(args, rank, world, local):
+    """Appended to the default line when more than one GPU runs: a short run of benchmark configuration 5 (tables
+    split by T over the GPUs, every GPU sees all 262,144 tokens, partial sums combined by a reduce-scatter over
+    NVLink) with both exchanges, beside the same per-GPU shape without any exchange.  k = 8 at every N; k = 6 and
+    k = 12 too at 8 GPUs.  Every rank runs it; rank 0 reports."""
+    device = torch.device("cuda", local)
+    ks = ["c5k8"] + (["c5k12", "c5k6"] if world >= 8 else [])
+    steps, warmup = 5, 3
+    rec = {"what": "tables sharded by T, all tokens on every GPU, fp32 partial sums reduce-scattered over tokens",
+           "nccl_ranks": torch.distributed.get_world_size(), "steps": steps, "warmup": warmup, "runs": {}}
+    for name in ks:
+        w = dict(WORKLOADS[name])
+        S = table_sharded_setup(w, rank, world, device)
+        N, d_out = w["N"], w["d_out"]
+        run = {"tokens": N, "tables_per_gpu": w["T"], "k": w["k"], "d": d_out,
+               "reduce_scattered_bytes_per_gpu": N * d_out * 4,
+               "bytes_leaving_each_gpu_over_nvlink": N * d_out * 4 * (world - 1) // world}
+        for rs in ("none", "nccl", "fused"):
+            step, peers = table_sharded_step_fn(S, rs, args.rs_chunk, world, device)
+            ms, _ = time_steps(step, steps, warmup, device, world)
+            key = {"none": "one_gpu_pace_no_exchange", "nccl": "nccl_reduce_scatter", "fused": "fused_in_gather_kernel"}[rs]
+            run[key] = {"ms_per_step": ms, "tokens_per_s": N / (ms * 1e-3)}
+            del step, peers
+        base = run["one_gpu_pace_no_exchange"]["ms_per_step"]
+        for key in ("nccl_reduce_scatter", "fused_in_gather_kernel"):
+            run[key]["pace_vs_no_exchange"] = base / run[key]["ms_per_step"]
+        rec["runs"][name] = run
+        del S
+        torch.cuda.empty_cache()
+    return rec if rank == 0 else None
+
+
+def run_table_sharded(args, rank, world, local):
+    """Config-5 style: every rank sees all N tokens, owns T_per_gpu tables (the whole layer has
+    T_per_gpu * world), partial sums are reduce-scattered over NVLink chunk by chunk."""
+    from lookupffn_b200 import sharded
+
+    w = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        w["N"] = args.tokens
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    S = table_sharded_setup(w, rank, world, device)
+    N, k, d_in, d_out, t_count, T, dt = w["N"], w["k"], w["d_in"], w["d_out"], S["t_count"], S["T"], S["dt"]
+    x = S["x"]
+    chunk = args.rs_chunk
+    step, peers = table_sharded_step_fn(S, args.rs, chunk, world, device)
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    ms, y = time_steps(step, args.steps, args.warmup, device, world)
     clocks = sampler.result()
-    elapsed_ms = e0.elapsed_time(e1)
+    elapsed_ms = ms * args.steps
 
     # end to end: x from pinned host memory every step, the rank's rows of y back to pinned host memory
-    x_host = torch.empty(x.shape, dtype=dt).pin_memory()
+    x_host = pinned_like(x)
     x_host.copy_(x)
-    y_host = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+    y_host = pinned_like(y)
 
     def e2e_step():
         x.copy_(x_host, non_blocking=True)
         y_host.copy_(step(), non_blocking=True)
+        return y_host
 
-    e2e_step()
-    torch.cuda.synchronize()
-    torch.distributed.barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    t = torch.tensor([elapsed_ms, e2e_s], dtype=torch.float64, device=device)
-    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    elapsed_ms, e2e_s = (float(v) for v in t.tolist())
+    e2e_ms, _ = time_steps(e2e_step, args.steps, 1, device, world)
+    e2e_s = e2e_ms * 1e-3 * args.steps
     if rank != 0:
         return None
     eb = 2 if w["dtype"] == "bf16" else 4
@@ -560,7 +759,31 @@ def encoder_gpu_comparator(model, step, B, S, cfg, device):
     with torch.inference_mode():
         ours_ffn_ms = time_ms(lambda: ffn(h), 10)
         ref_ffn_ms = time_ms(lambda: lookupffn_reference_gpu(ffn, h, fht, gat), 5)
-        ffn_err = float((ffn(h) - lookupffn_reference_gpu(ffn, h, fht, gat)).abs().max() / ffn(h).abs().max())
+        y_ours, y_ref = ffn(h), lookupffn_reference_gpu(ffn, h, fht, gat)
+        ffn_err = float((y_ours - y_ref).abs().max() / y_ours.abs().max())
+        # hash codes of this layer against the reference's GPU evaluation, with the disagreements binned by the
+        # magnitude of the coordinate (fp64 evaluation of the projection) that caused them
+        from oracle import parity as PAR
+        from oracle.ref_gpu_path import code_score_reference_gpu, projection_reference_gpu
+
+        T, rows = ffn.num_table, ffn.table_size
+        k = int(np.log2(rows))
+        hn = ffn.LayerNorm(h.reshape(-1, cfg.hidden_size))
+        pw, pb = ffn.hash.projection.weight, ffn.hash.projection.bias
+        z_ours = ffn.hash.projection(hn)
+        z_ref = projection_reference_gpu(hn, pw, pb, T * k, fht)
+        z64 = PAR.projection_fp64_torch(hn, pw, pb, T * k)
+        parity = PAR.sign_mismatch_report(z_ours.cpu().numpy(), z_ref.cpu().numpy(), z64.cpu().numpy())
+        code_ours = ffn.hash(hn)[0] - (torch.arange(T, device=device, dtype=torch.int32) * rows)[None]
+        code_ref = code_score_reference_gpu(z_ref.reshape(-1, T, k))[0]
+        differ = code_ours != code_ref
+        clean = ~differ.any(dim=-1)
+        yo, yr = y_ours.reshape(-1, y_ours.shape[-1]), y_ref.reshape(-1, y_ref.shape[-1])
+        parity.update({"hash_codes_checked": int(code_ref.numel()), "hash_code_mismatches": int(differ.sum()),
+                       "tokens": int(clean.numel()), "tokens_without_a_differing_code": int(clean.sum()),
+                       "ffn_output_max_rel_err_on_those_tokens":
+                           float((yo[clean] - yr[clean]).abs().max() / yr[clean].abs().max()) if bool(clean.any()) else None})
+        del z64, z_ours, z_ref
     patched = []
     try:
         for layer in model.encoder.layer:
@@ -577,7 +800,8 @@ def encoder_gpu_comparator(model, step, B, S, cfg, device):
                     "Hadamard and gather CUDA kernels + elementwise torch)",
             "seq_per_s": B / (ref_ms * 1e-3), "ms_per_step": ref_ms,
             "ffn_layer_ms": {"reference_style": ref_ffn_ms, "ours": ours_ffn_ms},
-            "max_abs_diff_over_max_abs": {"ffn_layer": ffn_err, "encoder_output": err}}
+            "max_abs_diff_over_max_abs": {"ffn_layer": ffn_err, "encoder_output": err},
+            "parity_sample": parity}
 
 
 def run_encoder(args, rank, world, local):
@@ -862,6 +1086,8 @@ def main():
     ap.add_argument("--rs", default="nccl", choices=["nccl", "fused", "fused-store"],
                     help="--shard tables: combine partial sums with NCCL reduce-scatter, or inside the gather kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-table-sharded", action="store_true",
+                    help="skip the short table-sharded run appended to the line when more than one GPU runs")
     ap.add_argument("--no-encoder", action="store_true", help="skip the short config-2 encoder run appended at N=1")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling on a small case)")
     ap.add_argument("--no-e2e", action="store_true", help="device path only, short report (for ncu captures)")
@@ -898,6 +1124,15 @@ def main():
         torch.distributed.destroy_process_group()
         return 0
     out = run_ours(args, rank, world, local)
+    if world > 1 and args.workload == "c3" and not args.tokens and not args.no_table_sharded:
+        # the other multi-GPU mode (tables sharded, reduce-scatter over NVLink), a short run appended to the line
+        torch.cuda.empty_cache()
+        try:
+            ts = table_sharded_record(args, rank, world, local)
+        except Exception as e:  # the headline line is printed regardless
+            ts = {"error": repr(e)}
+        if out is not None:
+            out["table_sharded"] = ts
     if out is not None:
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_path(args, 15.0)
@@ -911,6 +1146,15 @@ def main():
                                             "with_bf16_autocast_around_the_ffn":
                                                 enc["with_bf16_autocast_around_the_ffn"]["value"],
                                             "gpu_comparator": enc["gpu_comparator"]}
+            # and a short run of benchmark configuration 4 (training-mode gather, forward + backward) beside the
+            # reference's own CUDA kernels on the same tensors
+            torch.cuda.empty_cache()
+            c4_args = argparse.Namespace(**vars(args))
+            c4_args.steps, c4_args.warmup = 3, 3
+            c4 = run_train_gather(c4_args, rank, world, local)
+            out["training_gather_c4"] = {k: c4[k] for k in ("value", "unit", "ms_per_step", "kernels_ms",
+                                                            "algorithmic_GBps", "gpu_comparator", "steps")}
+            out["training_gather_c4"]["config"] = c4["config"]["workload"]
         print(json.dumps(out), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()

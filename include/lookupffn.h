@@ -106,6 +106,15 @@ int lffn_device_status(uint32_t *status_out, lffn_stream_t stream);
 int lffn_selftest_bounded_wait(int32_t poll_limit, lffn_stream_t stream);
 
 /*
+ * Measurement probe (no reference counterpart; not on the layer's path): reads `bytes` bytes at `buf` `repeats`
+ * times with the gather kernel's access pattern -- coalesced 16-byte read-only loads, twelve in flight per
+ * thread, the gather's grid.  With a buffer that fits L2 and several repeats, bytes * repeats / elapsed time is
+ * the L2 read bandwidth this pattern can reach: the ceiling the benchmark quotes the gather against.  `sink` is
+ * one device word that keeps the loads observable (it is practically never written).
+ */
+int lffn_probe_read(const void *buf, size_t bytes, int32_t repeats, uint32_t *sink, lffn_stream_t stream);
+
+/*
  * Walsh-Hadamard transform of each row, out = x H_D * scale.  Replaces
  * fast_hadamard_transform_kernel.fast_hadamard_transform(inp)
  * (bh4/fast_hadamard_transform/extension/torch_extension.cpp:5-32, kernel.py:39-44,78-89).
@@ -126,6 +135,16 @@ int lffn_fwht(const void *x, void *out, int64_t N, int32_t D, int32_t dtype, flo
  */
 int lffn_hash_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, int32_t t_begin,
                   int32_t t_count, int32_t *idx_out, float *w_out, float *z_out, lffn_stream_t stream);
+
+/*
+ * The same with the module's LayerNorm (lookup.py:84,99: nn.LayerNorm(hidden_size, eps) applied before the hash)
+ * done inside the kernel's load of x: u = (x - mean) * rstd * ln_gamma + ln_beta over the d_in columns, biased
+ * variance, eps inside the square root, fp32 arithmetic.  ln_gamma [d_in] fp32 (NULL: no LayerNorm, i.e.
+ * lffn_hash_fwd), ln_beta [d_in] fp32 or NULL.  Saves the [N, d_in] round trip of a separate LayerNorm kernel.
+ */
+int lffn_hash_fwd_ln(const lffn_hash_desc *desc, const float *ln_gamma, const float *ln_beta, float ln_eps,
+                     const void *x, int32_t x_dtype, int64_t N, int32_t t_begin, int32_t t_count, int32_t *idx_out,
+                     float *w_out, float *z_out, lffn_stream_t stream);
 
 /*
  * Codes and weights from already projected coordinates z [N, T, k] fp32: replaces
@@ -155,6 +174,15 @@ int lffn_code_weights_bwd(const float *z, const float *dw, int64_t N, int32_t T,
 int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype, void *out,
                     int32_t out_dtype, int64_t N, int32_t I, int64_t S, int32_t d, const float *bias,
                     lffn_stream_t stream);
+
+/*
+ * The same with the caller's residual connection folded into the epilogue: out = fl(fl(sum + bias) + residual),
+ * the `self.dropout(self.FFN(attn_output)) + attn_output` of EncoderLayer.forward (layer.py:75-78) in inference
+ * (dropout is the identity there).  residual [N, d] of out_dtype, or NULL; it may be `out` itself (in place).
+ */
+int lffn_gather_fwd_residual(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype, void *out,
+                             int32_t out_dtype, int64_t N, int32_t I, int64_t S, int32_t d, const float *bias,
+                             const void *residual, lffn_stream_t stream);
 
 /*
  * Gather fused with the reduce-scatter of the table-sharded mode (no reference counterpart: the reference is
@@ -244,6 +272,18 @@ int lffn_gather_bwd_tables_sorted_static(const int32_t *idx, const float *w, con
 int lffn_layer_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, int32_t t_begin,
                    int32_t t_count, const void *tables, int32_t table_dtype, int32_t d_out, const float *bias,
                    void *out, int32_t out_dtype, int32_t *idx_ws, float *w_ws, lffn_stream_t stream);
+
+/*
+ * The whole feed-forward block of an encoder layer in two kernels = LookupFFN.forward with its LayerNorm
+ * (lookup.py:98-110) plus the caller's residual add (layer.py:75-78, inference): LayerNorm inside the hash
+ * kernel's load (lffn_hash_fwd_ln), `+ bias` and `+ residual` inside the gather's epilogue
+ * (lffn_gather_fwd_residual).  ln_gamma NULL: no LayerNorm; residual NULL: no residual add.
+ */
+int lffn_layer_fwd_ln_residual(const lffn_hash_desc *desc, const float *ln_gamma, const float *ln_beta, float ln_eps,
+                               const void *x, int32_t x_dtype, int64_t N, int32_t t_begin, int32_t t_count,
+                               const void *tables, int32_t table_dtype, int32_t d_out, const float *bias,
+                               const void *residual, void *out, int32_t out_dtype, int32_t *idx_ws, float *w_ws,
+                               lffn_stream_t stream);
 
 /*
  * The same forward for callers that hold HOST buffers (the shape of the reference's CPU

@@ -42,15 +42,21 @@ _SIGNATURES = {
     "lffn_last_error_string": (C.c_char_p, []),
     "lffn_device_status": (C.c_int, [C.POINTER(C.c_uint32), C.c_void_p]),
     "lffn_selftest_bounded_wait": (C.c_int, [C.c_int32, C.c_void_p]),
+    "lffn_probe_read": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int32, C.c_void_p, C.c_void_p]),
     "lffn_fwht": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]),
     "lffn_hash_fwd": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lffn_hash_fwd_ln": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_int32,
+                                   C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lffn_code_weights": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                     C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lffn_code_weights_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                         C.c_void_p, C.c_void_p]),
     "lffn_gather_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64,
                                   C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "lffn_gather_fwd_residual": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
+                                           C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p,
+                                           C.c_void_p]),
     "lffn_gather_fwd_scatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
                                           C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_int64, C.c_int32,
                                           C.c_void_p]),
@@ -66,6 +72,10 @@ _SIGNATURES = {
     "lffn_layer_fwd": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                                  C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
                                  C.c_void_p, C.c_void_p]),
+    "lffn_layer_fwd_ln_residual": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_void_p, C.c_float, C.c_void_p,
+                                             C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
+                                             C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                             C.c_void_p, C.c_void_p]),
     "lffn_layer_fwd_host_ws_bytes": (C.c_size_t, [C.POINTER(HashDesc), C.c_int32, C.c_int32, C.c_int32, C.c_int64]),
     "lffn_layer_fwd_host": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32,
                                       C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_size_t,

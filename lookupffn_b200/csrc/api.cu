@@ -151,17 +151,26 @@ int lffn_fwht(const void *x, void *out, int64_t N, int32_t D, int32_t dtype, flo
     return launch_fwht(x, out, N, D, dtype, scale, static_cast<cudaStream_t>(stream));
 }
 
-int lffn_hash_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, int32_t t_begin,
-                  int32_t t_count, int32_t *idx_out, float *w_out, float *z_out, lffn_stream_t stream) {
+int lffn_hash_fwd_ln(const lffn_hash_desc *desc, const float *ln_gamma, const float *ln_beta, float ln_eps,
+                     const void *x, int32_t x_dtype, int64_t N, int32_t t_begin, int32_t t_count, int32_t *idx_out,
+                     float *w_out, float *z_out, lffn_stream_t stream) {
     int rc = check_hash_desc(desc, t_begin, t_count);
     if (rc != LFFN_OK) return rc;
     LFFN_REQUIRE(N >= 0, LFFN_ERR_INVALID_ARG, "hash_fwd: N = %lld", (long long)N);
+    LFFN_REQUIRE(ln_gamma != nullptr || ln_beta == nullptr, LFFN_ERR_INVALID_ARG,
+                 "hash_fwd: a LayerNorm bias without a LayerNorm weight");
+    LFFN_REQUIRE(ln_gamma == nullptr || ln_eps >= 0.f, LFFN_ERR_INVALID_ARG, "hash_fwd: LayerNorm eps %g < 0", ln_eps);
     if (N == 0) return LFFN_OK;  // nothing to do; empty buffers may be NULL
     LFFN_REQUIRE(x != nullptr, LFFN_ERR_INVALID_ARG, "hash_fwd: x is NULL");
     LFFN_REQUIRE((idx_out != nullptr) == (w_out != nullptr) && (idx_out != nullptr || z_out != nullptr),
                  LFFN_ERR_INVALID_ARG, "hash_fwd: give idx_out and w_out together, or z_out alone");
-    return launch_hash_fwd(*desc, x, x_dtype, N, t_begin, t_count, idx_out, w_out, z_out,
+    return launch_hash_fwd(*desc, x, x_dtype, N, t_begin, t_count, idx_out, w_out, z_out, ln_gamma, ln_beta, ln_eps,
                            static_cast<cudaStream_t>(stream));
+}
+
+int lffn_hash_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, int32_t t_begin,
+                  int32_t t_count, int32_t *idx_out, float *w_out, float *z_out, lffn_stream_t stream) {
+    return lffn_hash_fwd_ln(desc, nullptr, nullptr, 0.f, x, x_dtype, N, t_begin, t_count, idx_out, w_out, z_out, stream);
 }
 
 int lffn_code_weights(const float *z, int64_t N, int32_t T, int32_t k, int32_t bit_order, int32_t weight_mode,
@@ -196,6 +205,12 @@ int lffn_code_weights_bwd(const float *z, const float *dw, int64_t N, int32_t T,
 int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype, void *out,
                     int32_t out_dtype, int64_t N, int32_t I, int64_t S, int32_t d, const float *bias,
                     lffn_stream_t stream) {
+    return lffn_gather_fwd_residual(idx, w, tables, table_dtype, out, out_dtype, N, I, S, d, bias, nullptr, stream);
+}
+
+int lffn_gather_fwd_residual(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype, void *out,
+                             int32_t out_dtype, int64_t N, int32_t I, int64_t S, int32_t d, const float *bias,
+                             const void *residual, lffn_stream_t stream) {
     int rc = check_gather(N, I, S, d, table_dtype);
     if (rc != LFFN_OK) return rc;
     LFFN_REQUIRE(out_dtype == LFFN_F32 || out_dtype == LFFN_BF16, LFFN_ERR_INVALID_ARG, "gather_fwd: out dtype %d",
@@ -205,7 +220,7 @@ int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int3
                  LFFN_ERR_INVALID_ARG, "gather_fwd: NULL buffer");
     LFFN_REQUIRE(aligned16(tables) && aligned16(out), LFFN_ERR_INVALID_ARG,
                  "gather_fwd: tables and out must be 16-byte aligned");
-    return launch_gather_fwd(idx, w, tables, table_dtype, out, out_dtype, N, I, S, d, bias,
+    return launch_gather_fwd(idx, w, tables, table_dtype, out, out_dtype, N, I, S, d, bias, residual,
                              static_cast<cudaStream_t>(stream));
 }
 
@@ -274,11 +289,21 @@ int lffn_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const floa
 int lffn_layer_fwd(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, int32_t t_begin,
                    int32_t t_count, const void *tables, int32_t table_dtype, int32_t d_out, const float *bias,
                    void *out, int32_t out_dtype, int32_t *idx_ws, float *w_ws, lffn_stream_t stream) {
-    int rc = lffn_hash_fwd(desc, x, x_dtype, N, t_begin, t_count, idx_ws, w_ws, nullptr, stream);
+    return lffn_layer_fwd_ln_residual(desc, nullptr, nullptr, 0.f, x, x_dtype, N, t_begin, t_count, tables, table_dtype,
+                                      d_out, bias, nullptr, out, out_dtype, idx_ws, w_ws, stream);
+}
+
+int lffn_layer_fwd_ln_residual(const lffn_hash_desc *desc, const float *ln_gamma, const float *ln_beta, float ln_eps,
+                               const void *x, int32_t x_dtype, int64_t N, int32_t t_begin, int32_t t_count,
+                               const void *tables, int32_t table_dtype, int32_t d_out, const float *bias,
+                               const void *residual, void *out, int32_t out_dtype, int32_t *idx_ws, float *w_ws,
+                               lffn_stream_t stream) {
+    int rc = lffn_hash_fwd_ln(desc, ln_gamma, ln_beta, ln_eps, x, x_dtype, N, t_begin, t_count, idx_ws, w_ws, nullptr,
+                              stream);
     if (rc != LFFN_OK) return rc;
     const int m = desc->weight_mode == LFFN_WEIGHT_SOFT_FLIP ? desc->k + 1 : 1;
-    return lffn_gather_fwd(idx_ws, w_ws, tables, table_dtype, out, out_dtype, N, t_count * m,
-                           (int64_t)t_count << desc->k, d_out, bias, stream);
+    return lffn_gather_fwd_residual(idx_ws, w_ws, tables, table_dtype, out, out_dtype, N, t_count * m,
+                                    (int64_t)t_count << desc->k, d_out, bias, residual, stream);
 }
 
 constexpr int HOST_LANES = 3;  // streams alternating over token chunks in lffn_layer_fwd_host

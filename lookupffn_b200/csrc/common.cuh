@@ -37,13 +37,15 @@ uint32_t *status_word();  // device pointer to this device's status word (alloca
 
 // launchers implemented in the .cu files, called by api.cu after argument checks
 int launch_gather_fwd(const int32_t *idx, const float *w, const void *tables, int table_dtype, void *out,
-                      int out_dtype, int64_t N, int I, int64_t S, int d, const float *bias, cudaStream_t st);
+                      int out_dtype, int64_t N, int I, int64_t S, int d, const float *bias, const void *residual,
+                      cudaStream_t st);
 int launch_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tables, int table_dtype,
                               float *const *peers, long long rows_per_owner, int slab, int first_owner, int64_t N,
                               int I, int64_t S,
                               int d, cudaStream_t st);
 int launch_hash_fwd(const lffn_hash_desc &h, const void *x, int x_dtype, int64_t N, int t_begin, int t_count,
-                    int32_t *idx_out, float *w_out, float *z_out, cudaStream_t st);
+                    int32_t *idx_out, float *w_out, float *z_out, const float *ln_g, const float *ln_b, float ln_eps,
+                    cudaStream_t st);
 int launch_code_weights(const float *z, int64_t N, int T, int k, int bit_order, int weight_mode, float tau,
                         int add_offsets, int32_t *idx_out, float *w_out, cudaStream_t st);
 int launch_code_weights_bwd(const float *z, const float *dw, int64_t N, int T, int k, int weight_mode, float tau,

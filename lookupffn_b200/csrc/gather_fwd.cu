@@ -58,9 +58,11 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
                                                          const float *__restrict__ bias, const int2 *__restrict__ seg,
                                                          int i0, int icnt, int resume, int finish, uint32_t *status,
                                                          float *const *__restrict__ peers, long long rows_per_owner,
-                                                         int slab, long long rot) {
+                                                         int slab, long long rot, const OutT *residual) {
     // i0/icnt: the slice of each token's index list this launch consumes; resume: start from the fp32 partial
     // sums already in `out`; finish: last slice, add the bias and convert (see launch_vpl_f on why lists are sliced)
+    // residual (may be null, may be `out` itself): [N, d] added after the bias, out = fl(fl(acc + bias) + residual),
+    // the `dropout(FFN(x)) + x` of the encoder layer (layer.py:75-78) in inference
     constexpr int EPV = Elem<TableT>::PER_VEC;
     const int lane = threadIdx.x & 31;
     const int warps_per_block = blockDim.x >> 5;
@@ -218,7 +220,7 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
             }
             continue;
         }
-        // epilogue: + bias (one rounded add, as `outputs + self.bias`), convert, 16-byte stores
+        // epilogue: + bias (one rounded add, as `outputs + self.bias`), + residual, convert, 16-byte stores
         OutT *orow = out + n * d + (long long)col0 * EPV;
 #pragma unroll
         for (int v = 0; v < VPL; v++) {
@@ -228,6 +230,11 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
 #pragma unroll
                     for (int e = 0; e < EPV; e++)
                         acc[v][e] = __fadd_rn(acc[v][e], __ldg(bias + (long long)(col0 + c) * EPV + e));
+                }
+                if (residual != nullptr && finish) {
+                    const OutT *rrow = residual + n * d + (long long)(col0 + c) * EPV;
+#pragma unroll
+                    for (int e = 0; e < EPV; e++) acc[v][e] = __fadd_rn(acc[v][e], Elem<OutT>::load1(rrow + e));
                 }
                 if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
@@ -262,7 +269,7 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
 
 template <typename TableT, typename OutT, int VPL, bool FULLV>
 static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, void *out, int64_t N, int I, int64_t S,
-                      int d, int col0, const float *bias, const int2 *seg, cudaStream_t st) {
+                      int d, int col0, const float *bias, const int2 *seg, const void *residual, cudaStream_t st) {
     // rows in flight per warp; 2 KB bf16 rows (VPL = 4) measured best with 3 (config-5 shape: 2.41 -> 2.14 ms)
     constexpr int U = (VPL <= 3) ? LFFN_GATHER_U_NARROW
                       : (VPL == 4 && sizeof(TableT) == 2) ? 3
@@ -289,6 +296,7 @@ static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, 
         if (slices > I / 128) slices = I / 128;
         if (slices < 1) slices = 1;
     }
+    if (residual == out) slices = 1;  // in-place residual: `out` cannot also park partial sums between slices
     const int per = slices == 1 ? I : ((I + slices - 1) / slices + 31) / 32 * 32;
     uint32_t *status = status_word();
     LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
@@ -296,7 +304,8 @@ static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, 
         const int icnt = I - i0 < per ? I - i0 : per;
         kern<<<(unsigned)grid, THREADS, 0, st>>>(idx, w, static_cast<const TableT *>(tables), static_cast<OutT *>(out), N,
                                                  I, S, d, col0, bias, seg, i0, icnt, i0 > 0 ? 1 : 0,
-                                                 i0 + icnt >= I ? 1 : 0, status, nullptr, 0, -1, 0);
+                                                 i0 + icnt >= I ? 1 : 0, status, nullptr, 0, -1, 0,
+                                                 static_cast<const OutT *>(residual));
         LFFN_CHECK_CUDA(cudaGetLastError());
         if (I == 0) break;
     }
@@ -331,7 +340,7 @@ static int launch_scatter_f(const int32_t *idx, const float *w, const void *tabl
     if (grid > want) grid = want;
     if (grid < 1) grid = 1;
     kern<<<(unsigned)grid, THREADS, smem, st>>>(idx, w, static_cast<const TableT *>(tables), nullptr, N, I, S, d, col0, nullptr,
-                                                nullptr, 0, I, 0, 1, status, peers, rows_per_owner, slab_k, rot);
+                                                nullptr, 0, I, 0, 1, status, peers, rows_per_owner, slab_k, rot, nullptr);
     LFFN_CHECK_CUDA(cudaGetLastError());
     return LFFN_OK;
 }
@@ -380,16 +389,16 @@ int launch_gather_fwd_scatter(const int32_t *idx, const float *w, const void *ta
 // FULLV: the column tile is exactly VPL*32 vectors wide, so no lane needs a column predicate
 template <typename TableT, typename OutT, int VPL>
 static int launch_vpl(const int32_t *idx, const float *w, const void *tables, void *out, int64_t N, int I, int64_t S,
-                      int d, int col0, const float *bias, const int2 *seg, cudaStream_t st) {
+                      int d, int col0, const float *bias, const int2 *seg, const void *residual, cudaStream_t st) {
     const int nvec = min(d / Elem<TableT>::PER_VEC - col0, VPL * 32);
     if (nvec == VPL * 32)
-        return launch_vpl_f<TableT, OutT, VPL, true>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st);
-    return launch_vpl_f<TableT, OutT, VPL, false>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st);
+        return launch_vpl_f<TableT, OutT, VPL, true>(idx, w, tables, out, N, I, S, d, col0, bias, seg, residual, st);
+    return launch_vpl_f<TableT, OutT, VPL, false>(idx, w, tables, out, N, I, S, d, col0, bias, seg, residual, st);
 }
 
 template <typename TableT, typename OutT>
 static int launch_typed(const int32_t *idx, const float *w, const void *tables, void *out, int64_t N, int I,
-                        int64_t S, int d, const float *bias, const int2 *seg, cudaStream_t st) {
+                        int64_t S, int d, const float *bias, const int2 *seg, const void *residual, cudaStream_t st) {
     constexpr int EPV = Elem<TableT>::PER_VEC;
     const int row_vecs = d / EPV;
     constexpr int MAXV = 8;  // widest column tile one launch covers: 8 vectors per lane
@@ -398,13 +407,13 @@ static int launch_typed(const int32_t *idx, const float *w, const void *tables, 
         const int vpl = (nvec + 31) / 32;
         int rc;
         switch (vpl) {
-            case 1: rc = launch_vpl<TableT, OutT, 1>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st); break;
-            case 2: rc = launch_vpl<TableT, OutT, 2>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st); break;
-            case 3: rc = launch_vpl<TableT, OutT, 3>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st); break;
-            case 4: rc = launch_vpl<TableT, OutT, 4>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st); break;
+            case 1: rc = launch_vpl<TableT, OutT, 1>(idx, w, tables, out, N, I, S, d, col0, bias, seg, residual, st); break;
+            case 2: rc = launch_vpl<TableT, OutT, 2>(idx, w, tables, out, N, I, S, d, col0, bias, seg, residual, st); break;
+            case 3: rc = launch_vpl<TableT, OutT, 3>(idx, w, tables, out, N, I, S, d, col0, bias, seg, residual, st); break;
+            case 4: rc = launch_vpl<TableT, OutT, 4>(idx, w, tables, out, N, I, S, d, col0, bias, seg, residual, st); break;
             case 5:
-            case 6: rc = launch_vpl<TableT, OutT, 6>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st); break;
-            default: rc = launch_vpl<TableT, OutT, 8>(idx, w, tables, out, N, I, S, d, col0, bias, seg, st); break;
+            case 6: rc = launch_vpl<TableT, OutT, 6>(idx, w, tables, out, N, I, S, d, col0, bias, seg, residual, st); break;
+            default: rc = launch_vpl<TableT, OutT, 8>(idx, w, tables, out, N, I, S, d, col0, bias, seg, residual, st); break;
         }
         if (rc != LFFN_OK) return rc;
     }
@@ -412,15 +421,16 @@ static int launch_typed(const int32_t *idx, const float *w, const void *tables, 
 }
 
 int launch_gather_fwd(const int32_t *idx, const float *w, const void *tables, int table_dtype, void *out,
-                      int out_dtype, int64_t N, int I, int64_t S, int d, const float *bias, cudaStream_t st) {
+                      int out_dtype, int64_t N, int I, int64_t S, int d, const float *bias, const void *residual,
+                      cudaStream_t st) {
     if (table_dtype == LFFN_F32 && out_dtype == LFFN_F32)
-        return launch_typed<float, float>(idx, w, tables, out, N, I, S, d, bias, nullptr, st);
+        return launch_typed<float, float>(idx, w, tables, out, N, I, S, d, bias, nullptr, residual, st);
     if (table_dtype == LFFN_F32 && out_dtype == LFFN_BF16)
-        return launch_typed<float, __nv_bfloat16>(idx, w, tables, out, N, I, S, d, bias, nullptr, st);
+        return launch_typed<float, __nv_bfloat16>(idx, w, tables, out, N, I, S, d, bias, nullptr, residual, st);
     if (table_dtype == LFFN_BF16 && out_dtype == LFFN_F32)
-        return launch_typed<__nv_bfloat16, float>(idx, w, tables, out, N, I, S, d, bias, nullptr, st);
+        return launch_typed<__nv_bfloat16, float>(idx, w, tables, out, N, I, S, d, bias, nullptr, residual, st);
     if (table_dtype == LFFN_BF16 && out_dtype == LFFN_BF16)
-        return launch_typed<__nv_bfloat16, __nv_bfloat16>(idx, w, tables, out, N, I, S, d, bias, nullptr, st);
+        return launch_typed<__nv_bfloat16, __nv_bfloat16>(idx, w, tables, out, N, I, S, d, bias, nullptr, residual, st);
     set_error("gather_fwd: unknown dtype (table %d, out %d)", table_dtype, out_dtype);
     return LFFN_ERR_INVALID_ARG;
 }
@@ -429,7 +439,7 @@ int launch_gather_fwd(const int32_t *idx, const float *w, const void *tables, in
 // src[idx[seg[r].x + j]] * w[seg[r].x + j], j < seg[r].y, in list order.
 int launch_gather_segmented(const int32_t *idx, const float *w, const float *src, float *out, int64_t n_out,
                             const int2 *seg, int64_t n_src, int d, cudaStream_t st) {
-    return launch_typed<float, float>(idx, w, src, out, n_out, 0, n_src, d, nullptr, seg, st);
+    return launch_typed<float, float>(idx, w, src, out, n_out, 0, n_src, d, nullptr, seg, nullptr, st);
 }
 
 }  // namespace lffn

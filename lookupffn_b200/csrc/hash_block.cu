@@ -42,6 +42,7 @@ constexpr int HB_MP = 36;       // padded tokens per coordinate row
 constexpr int HB_THREADS = 256;
 constexpr int HB_CARRY = 16;
 constexpr int HB_WFLOATS = 16384;  // staged weights per pass: PC * BS floats
+constexpr int HB_LN_FLOATS = 2 * HB_M;  // LayerNorm statistics (mean, 1/sigma) of the tile's tokens
 
 template <int RADIX>
 __device__ __forceinline__ void radix_butterflies(float (&v)[RADIX]) {
@@ -100,13 +101,39 @@ __device__ __forceinline__ void fwht_tile(float *Y, int D, float scale, int warp
 // ---- tile phases shared by the two kernels (THREADS threads, NW = THREADS / 32 warps) ---------------------------------
 // Start of a rotation: keep the last coordinates of the previous rotation (for a table that straddles the
 // boundary), then load the tile transposed and zero-padded.  The caller synchronises afterwards.
+// lnstat [2][HB_M]: mean and 1/sqrt(var + eps) of every token of the tile, filled here when the LayerNorm prologue
+// is on (a warp owns a token's row: two passes over it for the statistics, a third writes the normalised values).
 template <typename XT, int THREADS>
-__device__ __forceinline__ void tile_load(float *dst, const HashArgs &a, long long n0, int mt, int D) {
+__device__ __forceinline__ void tile_load(float *dst, const HashArgs &a, long long n0, int mt, int D, float *lnstat) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int mm = warp; mm < HB_M; mm += THREADS / 32) {
         const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
-        for (int e = lane; e < D; e += 32)
-            dst[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+        if (a.ln_g != nullptr) {
+            float mean = 0.f, rstd = 1.f;
+            if (mm < mt) {
+                float s = 0.f;
+                for (int e = lane; e < a.d_in; e += 32) s += Elem<XT>::load1(xrow + e);
+                mean = warp_sum(s) / (float)a.d_in;
+                float q = 0.f;
+                for (int e = lane; e < a.d_in; e += 32) {
+                    const float c = Elem<XT>::load1(xrow + e) - mean;
+                    q = fmaf(c, c, q);
+                }
+                rstd = 1.f / sqrtf(warp_sum(q) / (float)a.d_in + a.ln_eps);
+            }
+            if (lane == 0) {
+                lnstat[mm] = mean;
+                lnstat[HB_M + mm] = rstd;
+            }
+            for (int e = lane; e < D; e += 32)
+                dst[e * HB_MP + mm] = (mm < mt && e < a.d_in)
+                                          ? ln_apply(Elem<XT>::load1(xrow + e), mean, rstd, __ldg(a.ln_g + e),
+                                                     a.ln_b != nullptr ? __ldg(a.ln_b + e) : 0.f)
+                                          : 0.f;
+        } else {
+            for (int e = lane; e < D; e += 32)
+                dst[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+        }
     }
 }
 
@@ -118,11 +145,12 @@ __device__ __forceinline__ void tile_save_carry(const float *Y, float *carry, in
 }
 
 template <typename XT, int THREADS>
-__device__ __forceinline__ void tile_begin_rotation(float *Y, float *carry, const HashArgs &a, long long n0, int mt, int D) {
+__device__ __forceinline__ void tile_begin_rotation(float *Y, float *carry, const HashArgs &a, long long n0, int mt, int D,
+                                                    float *lnstat) {
     __syncthreads();
     tile_save_carry(Y, carry, D, THREADS);
     __syncthreads();
-    tile_load<XT, THREADS>(Y, a, n0, mt, D);
+    tile_load<XT, THREADS>(Y, a, n0, mt, D, lnstat);
 }
 
 // End of a rotation: z = fl(fl(mix_a * y) + fl(mix_b * u)) + bias in place, then codes and weights of the
@@ -131,7 +159,7 @@ __device__ __forceinline__ void tile_begin_rotation(float *Y, float *carry, cons
 // rotation boundary and z itself is not wanted the mix is folded into the code/weight step (Y is not rewritten).
 template <typename XT, int THREADS>
 __device__ __forceinline__ void tile_end_rotation(float *Y, const float *carry, const HashArgs &a, long long n0, int mt,
-                                                  int D, int r, const float *Xs = nullptr) {
+                                                  int D, int r, const float *lnstat, const float *Xs = nullptr) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k = a.k;
     const int m = a.weight_mode == LFFN_WEIGHT_SOFT_FLIP ? k + 1 : 1;
@@ -153,7 +181,9 @@ __device__ __forceinline__ void tile_end_rotation(float *Y, const float *carry, 
         for (int mm = warp; mm < HB_M; mm += THREADS / 32) {
             const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;
             for (int e = lane; e < D; e += 32) {
-                const float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+                float u = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
+                if (a.ln_g != nullptr && mm < mt && e < a.d_in)  // the statistics of tile_load
+                    u = ln_apply(u, lnstat[mm], lnstat[HB_M + mm], __ldg(a.ln_g + e), a.ln_b != nullptr ? __ldg(a.ln_b + e) : 0.f);
                 const long long g = c_lo + e;
                 float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + mm]), __fmul_rn(a.mix_b, u));
                 if (a.bias != nullptr && g < (long long)a.T * k) z = __fadd_rn(z, __ldg(a.bias + g));
@@ -222,6 +252,7 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, i
     float *Y = smem;                         // [D][HB_MP]
     float *Ws = Y + (size_t)D * HB_MP;       // [PC/BS][BS][BS] swizzled
     float *carry = Ws + HB_WFLOATS;          // [HB_CARRY][HB_MP]
+    float *lnstat = carry + HB_CARRY * HB_MP;  // [2][HB_M]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int PC = min(D, BS <= 64 ? 256 : HB_WFLOATS / BS);  // columns per pass
     const int bs4mask = BS / 4 - 1;
@@ -231,7 +262,7 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, i
         const long long n0 = tile * HB_M;
         const int mt = (int)min((long long)HB_M, a.N - n0);  // valid tokens in the tile
         for (int r = a.r_lo; r <= a.r_hi; r++) {
-            tile_begin_rotation<XT, HB_THREADS>(Y, carry, a, n0, mt, D);
+            tile_begin_rotation<XT, HB_THREADS>(Y, carry, a, n0, mt, D, lnstat);
             __syncthreads();
             for (int s = 0; s < a.S; s++) {
                 const float *wstage = a.w + ((long long)r * a.S + s) * D * BS;
@@ -283,7 +314,7 @@ __global__ void __launch_bounds__(HB_THREADS, 1) hash_block_kernel(HashArgs a, i
                 }
                 fwht_tile(Y, D, a.had_scale, warp, lane);
             }
-            tile_end_rotation<XT, HB_THREADS>(Y, carry, a, n0, mt, D, r);
+            tile_end_rotation<XT, HB_THREADS>(Y, carry, a, n0, mt, D, r, lnstat);
         }
     }
 }
@@ -372,7 +403,8 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     float *carry = Wb + 2 * HF_CHUNK_FLOATS;      // [HB_CARRY][HB_MP]
     unsigned long long *bars = reinterpret_cast<unsigned long long *>(carry + HB_CARRY * HB_MP);
     unsigned long long *full = bars, *empty = bars + HF_NBUF;  // one pair per weight buffer
-    float *Xs = X0 ? carry + HB_CARRY * HB_MP + HF_BAR_FLOATS : nullptr;  // [D][HB_MP]
+    float *lnstat = carry + HB_CARRY * HB_MP + HF_BAR_FLOATS;                // [2][HB_M]
+    float *Xs = X0 ? lnstat + HB_LN_FLOATS : nullptr;                         // [D][HB_MP]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int NB = D / 64;
     const int cps = (D / PC) * (64 / CR);            // chunks per stage: passes x row slices
@@ -459,13 +491,13 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
         if constexpr (X0) {
             if (first_of_tile) {
                 __syncthreads();  // the previous unit has finished reading Xs
-                tile_load<XT, THREADS>(Xs, a, n0, mt, D);
+                tile_load<XT, THREADS>(Xs, a, n0, mt, D, lnstat);
             } else if (D % a.k != 0) {
                 __syncthreads();
                 tile_save_carry(Y, carry, D, THREADS);
             }
         } else {
-            tile_begin_rotation<XT, THREADS>(Y, carry, a, n0, mt, D);
+            tile_begin_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, lnstat);
         }
         __syncthreads();  // the tile (and the carry rows) are in place
         HB_MARK(HB_PH_TILE);
@@ -527,7 +559,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
             fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
             HB_MARK(HB_PH_HADAMARD);
         }
-        tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r, Xs);
+        tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r, lnstat, Xs);
 #ifdef LFFN_HB_PHASE_CLOCKS
         __syncthreads();
 #endif
@@ -568,7 +600,7 @@ int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, c
         set_error("hash_fwd: block-diagonal projection supports D a power of two in [64, 1024], got %d", a.D);
         return LFFN_ERR_UNSUPPORTED;
     }
-    const size_t smem = ((size_t)a.D * HB_MP + HB_WFLOATS + HB_CARRY * HB_MP) * sizeof(float);
+    const size_t smem = ((size_t)a.D * HB_MP + HB_WFLOATS + HB_CARRY * HB_MP + HB_LN_FLOATS) * sizeof(float);
     const long long ntiles = (a.N + HB_M - 1) / HB_M;
     long long grid = num_sms();
     if (grid > ntiles) grid = ntiles;
@@ -583,7 +615,7 @@ int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, c
         if (grid > groups) grid = groups;
         if (grid < 1) grid = 1;
         const int threads = wide ? 512 : 256;
-        const size_t smem_b = smem + HF_BAR_FLOATS * sizeof(float);              // + the four mbarriers
+        const size_t smem_b = smem + HF_BAR_FLOATS * sizeof(float);              // + the mbarriers (the statistics sit behind them)
         const size_t smem_x0 = smem_b + (size_t)a.D * HB_MP * sizeof(float);  // + the resident copy of the input tile
         const bool x0 = smem_x0 <= 227 * 1024;
         const size_t smem_k = x0 ? smem_x0 : smem_b;

@@ -21,7 +21,22 @@ struct HashArgs {
     float *w_out;
     float *z_out;
     uint32_t *status;  // device status word (may be null)
+    // optional LayerNorm prologue (lookup.py:84,99): u = (x - mean) * rstd * ln_g + ln_b over the d_in columns,
+    // biased variance, eps inside the square root; ln_g == nullptr: x is used as it is
+    const float *ln_g;
+    const float *ln_b;
+    float ln_eps;
 };
+
+// LayerNorm statistics of one row held by a warp: `sum` and then `sq` are this lane's partial sums.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) v += __shfl_xor_sync(FULL, v, s);
+    return v;
+}
+__device__ __forceinline__ float ln_apply(float x, float mean, float rstd, float g, float b) {
+    return __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(x, mean), rstd), g), b);
+}
 
 // e^x for x <= 0 as one multiply and one ex2.approx.  The result is only ever used as 1 + e^x: its error (about two
 // ulp of e^x, plus |x| * 2^-24 relative from rounding x * log2(e), which matters only where e^x is tiny) moves

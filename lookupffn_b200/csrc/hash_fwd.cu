@@ -58,6 +58,32 @@ __device__ __forceinline__ void load_row(float (&v)[V], const XT *row, int d_in,
     }
 }
 
+// mean and 1/sqrt(var + eps) of a row spread over a warp as in load_row (two passes over the registers)
+template <int V>
+__device__ __forceinline__ void row_stats(const float (&v)[V], int d_in, int lane, float eps, float &mean, float &rstd) {
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; j++) s += v[j];  // padding columns hold zeros
+    mean = warp_sum(s) / (float)d_in;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+        const float c = (j * 32 + lane < d_in) ? v[j] - mean : 0.f;
+        q = fmaf(c, c, q);
+    }
+    rstd = 1.f / sqrtf(warp_sum(q) / (float)d_in + eps);
+}
+
+template <int V>
+__device__ __forceinline__ void row_normalise(float (&v)[V], int d_in, int lane, float mean, float rstd,
+                                              const float *__restrict__ g, const float *__restrict__ b) {
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+        const int e = j * 32 + lane;
+        if (e < d_in) v[j] = ln_apply(v[j], mean, rstd, __ldg(g + e), b != nullptr ? __ldg(b + e) : 0.f);
+    }
+}
+
 template <int V, typename XT>
 __global__ void __launch_bounds__(256) fwht_kernel(const XT *__restrict__ x, XT *__restrict__ out, long long N,
                                                    float scale) {
@@ -101,9 +127,16 @@ __global__ void __launch_bounds__(128) hash_diag_kernel(HashArgs a) {
 
     for (long long n = warp0; n < a.N; n += nwarps) {
         const XT *xrow = static_cast<const XT *>(a.x) + n * a.d_in;
+        float mean = 0.f, rstd = 1.f;
+        if (a.ln_g != nullptr) {
+            float v0[V];
+            load_row<V, XT>(v0, xrow, a.d_in, lane);
+            row_stats<V>(v0, a.d_in, lane, a.ln_eps, mean, rstd);
+        }
         for (int r = a.r_lo; r <= a.r_hi; r++) {
             float v[V];
             load_row<V, XT>(v, xrow, a.d_in, lane);
+            if (a.ln_g != nullptr) row_normalise<V>(v, a.d_in, lane, mean, rstd, a.ln_g, a.ln_b);
             for (int s = 0; s < a.S; s++) {
                 const float *ws = a.w + ((long long)r * a.S + s) * D;
 #pragma unroll
@@ -117,6 +150,7 @@ __global__ void __launch_bounds__(128) hash_diag_kernel(HashArgs a) {
             // z = fl(fl(mix_a * y) + fl(mix_b * u)) + bias
             float u[V];
             load_row<V, XT>(u, xrow, a.d_in, lane);
+            if (a.ln_g != nullptr) row_normalise<V>(u, a.d_in, lane, mean, rstd, a.ln_g, a.ln_b);
             __syncwarp();  // every lane is done reading the previous rotation's buffer
             float keep = 0.f;
             if (lane < CARRY) keep = zs[zpad(D - CARRY + lane)];
@@ -235,6 +269,38 @@ __device__ __forceinline__ void load_row_vec8(float (&v)[NV][8], const XT *row, 
     }
 }
 
+template <int NV>
+__device__ __forceinline__ void row_stats_vec8(const float (&v)[NV][8], int d_in, int lane, float eps, float &mean,
+                                               float &rstd) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++)
+#pragma unroll
+        for (int q = 0; q < 8; q++) s += v[i][q];
+    mean = warp_sum(s) / (float)d_in;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++)
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const float c = ((i * 32 + lane) * 8 + q < d_in) ? v[i][q] - mean : 0.f;
+            sq = fmaf(c, c, sq);
+        }
+    rstd = 1.f / sqrtf(warp_sum(sq) / (float)d_in + eps);
+}
+
+template <int NV>
+__device__ __forceinline__ void row_normalise_vec8(float (&v)[NV][8], int d_in, int lane, float mean, float rstd,
+                                                   const float *__restrict__ g, const float *__restrict__ b) {
+#pragma unroll
+    for (int i = 0; i < NV; i++)
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const int e = (i * 32 + lane) * 8 + q;
+            if (e < d_in) v[i][q] = ln_apply(v[i][q], mean, rstd, __ldg(g + e), b != nullptr ? __ldg(b + e) : 0.f);
+        }
+}
+
 template <int NV, int K, typename XT>
 __global__ void __launch_bounds__(128, (NV >= 8 ? 2 : 4)) hash_diag_vec8_kernel(HashArgs a, int x_vec_ok, int bias_vec_ok) {
     constexpr int D = NV * 256;
@@ -251,9 +317,16 @@ __global__ void __launch_bounds__(128, (NV >= 8 ? 2 : 4)) hash_diag_vec8_kernel(
 
     for (long long n = warp0; n < a.N; n += nwarps) {
         const XT *xrow = static_cast<const XT *>(a.x) + n * a.d_in;
+        float mean = 0.f, rstd = 1.f;
+        if (a.ln_g != nullptr) {
+            float v0[NV][8];
+            load_row_vec8<NV, XT>(v0, xrow, a.d_in, lane, x_vec_ok != 0);
+            row_stats_vec8<NV>(v0, a.d_in, lane, a.ln_eps, mean, rstd);
+        }
         for (int r = a.r_lo; r <= a.r_hi; r++) {
             float v[NV][8];
             load_row_vec8<NV, XT>(v, xrow, a.d_in, lane, x_vec_ok != 0);
+            if (a.ln_g != nullptr) row_normalise_vec8<NV>(v, a.d_in, lane, mean, rstd, a.ln_g, a.ln_b);
             for (int s = 0; s < a.S; s++) {
                 const float *ws = a.w + ((long long)r * a.S + s) * D;
 #pragma unroll
@@ -277,6 +350,7 @@ __global__ void __launch_bounds__(128, (NV >= 8 ? 2 : 4)) hash_diag_vec8_kernel(
             if (a.mix_b != 0.f) {
                 float u[NV][8];
                 load_row_vec8<NV, XT>(u, xrow, a.d_in, lane, x_vec_ok != 0);
+                if (a.ln_g != nullptr) row_normalise_vec8<NV>(u, a.d_in, lane, mean, rstd, a.ln_g, a.ln_b);
 #pragma unroll
                 for (int i = 0; i < NV; i++)
 #pragma unroll
@@ -515,8 +589,12 @@ static int launch_hash_diag_t(const HashArgs &a, cudaStream_t st) {
 int launch_hash_block(const HashArgs &a, int BS, int transpose_w, int x_dtype, cudaStream_t st);  // hash_block.cu
 
 int launch_hash_fwd(const lffn_hash_desc &h, const void *x, int x_dtype, int64_t N, int t_begin, int t_count,
-                    int32_t *idx_out, float *w_out, float *z_out, cudaStream_t st) {
+                    int32_t *idx_out, float *w_out, float *z_out, const float *ln_g, const float *ln_b, float ln_eps,
+                    cudaStream_t st) {
     HashArgs a;
+    a.ln_g = ln_g;
+    a.ln_b = ln_b;
+    a.ln_eps = ln_eps;
     a.x = x;
     a.N = N;
     a.d_in = h.d_in;

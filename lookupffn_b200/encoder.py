@@ -69,6 +69,9 @@ class EncoderLayer(nn.Module):
 
     def forward(self, hidden_states, attention_mask):
         attn_output = self.dropout(self.attention(hidden_states, attention_mask)) + hidden_states
+        if not self.training or self.dropout.p == 0:
+            # dropout is the identity: LayerNorm -> hash -> gather -> + bias -> + residual run as two kernels
+            return self.FFN(attn_output, residual=attn_output)
         return self.dropout(self.FFN(attn_output)) + attn_output
 
 

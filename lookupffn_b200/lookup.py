@@ -128,11 +128,18 @@ class Hashing(nn.Module):
     def candidates(self):
         return self.code_length + 1 if self.weight_mode == WEIGHT_SOFT_FLIP else 1
 
-    def forward(self, x, t_begin=0, t_count=None):
-        """x [N, hidden] -> (row indices int32 [N, T*m] with table offsets added, weights fp32 [N, T*m])."""
+    def fuses_layer_norm(self):
+        """True when the projection runs in this package's hash kernel, which can apply the LayerNorm in its load."""
+        return not isinstance(self.projection, nn.Linear)
+
+    def forward(self, x, t_begin=0, t_count=None, layer_norm=None):
+        """x [N, hidden] -> (row indices int32 [N, T*m] with table offsets added, weights fp32 [N, T*m]).
+        layer_norm = (weight, bias, eps): x is the un-normalised input and the kernel applies the LayerNorm
+        (inference with a bh4 / sign_hadamard projection only)."""
         t_count = self.num_table - t_begin if t_count is None else t_count
         p = self.projection
         needs_grad = torch.is_grad_enabled() and (x.requires_grad or any(q.requires_grad for q in p.parameters()))
+        assert layer_norm is None or (self.fuses_layer_norm() and not needs_grad)
         if isinstance(p, nn.Linear):
             z = p(x).float().reshape(x.shape[0], self.num_table, self.code_length)
             z = z[:, t_begin:t_begin + t_count].contiguous()
@@ -151,7 +158,7 @@ class Hashing(nn.Module):
         desc = ops.make_hash_desc(self.hidden_size, wk, p.bias.detach().contiguous(), self.num_table,
                                   self.code_length, transpose_w=tw, had_scale=p.had_scale, mix_a=p.mix[0],
                                   mix_b=p.mix[1], bit_order=self.bit_order, weight_mode=self.weight_mode, tau=self.tau)
-        idx, w, _ = ops.hash_fwd(x, desc, t_begin=t_begin, t_count=t_count)
+        idx, w, _ = ops.hash_fwd(x, desc, t_begin=t_begin, t_count=t_count, layer_norm=layer_norm)
         return idx, w
 
 
@@ -174,19 +181,34 @@ class LookupFFN(nn.Module):
         return (f"hidden_size={self.hidden_size}, num_table={self.num_table}, table_size={self.table_size}, "
                 f"output_size={self.output_size}")
 
-    def _forward(self, hidden_states):
+    def _inference(self):
+        """No gradient can be asked for: the fused two-kernel path applies."""
+        return not (torch.is_grad_enabled() and any(p.requires_grad for p in self.parameters()))
+
+    def _forward(self, hidden_states, residual=None):
         if not hidden_states.is_cuda:
             raise RuntimeError("lookupffn_b200.LookupFFN runs on CUDA tensors only (no CPU fallback)")
+        if self._inference() and not hidden_states.requires_grad and self.hash.fuses_layer_norm() \
+                and hidden_states.dtype in (torch.float32, torch.bfloat16):
+            # two kernels: LayerNorm inside the hash kernel's load; bias and residual inside the gather's epilogue
+            ln = self.LayerNorm
+            code, score = self.hash(hidden_states, layer_norm=(ln.weight, ln.bias, ln.eps))
+            T, rows, d = self.tables.shape
+            return ops.weighted_vector_gather_add(code, self.tables.reshape(T * rows, d), score, bias=self.bias,
+                                                  residual=residual)
         hidden_states = self.LayerNorm(hidden_states)
         code, score = self.hash(hidden_states)
         outputs = self.gather(code, score, self.tables)
-        return outputs
+        return outputs if residual is None else outputs + residual.reshape(outputs.shape).to(outputs.dtype)
 
-    def forward(self, hidden_states):
+    def forward(self, hidden_states, residual=None):
+        """residual (optional, same leading dims, output_size last): added to the result, as the encoder layer
+        does (layer.py:75-78: dropout(FFN(x)) + x); in inference the add rides in the gather kernel's epilogue.
+        Callers that apply dropout between the two keep doing the add themselves."""
         shape = hidden_states.shape[:-1]
         dim = hidden_states.shape[-1]
         hidden_states = hidden_states.reshape(int(np.prod(shape)), dim)
-        outputs = self._forward(hidden_states)
+        outputs = self._forward(hidden_states, residual)
         return outputs.reshape(*shape, self.output_size)
 
     def gather(self, indexes, weights, tables):

@@ -71,9 +71,10 @@ def make_hash_desc(d_in, proj_w, proj_bias, T, k, transpose_w=False, had_scale=1
     return desc
 
 
-def hash_fwd(x, desc, t_begin=0, t_count=None, want_z=False, want_codes=True):
+def hash_fwd(x, desc, t_begin=0, t_count=None, want_z=False, want_codes=True, layer_norm=None):
     """x [N, d_in] -> (idx int32 [N, t_count*m] with table offsets, w fp32 [N, t_count*m], z or None).
-    Reference: Hashing.forward (lookup.py:64-77) + the offsets of LookupFFN.gather (lookup.py:126)."""
+    Reference: Hashing.forward (lookup.py:64-77) + the offsets of LookupFFN.gather (lookup.py:126).
+    layer_norm = (weight, bias, eps): the module's LayerNorm (lookup.py:99) applied inside the kernel's load."""
     L.require_cuda(x)
     if x.dtype == torch.float16:  # the reference trains under fp16 autocast; the kernels read fp32 or bf16
         x = x.float()
@@ -87,9 +88,17 @@ def hash_fwd(x, desc, t_begin=0, t_count=None, want_z=False, want_codes=True):
         w = torch.empty((N, t_count * m), dtype=torch.float32, device=x.device)
     if want_z:
         z = torch.empty((N, t_count * desc.k), dtype=torch.float32, device=x.device)
+    g = b = None
+    eps = 0.0
+    if layer_norm is not None:
+        g, b, eps = layer_norm
+        g = _contig(g.detach().float())
+        b = None if b is None else _contig(b.detach().float())
+        L.require_cuda(g, b)
     with torch.cuda.device(x.device):
-        L.check(L.lib().lffn_hash_fwd(C.byref(desc), L.ptr(x), L.dtype_code(x.dtype), N, t_begin, t_count, L.ptr(idx),
-                                      L.ptr(w), L.ptr(z), L.stream_ptr(x.device)))
+        L.check(L.lib().lffn_hash_fwd_ln(C.byref(desc), L.ptr(g), L.ptr(b), float(eps), L.ptr(x),
+                                         L.dtype_code(x.dtype), N, t_begin, t_count, L.ptr(idx), L.ptr(w), L.ptr(z),
+                                         L.stream_ptr(x.device)))
     return idx, w, z
 
 
@@ -253,9 +262,10 @@ def _check_gather_args(indexes, source, weights):
     assert weights.shape == indexes.shape
 
 
-def weighted_vector_gather_add(indexes, source, weights, bias=None, out_dtype=None):
-    """outputs[b] = sum_i weights[b, i] * source[indexes[b, i]] (+ bias).
-    Reference: weighted_vector_gather_add(indexes, source, weights) (gather/cuda/kernel.py:22-70)."""
+def weighted_vector_gather_add(indexes, source, weights, bias=None, out_dtype=None, residual=None):
+    """outputs[b] = sum_i weights[b, i] * source[indexes[b, i]] (+ bias) (+ residual[b]).
+    Reference: weighted_vector_gather_add(indexes, source, weights) (gather/cuda/kernel.py:22-70); the bias add
+    of lookup.py:108 and the residual add of layer.py:75-78 ride in the kernel's epilogue when given."""
     _check_gather_args(indexes, source, weights)
     indexes, source, weights = _contig(indexes), _contig(source), _contig(weights)
     N, I = indexes.shape
@@ -264,10 +274,13 @@ def weighted_vector_gather_add(indexes, source, weights, bias=None, out_dtype=No
     out = torch.empty((N, d), dtype=out_dtype, device=source.device)
     if bias is not None:
         bias = _contig(bias.float())
+    if residual is not None:
+        L.require_cuda(residual)
+        residual = _contig(residual.reshape(N, d).to(out_dtype))
     with torch.cuda.device(source.device):
-        L.check(L.lib().lffn_gather_fwd(L.ptr(indexes), L.ptr(weights), L.ptr(source), L.dtype_code(source.dtype),
-                                        L.ptr(out), L.dtype_code(out_dtype), N, I, S, d, L.ptr(bias),
-                                        L.stream_ptr(source.device)))
+        L.check(L.lib().lffn_gather_fwd_residual(L.ptr(indexes), L.ptr(weights), L.ptr(source),
+                                                 L.dtype_code(source.dtype), L.ptr(out), L.dtype_code(out_dtype), N, I,
+                                                 S, d, L.ptr(bias), L.ptr(residual), L.stream_ptr(source.device)))
     return out
 
 

@@ -11,6 +11,8 @@ Outputs
   oracle/liblffn_oracle.so   C restatement (oracle/lffn_oracle.c)
   oracle/_ref/ccs_cpu*.so          reference compute_code_score extension, unmodified source
   oracle/_ref/gather_add_cpu*.so   reference CPU gather extension, unmodified source
+  oracle/_ref/sbdht_cpu*.so        reference CPU BH4 extension (block-diagonal x Hadamard), unmodified source, compiled
+                                   against the stand-in oracle/standin/libxsmm.h (the real libxsmm is not available)
   oracle/_ref/gather_add*.so       reference CUDA gather extension (fp32 / fp16 kernels), unmodified source, sm_100a
   oracle/_ref/fast_hadamard_transform_kernel*.so   reference CUDA Hadamard extension, unmodified source, sm_100a
 The reference sources are compiled where they lie; nothing is copied.  The two CUDA modules are the GPU comparator:
@@ -37,7 +39,10 @@ REF_EXTENSIONS = {
     # module name -> source relative to prenorm_lookup/
     "ccs_cpu": os.path.join("compute_code_score", "torch_extension.cc"),
     "gather_add_cpu": os.path.join("gather", "cpu", "torch_extension.cpp"),
+    # the CPU BH4 extension includes <libxsmm.h> (third-party, absent): compiled against oracle/standin/libxsmm.h
+    "sbdht_cpu": os.path.join("bh4", "cpu", "torch_extension.cpp"),
 }
+REF_EXTRA_INCLUDES = {"sbdht_cpu": [os.path.join(HERE, "standin")]}
 
 
 def _newer(target, sources):
@@ -102,7 +107,7 @@ def build_ref(force=False, verbose=True):
         cmd = (["g++", "-std=c++17", "-O3", "-mavx2", "-mfma", "-fopenmp", "-fPIC", "-shared", "-w",
                 f"-DTORCH_EXTENSION_NAME={name}", "-DTORCH_API_INCLUDE_EXTENSION_H",
                 f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
-               + inc + [src, "-o", out, f"-L{libdir}", f"-Wl,-rpath,{libdir}",
+               + inc + [f"-I{d}" for d in REF_EXTRA_INCLUDES.get(name, [])] + [src, "-o", out, f"-L{libdir}", f"-Wl,-rpath,{libdir}",
                         "-ltorch_python", "-ltorch", "-ltorch_cpu", "-lc10", "-lgomp"])
         if verbose:
             print(" ".join(cmd), flush=True)

@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from oracle import oracle as O
+from oracle import parity as PAR
 
 pytestmark = pytest.mark.gpu
 
@@ -225,11 +226,35 @@ def test_bh4_matches_reference_golden(dev, golden):
         z = t2n(mod(torch.from_numpy(x).to(dev)))
         zr = golden[f"bh4_{tag}_z"]
         assert rel_err(z, zr) < 2e-5
-        diff = (z > 0) != (zr > 0)
-        assert np.abs(zr[diff]).max(initial=0.0) < 1e-5
+        # signs against the reference's own evaluation: only coordinates with |v| < 1e-6 (fp64 v) may differ
+        z64 = PAR.projection_fp64_torch(torch.from_numpy(x).to(dev), w, mod.bias.detach(), out_dim).cpu().numpy()
+        PAR.assert_codes_match_up_to_tiny_coordinates(z, zr, z64)
     # no bounded wait inside the block kernel (weight chunks arriving by bulk copy) ran out
     from lookupffn_b200 import _lib
     assert _lib.device_status(dev) & _lib.STATUS_TIMEOUT == 0
+
+
+def test_cpu_bh4_convention_matches_reference_cpu_extension(dev):
+    """transpose_w=1 with had_scale=1/D is the projection of the reference's CPU extension
+    (bh4/cpu/torch_extension.cpp:123-196); vectors from that extension itself (tests/golden/sbdht_golden.npz).
+    Both block kernels are exercised: the 64 x 64 fast path ([i][o] weights as given) and the generic one."""
+    import os
+
+    from lookupffn_b200 import ops
+
+    g = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "sbdht_golden.npz")))
+    x, w, out = g["sbdht_x"], g["sbdht_w"], g["sbdht_out"]
+    D = x.shape[1]
+    xd, wd = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+    z = ops.bh4(xd, wd, transpose_w=True, had_scale=1.0 / D)
+    assert rel_err(t2n(z), out) < 2e-6
+    np.testing.assert_array_equal(t2n(z), O.project(x, w, out.shape[1], transpose_w=True, had_scale=1.0 / D,
+                                                    mix_a=1.0, mix_b=0.0))
+    # the same function through the other weight layout: W^T handed over with transpose_w=0 (generic kernel)
+    z2 = ops.bh4(xd, wd.transpose(-1, -2).contiguous(), transpose_w=False, had_scale=1.0 / D)
+    np.testing.assert_array_equal(t2n(z2), t2n(z))
+    f = ops.hadamard(torch.from_numpy(g["fwht_x"]).to(dev), scale=1.0 / D)
+    assert rel_err(t2n(f), g["fwht_out"]) < 1e-6
 
 
 # ---- gather forward ----------------------------------------------------------------------------------
@@ -389,13 +414,15 @@ def test_module_matches_reference_golden(dev, golden, tag):
     assert y.shape == golden[f"mod_{tag}_y"].shape  # leading dims kept (lookup.py:112-118)
     code = t2n(idx) - (np.arange(T) * rows)[None].astype(np.int32)
     ref_code = golden[f"mod_{tag}_code"]
-    # LayerNorm and (dense) the projection run in torch on the GPU: coordinates at rounding level may flip
+    # LayerNorm and (dense) the projection run in torch on the GPU: a code may differ from the reference's only
+    # when one of its coordinates has |v| < 1e-6; tokens without a differing code must match in weights and output
     zr = golden[f"mod_{tag}_z"].reshape(-1, T, int(np.log2(rows)))
     flipped = code != ref_code
-    assert np.abs(zr[flipped]).min(axis=-1).max(initial=0.0) < 1e-5
-    if not flipped.any():
-        assert rel_err(t2n(w), golden[f"mod_{tag}_score"]) < 1e-4
-        assert rel_err(t2n(y), golden[f"mod_{tag}_y"]) < 1e-4
+    assert np.abs(zr[flipped]).min(axis=-1).max(initial=0.0) < PAR.V_EPS
+    clean = ~flipped.any(axis=-1)
+    assert clean.sum() >= 0.9 * clean.size
+    assert rel_err(t2n(w)[clean], golden[f"mod_{tag}_score"].reshape(-1, T)[clean]) < 1e-4
+    assert rel_err(t2n(y).reshape(-1, d_out)[clean], golden[f"mod_{tag}_y"].reshape(-1, d_out)[clean]) < 1e-4
 
 
 def test_module_backward_tables_and_bias(dev):

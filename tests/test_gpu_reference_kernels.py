@@ -133,8 +133,8 @@ def test_fwht_against_reference_fp16_kernels(dev, ref_fht, D):
 def test_layer_against_reference_style_gpu_path(dev, ref_fht, ref_gather):
     """The whole layer against the reference's GPU evaluation (torch.einsum + its Hadamard and gather kernels +
     elementwise torch, oracle/ref_gpu_path.py).  einsum sums in another order than the fused kernel's fmaf chain, so
-    z agrees to rounding, codes may differ only where |z| is at rounding level, and tokens without such a
-    coordinate get the same output to 1e-3 (north_star's fp32 bound)."""
+    z agrees to rounding, codes may differ only on coordinates with |v| < 1e-6, and tokens without such a
+    coordinate get the same output to 1e-3 (the fp32 bound of the task)."""
     from argparse import Namespace
 
     from lookupffn_b200 import ops
@@ -157,8 +157,12 @@ def test_layer_against_reference_style_gpu_path(dev, ref_fht, ref_gather):
         code, score = ops.compute_code_score(z.reshape(-1, 64, 8).contiguous())
         assert torch.equal(code, code_ref)                       # same z in: identical codes
         assert rel_err(score.cpu(), score_ref.cpu()) < 1e-5
+        # signs against the reference's GPU evaluation: only coordinates with |v| < 1e-6 (fp64 v) may differ
+        from oracle import parity as PAR
+
+        z64 = PAR.projection_fp64_torch(h, mod.hash.projection.weight, mod.hash.projection.bias, 64 * 8)
+        rep, _ = PAR.assert_codes_match_up_to_tiny_coordinates(z.cpu().numpy(), z_ref.cpu().numpy(), z64.cpu().numpy())
         flipped = ((z > 0) != (z_ref > 0))
-        assert float(z_ref[flipped].abs().max()) < 1e-5 if bool(flipped.any()) else True
         y = mod(x).reshape(-1, 512)
         y_ref = RG.lookupffn_reference_gpu(mod, x, ref_fht, ref_gather).reshape(-1, 512)
         clean = ~flipped.any(dim=-1)

@@ -6,6 +6,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle as O
+from oracle import parity as PAR
 
 
 def rel_err(a, b):
@@ -62,9 +63,12 @@ def test_bh4_projection_matches_reference(golden, tag):
     z = O.project(x, w, out_dim, bias=bias)
     zr = golden[f"bh4_{tag}_z"]
     assert rel_err(z, zr) < 2e-5
-    # sign bits may differ from an einsum/matmul evaluation only where |z| is at rounding level
-    diff = (z > 0) != (zr > 0)
-    assert np.abs(zr[diff]).max(initial=0.0) < 1e-5
+    # sign bits may differ from the reference's einsum/matmul evaluation only on coordinates with |v| < 1e-6
+    # (v judged on an fp64 evaluation); the disagreements are counted
+    import torch
+
+    z64 = PAR.projection_fp64_torch(torch.from_numpy(x), torch.from_numpy(w), torch.from_numpy(bias), out_dim).numpy()
+    PAR.assert_codes_match_up_to_tiny_coordinates(z, zr, z64)
 
 
 def test_gather_matches_reference(golden):
@@ -127,15 +131,16 @@ def test_whole_module_matches_reference(golden, tag):
     idx, w = O.code_weights(zr, T, k, add_offsets=False)
     np.testing.assert_array_equal(idx, golden[f"mod_{tag}_code"])
     assert rel_err(w, golden[f"mod_{tag}_score"]) < 1e-5
-    # the oracle's own pipeline: codes differ only on coordinates at rounding level
+    # the oracle's own pipeline: codes may differ only on coordinates with |v| < 1e-6; tokens without such a
+    # coordinate must give the reference's codes exactly and its output to 1e-4
     idx2, w2 = O.code_weights(z, T, k, add_offsets=False)
-    diff = (z > 0) != (zr > 0)
-    assert np.abs(zr[diff]).max(initial=0.0) < 1e-5
-    if not diff.any():
-        np.testing.assert_array_equal(idx2, golden[f"mod_{tag}_code"])
-        off = (np.arange(T) * rows)[None].astype(np.int32)
-        y = O.gather(idx2 + off, w2, P["tables"].reshape(T * rows, d_out), bias=P["bias"])
-        assert rel_err(y, golden[f"mod_{tag}_y"].reshape(-1, d_out)) < 1e-4
+    _, diff = PAR.assert_codes_match_up_to_tiny_coordinates(z, zr)
+    clean = ~diff.any(axis=-1)
+    assert clean.sum() >= 0.9 * clean.size
+    np.testing.assert_array_equal(idx2[clean], golden[f"mod_{tag}_code"][clean])
+    off = (np.arange(T) * rows)[None].astype(np.int32)
+    y = O.gather(idx2 + off, w2, P["tables"].reshape(T * rows, d_out), bias=P["bias"])
+    assert rel_err(y[clean], golden[f"mod_{tag}_y"].reshape(-1, d_out)[clean]) < 1e-4
     if tag == "bh4":
         y2 = O.layer_fwd(x2, P["hash.projection.weight"], P["tables"], T, k,
                          ln=(P["LayerNorm.weight"], P["LayerNorm.bias"], 1e-5),
@@ -143,3 +148,20 @@ def test_whole_module_matches_reference(golden, tag):
         off = (np.arange(T) * rows)[None].astype(np.int32)
         np.testing.assert_array_equal(
             y2, O.gather(idx2 + off, w2, P["tables"].reshape(T * rows, d_out), bias=P["bias"]))
+
+
+def test_cpu_bh4_convention_matches_reference_cpu_extension():
+    """The reference's CPU inference path computes the projection with x . W per block and H / D
+    (bh4/cpu/torch_extension.cpp:123-196), not the x . W^T and unnormalised H of its CUDA/training path.  The
+    oracle reaches it with transpose_w=True, had_scale=1/D; tests/golden/sbdht_golden.npz holds outputs of the
+    reference's own CPU extension (built against a stand-in libxsmm header, make_sbdht_golden.py)."""
+    import os
+
+    g = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "sbdht_golden.npz")))
+    x, w, out = g["sbdht_x"], g["sbdht_w"], g["sbdht_out"]
+    D = x.shape[1]
+    z = O.project(x, w, out.shape[1], transpose_w=True, had_scale=1.0 / D, mix_a=1.0, mix_b=0.0)
+    assert rel_err(z, out) < 2e-6          # summation order of the 64-term products and of the butterflies differs
+    other = O.project(x, w, out.shape[1], transpose_w=False, had_scale=1.0 / D, mix_a=1.0, mix_b=0.0)
+    assert rel_err(other, out) > 0.5       # the CUDA convention is a different function of the same weights
+    assert rel_err(O.fwht(g["fwht_x"], 1.0 / D), g["fwht_out"]) < 1e-6
