@@ -303,19 +303,23 @@ def run_ours(args, rank, world, local):
     l2_resident_ms = ev_l2[0].elapsed_time(ev_l2[1]) / 3
     del idx_l2, y_l2
 
-    # Hardware ceiling of that access pattern: plain coalesced 16-byte reads of a 32 MiB buffer that stays in L2,
-    # issued by the gather's grid with the gather's number of loads in flight (lffn_probe_read).  Outside the timed
-    # region.  One launch reads about as many bytes as the gather launch does.
+    # Hardware ceiling of that access pattern: plain coalesced 16-byte reads of a 32 MiB buffer that stays in L2
+    # (lffn_probe_read), in three configurations of loads in flight per SM; the best one is the ceiling.  Outside
+    # the timed region.  One launch reads about as many bytes as the gather launch does.
     probe_bytes = min(32 << 20, tables.numel() * tables.element_size()) // 16 * 16
     reps = max(8, int(algorithmic_bytes_per_token(w) * N // probe_bytes))
     sink = torch.zeros(1, dtype=torch.int32, device=device)
-    L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, 4, L.ptr(sink), sp))
-    ev_p = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    ev_p[0].record(stream)
-    L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, reps, L.ptr(sink), sp))
-    ev_p[1].record(stream)
-    torch.cuda.synchronize()
-    l2_read_peak = probe_bytes * reps / (ev_p[0].elapsed_time(ev_p[1]) * 1e-3) / 1e9  # GB/s
+    l2_probe = {}
+    for mode, name in ((0, "12_loads_per_thread_gather_residency"), (1, "8_loads_per_thread_full_occupancy"),
+                       (2, "16_loads_per_thread_full_occupancy")):
+        L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, 4, mode, L.ptr(sink), sp))
+        ev_p = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev_p[0].record(stream)
+        L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, reps, mode, L.ptr(sink), sp))
+        ev_p[1].record(stream)
+        torch.cuda.synchronize()
+        l2_probe[name] = probe_bytes * reps / (ev_p[0].elapsed_time(ev_p[1]) * 1e-3) / 1e9  # GB/s
+    l2_read_peak = max(l2_probe.values())
 
     if args.no_e2e:  # profiling runs: device path only
         if rank == 0:
@@ -429,8 +433,9 @@ def run_ours(args, rank, world, local):
                      "dram_frac": traffic / (gather_ms * 1e-3) / 1e9 / peak if traffic else None,
                      "l2_hit_rate": prof["l2_hit_rate"] if prof else None,
                      "l2_read_peak": l2_read_peak, "frac_of_l2_read_peak": achieved / l2_read_peak,
-                     "l2_read_peak_source": "lffn_probe_read: 16-byte loads of an L2-resident 32 MiB buffer by the "
-                                            "gather's grid, measured in this run",
+                     "l2_read_peak_source": "lffn_probe_read: 16-byte loads of an L2-resident 32 MiB buffer, best of "
+                                            "three configurations, measured in this run",
+                     "l2_read_probe_GBps": l2_probe,
                      # the same launch with all indices folded into an L2-resident band of 32 tables:
                      "l2_resident_launch_ms": l2_resident_ms, "frac_of_l2_resident_launch": l2_resident_ms / gather_ms},
         "e2e": {"value": e2e_value, "unit": "tokens/s",
@@ -728,6 +733,75 @@ def run_train_gather(args, rank, world, local):
     }
 
 
+def run_train_layer(args, rank, world, local):
+    """One training step (forward + full backward: tables, bias, projection weights and bias, LayerNorm, input) of a
+    LookupFFN layer with the reference's pre-training shape (cfgs/roberta/small-512/lookup-t128-s8-bh4.py: hidden
+    512, 128 tables of 256 rows, BH4 projection with 64 x 64 blocks; 64 sequences x 512 tokens = 32768 tokens per
+    GPU), fp32, beside the reference's autograd over its own CUDA kernels on the same module and inputs."""
+    from argparse import Namespace
+
+    from lookupffn_b200 import LookupFFN
+
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    cfg = Namespace(hidden_size=512, ffn_num_table=128, ffn_table_size=256, layer_norm_eps=1e-5, projection_type="bh4",
+                    block_size=64)
+    torch.manual_seed(77)
+    mod = LookupFFN(cfg, 512).to(device).train()
+    N = args.tokens or 32768
+    gen = torch.Generator(device=device).manual_seed(5 + rank)
+    x = torch.randn(N, 512, generator=gen, device=device, requires_grad=True)
+    dy = torch.randn(N, 512, generator=gen, device=device)
+
+    def step(fn):
+        for q in mod.parameters():
+            q.grad = None
+        x.grad = None
+        y = fn(x)
+        y.backward(dy)
+        return y
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            step(fn)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step(fn)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    steps = min(args.steps, 10)
+    ms = timed(mod, steps, 3)
+    ours = {n: q.grad.clone() for n, q in mod.named_parameters()}
+    ours["x"] = x.grad.clone()
+    comparator = None
+    if not args.no_cpu_baseline:
+        from oracle import build as obuild
+
+        fht = obuild.load_ref_module("fast_hadamard_transform_kernel")
+        gat = obuild.load_ref_module("gather_add")
+        if fht is not None and gat is not None:
+            from oracle.ref_gpu_path import lookupffn_reference_gpu_training
+
+            ref_fn = lambda t: lookupffn_reference_gpu_training(mod, t, fht, gat)  # noqa: E731
+            ref_ms = timed(ref_fn, min(steps, 5), 2)
+            ref = {n: q.grad.clone() for n, q in mod.named_parameters()}
+            ref["x"] = x.grad.clone()
+            comparator = {"what": "the reference's autograd over torch.einsum, its Hadamard, gather, inner-product and "
+                                  "scatter-add CUDA kernels (compiled unmodified for sm_100a) on the same module",
+                          "ms_per_step": ref_ms, "ratio": ref_ms / ms,
+                          "gradient_max_abs_diff_over_max_abs":
+                              {n: float((ours[n] - ref[n]).abs().max() / ref[n].abs().max()) for n in ours}}
+    if rank != 0:
+        return None
+    return {"metric": "lookupffn_layer_training_step", "value": N / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+            "steps": steps, "config": f"LookupFFN forward + backward, N={N} tokens, hidden 512, T=128, k=8, bh4 64x64, fp32",
+            "gpu_comparator": comparator}
+
+
 def encoder_gpu_comparator(model, step, B, S, cfg, device):
     """Baseline leg of the encoder run (N = 1, outside the timed region): the same model with every FFN evaluated the
     way the reference does it on a GPU -- torch.einsum for the 64 x 64 blocks, the reference's own Hadamard and
@@ -768,13 +842,17 @@ def encoder_gpu_comparator(model, step, B, S, cfg, device):
 
         T, rows = ffn.num_table, ffn.table_size
         k = int(np.log2(rows))
-        hn = ffn.LayerNorm(h.reshape(-1, cfg.hidden_size))
+        h2 = h.reshape(-1, cfg.hidden_size)
+        ln = (ffn.LayerNorm.weight, ffn.LayerNorm.bias, ffn.LayerNorm.eps)
         pw, pb = ffn.hash.projection.weight, ffn.hash.projection.bias
-        z_ours = ffn.hash.projection(hn)
-        z_ref = projection_reference_gpu(hn, pw, pb, T * k, fht)
-        z64 = PAR.projection_fp64_torch(hn, pw, pb, T * k)
+        # ours: the inference path, LayerNorm inside the hash kernel; reference: torch LayerNorm, einsum, its own
+        # Hadamard kernel; fp64: the same formulas in double from a double LayerNorm
+        z_ours = ffn.hash.project(h2, layer_norm=ln)
+        z_ref = projection_reference_gpu(ffn.LayerNorm(h2), pw, pb, T * k, fht)
+        hn64 = torch.nn.functional.layer_norm(h2.double(), (cfg.hidden_size,), ln[0].double(), ln[1].double(), ln[2])
+        z64 = PAR.projection_fp64_torch(hn64, pw, pb, T * k)
         parity = PAR.sign_mismatch_report(z_ours.cpu().numpy(), z_ref.cpu().numpy(), z64.cpu().numpy())
-        code_ours = ffn.hash(hn)[0] - (torch.arange(T, device=device, dtype=torch.int32) * rows)[None]
+        code_ours = ffn.hash(h2, layer_norm=ln)[0] - (torch.arange(T, device=device, dtype=torch.int32) * rows)[None]
         code_ref = code_score_reference_gpu(z_ref.reshape(-1, T, k))[0]
         differ = code_ours != code_ref
         clean = ~differ.any(dim=-1)
@@ -783,12 +861,15 @@ def encoder_gpu_comparator(model, step, B, S, cfg, device):
                        "tokens": int(clean.numel()), "tokens_without_a_differing_code": int(clean.sum()),
                        "ffn_output_max_rel_err_on_those_tokens":
                            float((yo[clean] - yr[clean]).abs().max() / yr[clean].abs().max()) if bool(clean.any()) else None})
+        del hn64
         del z64, z_ours, z_ref
     patched = []
     try:
         for layer in model.encoder.layer:
             m = layer.FFN
-            m.forward = (lambda hs, m=m: lookupffn_reference_gpu(m, hs, fht, gat))
+            m.forward = (lambda hs, residual=None, m=m:
+                         lookupffn_reference_gpu(m, hs, fht, gat) if residual is None
+                         else lookupffn_reference_gpu(m, hs, fht, gat) + residual)
             patched.append(m)
         ref_out = step().float()
         ref_ms = time_ms(step, 5)
@@ -1072,7 +1153,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c2enc", "c4"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c2enc", "c4", "train"])
     ap.add_argument("--projection", default="bh4", choices=["bh4", "sign_hadamard", "dense"],
                     help="projection of the c2enc workload (bh4 = the reference configs)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -1110,8 +1191,8 @@ def main():
         torch.cuda.set_device(local)
         torch.distributed.init_process_group("nccl", rank=rank, world_size=world,
                                              device_id=torch.device("cuda", local))
-    if args.workload in ("c2enc", "c4"):
-        out = run_encoder(args, rank, world, local) if args.workload == "c2enc" else run_train_gather(args, rank, world, local)
+    if args.workload in ("c2enc", "c4", "train"):
+        out = {"c2enc": run_encoder, "c4": run_train_gather, "train": run_train_layer}[args.workload](args, rank, world, local)
         if out is not None:
             print(json.dumps(out), flush=True)
         if world > 1:
@@ -1155,6 +1236,8 @@ def main():
             out["training_gather_c4"] = {k: c4[k] for k in ("value", "unit", "ms_per_step", "kernels_ms",
                                                             "algorithmic_GBps", "gpu_comparator", "steps")}
             out["training_gather_c4"]["config"] = c4["config"]["workload"]
+            torch.cuda.empty_cache()
+            out["training_step_reference_layer_shape"] = run_train_layer(c4_args, rank, world, local)
         print(json.dumps(out), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -92,6 +92,22 @@ typedef struct lffn_hash_desc {
 int lffn_version(void);
 const char *lffn_last_error_string(void);
 
+/*
+ * Tracing, off by default (the reference carries per-stage wall-clock timers around projection, code/score and
+ * gather, commented out: lookup.py:67-75,103-106).
+ *   LFFN_TRACE_NVTX         every entry point brackets its host-side work with an NVTX range named after it, so
+ *                           a timeline tool shows which call enqueued which kernels
+ *   LFFN_TRACE_STAGE_TIMES  lffn_layer_fwd / lffn_layer_fwd_ln_residual record CUDA events before the hash kernel,
+ *                           between the two kernels and after the gather; lffn_trace_last_layer_times waits for
+ *                           the last such call on the current device and returns the two durations in ms
+ * The flags are process-wide.  With stage times on, whole-layer calls on one device should come from one stream at
+ * a time (the events are per device); lffn_layer_fwd_host issues many such calls and leaves the last chunk's times.
+ */
+#define LFFN_TRACE_NVTX 1u
+#define LFFN_TRACE_STAGE_TIMES 2u
+int lffn_trace_configure(uint32_t flags);
+int lffn_trace_last_layer_times(float *hash_ms, float *gather_ms);
+
 /* Reads and clears the status word of the current device with one atomic exchange on `stream`, then
  * synchronises `stream`.  A flag raised concurrently by a kernel on another stream is never lost: it is either in
  * this value or in the next one. */
@@ -107,12 +123,15 @@ int lffn_selftest_bounded_wait(int32_t poll_limit, lffn_stream_t stream);
 
 /*
  * Measurement probe (no reference counterpart; not on the layer's path): reads `bytes` bytes at `buf` `repeats`
- * times with the gather kernel's access pattern -- coalesced 16-byte read-only loads, twelve in flight per
- * thread, the gather's grid.  With a buffer that fits L2 and several repeats, bytes * repeats / elapsed time is
- * the L2 read bandwidth this pattern can reach: the ceiling the benchmark quotes the gather against.  `sink` is
- * one device word that keeps the loads observable (it is practically never written).
+ * times with the gather kernel's kind of access -- coalesced 16-byte read-only loads that bypass L1.  With a
+ * buffer that fits L2 and several repeats, bytes * repeats / elapsed time is an L2 read bandwidth.  How much an SM
+ * keeps in flight decides the rate, so there are three configurations: mode 0 = 12 loads per thread at the gather
+ * kernel's own residency (4 CTAs of 128 threads per SM), mode 1 = 8 and mode 2 = 16 loads per thread at full
+ * occupancy.  The benchmark quotes the gather against the best of them.  `sink` is one device word that keeps the
+ * loads observable (it is practically never written).
  */
-int lffn_probe_read(const void *buf, size_t bytes, int32_t repeats, uint32_t *sink, lffn_stream_t stream);
+int lffn_probe_read(const void *buf, size_t bytes, int32_t repeats, int32_t mode, uint32_t *sink,
+                    lffn_stream_t stream);
 
 /*
  * Walsh-Hadamard transform of each row, out = x H_D * scale.  Replaces
@@ -160,6 +179,25 @@ int lffn_code_weights(const float *z, int64_t N, int32_t T, int32_t k, int32_t b
  */
 int lffn_code_weights_bwd(const float *z, const float *dw, int64_t N, int32_t T, int32_t k, int32_t weight_mode,
                           float tau, float *dz, lffn_stream_t stream);
+
+/*
+ * Backward pass of the block-diagonal projection z = BH4(x) for training: what autograd derives from bh4_cuda's
+ * chain of torch.einsum("bni,noi->bno") and Hadamard transforms (bh4/kernel.py:23-36; the transform's backward is
+ * the transform, bh4/fast_hadamard_transform/kernel.py:47-54) and from the mix / slice / bias of lookup.py:29-39.
+ *   desc       the projection as for lffn_hash_fwd with T*k = the number of output columns of z, BS = 64,
+ *              D in {256, 512, 1024}, transpose_w = 1 and desc->proj_w the weights in [R, S, D/64, i, o] order
+ *              (the copy the forward fast path uses); desc->proj_bias is not read
+ *   proj_w_oi  the same weights in the parameter's own order [R, S, D/64, o, i]
+ *   x          [N, d_in] of x_dtype, the input of the forward call;   dz  fp32 [N, T*k], the upstream gradient
+ *   du         fp32 [N, D]: gradient with respect to the zero-padded input (its first d_in columns are dx), or NULL
+ *   dw         fp32 [R, S, D/64, 64, 64] in the parameter's order, or NULL;   dbias  fp32 [T*k], or NULL
+ *   ws         workspace of lffn_proj_bwd_ws_bytes(desc, N) bytes, 256-byte aligned
+ * The stage inputs are recomputed, not kept from the forward pass.  fp32 fused multiply-adds throughout, no
+ * atomics: results are the same from run to run.
+ */
+size_t lffn_proj_bwd_ws_bytes(const lffn_hash_desc *desc, int64_t N);
+int lffn_proj_bwd(const lffn_hash_desc *desc, const float *proj_w_oi, const void *x, int32_t x_dtype, int64_t N,
+                  const float *dz, float *du, float *dw, float *dbias, void *ws, size_t ws_bytes, lffn_stream_t stream);
 
 /*
  * out[n, :] = sum_i w[n, i] * tables[idx[n, i], :] (+ bias): replaces

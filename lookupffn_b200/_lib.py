@@ -16,6 +16,7 @@ F32, BF16 = 0, 1
 MSB_FIRST, LSB_FIRST = 0, 1
 WEIGHT_SCORE, WEIGHT_ONES, WEIGHT_SOFT_FLIP = 0, 1, 2
 STATUS_INDEX_RANGE, STATUS_STRUCTURE, STATUS_TIMEOUT = 1, 2, 4
+TRACE_NVTX, TRACE_STAGE_TIMES = 1, 2
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 ERR_NAMES = {-1: "INVALID_ARG", -2: "UNSUPPORTED", -3: "CUDA", -4: "INDEX_RANGE", -5: "SCRATCH"}
@@ -40,9 +41,11 @@ class HashDesc(C.Structure):
 _SIGNATURES = {
     "lffn_version": (C.c_int, []),
     "lffn_last_error_string": (C.c_char_p, []),
+    "lffn_trace_configure": (C.c_int, [C.c_uint32]),
+    "lffn_trace_last_layer_times": (C.c_int, [C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "lffn_device_status": (C.c_int, [C.POINTER(C.c_uint32), C.c_void_p]),
     "lffn_selftest_bounded_wait": (C.c_int, [C.c_int32, C.c_void_p]),
-    "lffn_probe_read": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int32, C.c_void_p, C.c_void_p]),
+    "lffn_probe_read": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "lffn_fwht": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]),
     "lffn_hash_fwd": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -52,6 +55,9 @@ _SIGNATURES = {
                                     C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "lffn_code_weights_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                         C.c_void_p, C.c_void_p]),
+    "lffn_proj_bwd_ws_bytes": (C.c_size_t, [C.POINTER(HashDesc), C.c_int64]),
+    "lffn_proj_bwd": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p,
+                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "lffn_gather_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int64,
                                   C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "lffn_gather_fwd_residual": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
@@ -99,7 +105,7 @@ def lib():
                 "(nvcc, sm_100a).  lookupffn_b200 has no CPU or PyTorch fallback.")
         handle = C.CDLL(LIB_PATH)
         for name, (res, args) in _SIGNATURES.items():
-            fn = getattr(handle, name)
+            fn = getattr(handle, name)  # AttributeError here = the library is older than this binding: rebuild it
             fn.restype = res
             fn.argtypes = args
         _lib = handle

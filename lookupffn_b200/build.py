@@ -60,7 +60,7 @@ def build(force=False, verbose=False, ptxas_info=False, defines=(), output=None)
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
         objs = list(pool.map(compile_one, sources()))
-    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a"] + objs + ["-o", lib]
+    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a"] + objs + ["-o", lib, "-ldl"]
     if verbose:
         print(" ".join(link), flush=True)
     subprocess.check_call(link)

@@ -4,6 +4,8 @@
 #include <cstring>
 #include <mutex>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 
 namespace lffn {
@@ -77,6 +79,45 @@ static uint32_t *status_slot() {
     return b + next.fetch_add(1, std::memory_order_relaxed) % STATUS_SLOTS;
 }
 
+// ---- tracing (off unless lffn_trace_configure turns it on) ------------------------------------------------------
+static std::atomic<uint32_t> g_trace_flags{0};
+
+// NVTX range for the duration of an entry point's host-side work (launches are asynchronous: the range brackets
+// the enqueue, which is what a timeline tool lines up with the kernels it records itself)
+struct TraceRange {
+    bool on;
+    explicit TraceRange(const char *name) : on((g_trace_flags.load(std::memory_order_relaxed) & LFFN_TRACE_NVTX) != 0) {
+        if (on) nvtxRangePushA(name);
+    }
+    ~TraceRange() {
+        if (on) nvtxRangePop();
+    }
+};
+
+// events around the two stages of the last whole-layer call on each device
+struct StageEvents {
+    cudaEvent_t e[3] = {nullptr, nullptr, nullptr};
+    bool recorded = false;
+};
+static StageEvents g_stage_events[MAX_DEV];
+static std::mutex g_stage_mu[MAX_DEV];
+
+static bool stage_times_on() { return (g_trace_flags.load(std::memory_order_relaxed) & LFFN_TRACE_STAGE_TIMES) != 0; }
+
+// records event `which` of the current device on `st`; creates the three events on first use
+static int stage_event_record(int which, cudaStream_t st) {
+    int dev = 0;
+    LFFN_CHECK_CUDA(cudaGetDevice(&dev));
+    LFFN_REQUIRE(dev >= 0 && dev < MAX_DEV, LFFN_ERR_UNSUPPORTED, "device ordinal %d", dev);
+    std::lock_guard<std::mutex> lock(g_stage_mu[dev]);
+    StageEvents &E = g_stage_events[dev];
+    for (int i = 0; i < 3; i++)
+        if (E.e[i] == nullptr) LFFN_CHECK_CUDA(cudaEventCreate(&E.e[i]));
+    LFFN_CHECK_CUDA(cudaEventRecord(E.e[which], st));
+    if (which == 2) E.recorded = true;
+    return LFFN_OK;
+}
+
 static int check_hash_desc(const lffn_hash_desc *h, int t_begin, int t_count) {
     LFFN_REQUIRE(h != nullptr, LFFN_ERR_INVALID_ARG, "hash descriptor is NULL");
     LFFN_REQUIRE(h->proj_w != nullptr, LFFN_ERR_INVALID_ARG, "hash descriptor: proj_w is NULL");
@@ -122,6 +163,28 @@ extern "C" {
 
 int lffn_version(void) { return LFFN_VERSION; }
 
+int lffn_trace_configure(uint32_t flags) {
+    LFFN_REQUIRE((flags & ~(uint32_t)(LFFN_TRACE_NVTX | LFFN_TRACE_STAGE_TIMES)) == 0, LFFN_ERR_INVALID_ARG,
+                 "trace_configure: unknown flag bits in 0x%x", flags);
+    g_trace_flags.store(flags, std::memory_order_relaxed);
+    return LFFN_OK;
+}
+
+int lffn_trace_last_layer_times(float *hash_ms, float *gather_ms) {
+    LFFN_REQUIRE(hash_ms != nullptr && gather_ms != nullptr, LFFN_ERR_INVALID_ARG, "trace_last_layer_times: NULL output");
+    int dev = 0;
+    LFFN_CHECK_CUDA(cudaGetDevice(&dev));
+    LFFN_REQUIRE(dev >= 0 && dev < MAX_DEV, LFFN_ERR_UNSUPPORTED, "device ordinal %d", dev);
+    std::lock_guard<std::mutex> lock(g_stage_mu[dev]);
+    StageEvents &E = g_stage_events[dev];
+    LFFN_REQUIRE(E.recorded, LFFN_ERR_INVALID_ARG,
+                 "trace_last_layer_times: no whole-layer call was made on this device with LFFN_TRACE_STAGE_TIMES on");
+    LFFN_CHECK_CUDA(cudaEventSynchronize(E.e[2]));
+    LFFN_CHECK_CUDA(cudaEventElapsedTime(hash_ms, E.e[0], E.e[1]));
+    LFFN_CHECK_CUDA(cudaEventElapsedTime(gather_ms, E.e[1], E.e[2]));
+    return LFFN_OK;
+}
+
 const char *lffn_last_error_string(void) { return g_err; }
 
 int lffn_device_status(uint32_t *status_out, lffn_stream_t stream) {
@@ -154,6 +217,7 @@ int lffn_fwht(const void *x, void *out, int64_t N, int32_t D, int32_t dtype, flo
 int lffn_hash_fwd_ln(const lffn_hash_desc *desc, const float *ln_gamma, const float *ln_beta, float ln_eps,
                      const void *x, int32_t x_dtype, int64_t N, int32_t t_begin, int32_t t_count, int32_t *idx_out,
                      float *w_out, float *z_out, lffn_stream_t stream) {
+    TraceRange range("lffn_hash_fwd");
     int rc = check_hash_desc(desc, t_begin, t_count);
     if (rc != LFFN_OK) return rc;
     LFFN_REQUIRE(N >= 0, LFFN_ERR_INVALID_ARG, "hash_fwd: N = %lld", (long long)N);
@@ -211,6 +275,7 @@ int lffn_gather_fwd(const int32_t *idx, const float *w, const void *tables, int3
 int lffn_gather_fwd_residual(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype, void *out,
                              int32_t out_dtype, int64_t N, int32_t I, int64_t S, int32_t d, const float *bias,
                              const void *residual, lffn_stream_t stream) {
+    TraceRange range("lffn_gather_fwd");
     int rc = check_gather(N, I, S, d, table_dtype);
     if (rc != LFFN_OK) return rc;
     LFFN_REQUIRE(out_dtype == LFFN_F32 || out_dtype == LFFN_BF16, LFFN_ERR_INVALID_ARG, "gather_fwd: out dtype %d",
@@ -246,6 +311,7 @@ int lffn_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tabl
 
 int lffn_gather_bwd_weights(const int32_t *idx, const float *dy, const void *tables, int32_t table_dtype, float *dw,
                             int64_t N, int32_t I, int64_t S, int32_t d, lffn_stream_t stream) {
+    TraceRange range("lffn_gather_bwd_weights");
     int rc = check_gather(N, I, S, d, table_dtype);
     if (rc != LFFN_OK) return rc;
     if (N == 0 || I == 0) return LFFN_OK;  // nothing to do; empty buffers may be NULL
@@ -275,6 +341,7 @@ size_t lffn_gather_bwd_tables_sorted_scratch_bytes(int64_t N, int32_t T, int32_t
 int lffn_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const float *dy, float *dtables, int64_t N,
                                   int32_t T, int32_t m, int32_t rows, int32_t d, void *scratch, size_t scratch_bytes,
                                   lffn_stream_t stream) {
+    TraceRange range("lffn_gather_bwd_tables_sorted");
     LFFN_REQUIRE(T >= 1 && m >= 1 && rows >= 1, LFFN_ERR_INVALID_ARG, "gather_bwd_tables_sorted: bad T/m/rows");
     int rc = check_gather(N, T * m, (int64_t)T * rows, d, LFFN_F32);
     if (rc != LFFN_OK) return rc;
@@ -298,12 +365,20 @@ int lffn_layer_fwd_ln_residual(const lffn_hash_desc *desc, const float *ln_gamma
                                const void *tables, int32_t table_dtype, int32_t d_out, const float *bias,
                                const void *residual, void *out, int32_t out_dtype, int32_t *idx_ws, float *w_ws,
                                lffn_stream_t stream) {
-    int rc = lffn_hash_fwd_ln(desc, ln_gamma, ln_beta, ln_eps, x, x_dtype, N, t_begin, t_count, idx_ws, w_ws, nullptr,
-                              stream);
+    TraceRange range("lffn_layer_fwd");
+    const bool timed = stage_times_on();
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = LFFN_OK;
+    if (timed && (rc = stage_event_record(0, st)) != LFFN_OK) return rc;
+    rc = lffn_hash_fwd_ln(desc, ln_gamma, ln_beta, ln_eps, x, x_dtype, N, t_begin, t_count, idx_ws, w_ws, nullptr, stream);
     if (rc != LFFN_OK) return rc;
+    if (timed && (rc = stage_event_record(1, st)) != LFFN_OK) return rc;
     const int m = desc->weight_mode == LFFN_WEIGHT_SOFT_FLIP ? desc->k + 1 : 1;
-    return lffn_gather_fwd_residual(idx_ws, w_ws, tables, table_dtype, out, out_dtype, N, t_count * m,
-                                    (int64_t)t_count << desc->k, d_out, bias, residual, stream);
+    rc = lffn_gather_fwd_residual(idx_ws, w_ws, tables, table_dtype, out, out_dtype, N, t_count * m,
+                                  (int64_t)t_count << desc->k, d_out, bias, residual, stream);
+    if (rc != LFFN_OK) return rc;
+    if (timed) rc = stage_event_record(2, st);
+    return rc;
 }
 
 constexpr int HOST_LANES = 3;  // streams alternating over token chunks in lffn_layer_fwd_host

@@ -155,14 +155,16 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
                         buf[u][v] = FULLV ? ld_row16(row + c) : ld_row16_pred(row + c, c < nvec);
                     }
                 }
+                {
 #pragma unroll
-                for (int u = 0; u < U; u++) {
+                    for (int u = 0; u < U; u++) {
 #pragma unroll
-                    for (int v = 0; v < VPL; v++) {
-                        float f[EPV];
-                        Elem<TableT>::unpack(buf[u][v], f);
+                        for (int v = 0; v < VPL; v++) {
+                            float f[EPV];
+                            Elem<TableT>::unpack(buf[u][v], f);
 #pragma unroll
-                        for (int e = 0; e < EPV; e++) acc[v][e] = fmaf(ww[u], f[e], acc[v][e]);
+                            for (int e = 0; e < EPV; e++) acc[v][e] = fmaf(ww[u], f[e], acc[v][e]);
+                        }
                     }
                 }
             }
@@ -279,6 +281,9 @@ static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, 
     int per_sm = 0;
     LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, 0));
     if (per_sm < 1) per_sm = 1;
+#ifdef LFFN_GATHER_CTAS_PER_SM
+    if (per_sm > LFFN_GATHER_CTAS_PER_SM) per_sm = LFFN_GATHER_CTAS_PER_SM;  // tuning builds: leave room on the SM
+#endif
     const long long want = (N + THREADS / 32 - 1) / (THREADS / 32);
     long long grid = (long long)num_sms() * per_sm;
     if (grid > want) grid = want;

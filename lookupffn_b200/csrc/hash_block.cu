@@ -389,7 +389,22 @@ constexpr int HF_BAR_FLOATS = 4 * HF_NBUF;     // a full and an empty mbarrier p
 // X0: shared memory has room for a second [D][HB_MP] array (D <= 512): the input tile is loaded once per tile and
 // kept there; the first stage of every rotation reads it directly and the mix at the end of a rotation takes u
 // from it, instead of eight passes over the tile's rows in global memory per tile.
-template <typename XT, int THREADS, bool X0>
+//
+// MODE selects what the tile pipeline is used for:
+//   0  the hashing stage itself (codes, weights, optionally z)
+//   1  the same forward walk for training's backward pass: the input y_s of every stage s is saved to
+//      a.act_out[s][tile] ([D][32] per tile, the shared-memory layout without its padding); no codes
+//   2  the backward walk of one rotation: g = mix_a * dz, then for s = S-1 .. 0: g <- H g * had_scale, saved to
+//      a.act_out[s][tile] (this is the gradient at the output of stage s's multiply), g <- g W[r, s] (a.w is then
+//      the parameter in its own [o][i] order, which is input-major for this product); the result, the gradient
+//      with respect to the rotation's input, goes to a.du_out[tile]
+// Modes 1 and 2 are launched for one rotation at a time (r_lo == r_hi).
+template <int THREADS>
+__device__ __forceinline__ void tile_save(const float *Y, float *dst, int D) {
+    for (int i = threadIdx.x; i < D * HB_M; i += THREADS) dst[i] = Y[(i >> 5) * HB_MP + (i & 31)];
+}
+
+template <typename XT, int THREADS, bool X0, int MODE = 0>
 __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     constexpr int PC = THREADS;            // columns per pass
     constexpr int CHUNK = 2 * HF_CHUNK_FLOATS / HF_NBUF;  // floats per weight buffer
@@ -436,7 +451,8 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     // runs HF_NBUF - 1 chunks ahead of the arithmetic.
     int nx_r = a.r_lo + (int)(u_begin % nrot), nx_s = 0, nx_p = 0, nx_h = 0;
     auto next_chunk_src = [&]() -> const float * {
-        const float *src = a.w + (((long long)nx_r * a.S + nx_s) * NB + NBLK * nx_p) * 4096 + nx_h * CR * 64;
+        const int s_eff = MODE == 2 ? a.S - 1 - nx_s : nx_s;  // the backward walk takes the stages in reverse
+        const float *src = a.w + (((long long)nx_r * a.S + s_eff) * NB + NBLK * nx_p) * 4096 + nx_h * CR * 64;
         if (++nx_h == 64 / CR) {
             nx_h = 0;
             if (++nx_p == D / PC) {
@@ -488,7 +504,14 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
         const long long n0 = tile * HB_M;
         const int mt = (int)min((long long)HB_M, a.N - n0);
         const bool first_of_tile = u == u_begin || r == a.r_lo;
-        if constexpr (X0) {
+        if constexpr (MODE == 2) {
+            __syncthreads();  // the previous unit has finished with Y
+            for (int mm = warp; mm < HB_M; mm += NW) {
+                const float *grow = a.dz + (n0 + mm) * a.dz_cols + (long long)r * D;
+                for (int e = lane; e < D; e += 32)
+                    Y[e * HB_MP + mm] = (mm < mt && (long long)r * D + e < a.dz_cols) ? __fmul_rn(a.mix_a, __ldg(grow + e)) : 0.f;
+            }
+        } else if constexpr (X0) {
             if (first_of_tile) {
                 __syncthreads();  // the previous unit has finished reading Xs
                 tile_load<XT, THREADS>(Xs, a, n0, mt, D, lnstat);
@@ -501,8 +524,8 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
         }
         __syncthreads();  // the tile (and the carry rows) are in place
         HB_MARK(HB_PH_TILE);
-        for (int s = 0; s < a.S; s++) {
-            const float *ysrc = (X0 && s == 0) ? Xs : Y;
+        // one stage's block-diagonal multiply: Y <- blockdiag(W) ysrc, pass by pass; false = a bounded wait ran out
+        auto multiply_stage = [&](const float *ysrc) -> bool {
             const int cq = tid % (PC / 4), tq = tid / (PC / 4);   // PC/4 column quads x 4 token octets
             const int g = cq >> 4, o4 = cq & 15;
             for (int p = 0; p < D / PC; p++) {
@@ -516,12 +539,12 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                     HB_MARK(HB_PH_FMA);
                     if (!issue_chunk(gc + HF_NBUF - 1)) {  // that chunk was not requested; the ones before it were
                         give_up(gc, gc + HF_NBUF - 1);
-                        return;
+                        return false;
                     }
                     const int buf = (int)(gc % HF_NBUF);
                     if (!mbar_wait(&full[buf], (unsigned)((gc / HF_NBUF) & 1))) {  // chunk gc has landed
                         give_up(gc, gc + HF_NBUF);
-                        return;
+                        return false;
                     }
                     HB_MARK(HB_PH_CHUNK_WAIT);
                     const float *wb = Wb + buf * CHUNK + g * (CR * 64);
@@ -554,12 +577,34 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                     *reinterpret_cast<ulonglong2 *>(yo + q * HB_MP + 4) = make_ulonglong2(acc[2][q], acc[3][q]);
                 }
             }
-            __syncthreads();
-            HB_MARK(HB_PH_WRITEBACK);
-            fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
-            HB_MARK(HB_PH_HADAMARD);
+            return true;
+        };
+        const size_t tile_floats = (size_t)D * HB_M;
+        if constexpr (MODE == 2) {
+            for (int sb = 0; sb < a.S; sb++) {
+                const int s = a.S - 1 - sb;
+                fwht_tile<NW>(Y, D, a.had_scale, warp, lane);  // ends with a CTA barrier
+                tile_save<THREADS>(Y, a.act_out + ((size_t)s * ntiles + tile) * tile_floats, D);
+                __syncthreads();  // the saved values have been read before the multiply overwrites them
+                if (!multiply_stage(Y)) return;
+                __syncthreads();
+            }
+            tile_save<THREADS>(Y, a.du_out + (size_t)tile * tile_floats, D);
+        } else {
+            for (int s = 0; s < a.S; s++) {
+                const float *ysrc = (X0 && s == 0) ? Xs : Y;
+                if constexpr (MODE == 1) {
+                    tile_save<THREADS>(ysrc, a.act_out + ((size_t)s * ntiles + tile) * tile_floats, D);
+                    __syncthreads();
+                }
+                if (!multiply_stage(ysrc)) return;
+                __syncthreads();
+                HB_MARK(HB_PH_WRITEBACK);
+                fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
+                HB_MARK(HB_PH_HADAMARD);
+            }
+            if constexpr (MODE == 0) tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r, lnstat, Xs);
         }
-        tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r, lnstat, Xs);
 #ifdef LFFN_HB_PHASE_CLOCKS
         __syncthreads();
 #endif
@@ -587,6 +632,40 @@ int launch_bounded_wait_selftest(int poll_limit, cudaStream_t st) {
     uint32_t *status = status_word();
     LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
     bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(poll_limit, status);
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return LFFN_OK;
+}
+
+// The tile pipeline in its training modes (see hash_block64_kernel): mode 1 saves every stage's input, mode 2 walks
+// one rotation backwards.  64 x 64 blocks, D a multiple of 256, a.w input-major for the product at hand.
+int launch_hash_block64_mode(const HashArgs &a, int mode, int x_dtype, cudaStream_t st) {
+    LFFN_REQUIRE(a.D % 256 == 0 && a.D >= 256 && a.D <= 1024 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0,
+                 LFFN_ERR_UNSUPPORTED, "block-diagonal backward: D = %d must be 256, 512 or 1024 and the weights 16-byte aligned", a.D);
+    LFFN_REQUIRE(a.r_lo == a.r_hi && (mode == 1 || mode == 2), LFFN_ERR_INVALID_ARG, "block-diagonal backward: one rotation per launch");
+    const long long ntiles = (a.N + HB_M - 1) / HB_M;
+    long long grid = num_sms();
+    if (grid > ntiles) grid = ntiles;
+    if (grid < 1) grid = 1;
+    const bool wide = a.D % 512 == 0;
+    const size_t smem_b = ((size_t)a.D * HB_MP + HB_WFLOATS + HB_CARRY * HB_MP + HB_LN_FLOATS + HF_BAR_FLOATS) * sizeof(float);
+    const size_t smem_x0 = smem_b + (size_t)a.D * HB_MP * sizeof(float);
+    const bool x0 = mode == 1 && smem_x0 <= 227 * 1024;
+    const size_t smem_k = x0 ? smem_x0 : smem_b;
+    void (*kern)(HashArgs) = nullptr;
+    if (mode == 2) {
+        kern = wide ? hash_block64_kernel<float, 512, false, 2> : hash_block64_kernel<float, 256, false, 2>;
+    } else if (x_dtype == LFFN_F32) {
+        kern = wide ? (x0 ? hash_block64_kernel<float, 512, true, 1> : hash_block64_kernel<float, 512, false, 1>)
+                    : (x0 ? hash_block64_kernel<float, 256, true, 1> : hash_block64_kernel<float, 256, false, 1>);
+    } else if (x_dtype == LFFN_BF16) {
+        kern = wide ? (x0 ? hash_block64_kernel<__nv_bfloat16, 512, true, 1> : hash_block64_kernel<__nv_bfloat16, 512, false, 1>)
+                    : (x0 ? hash_block64_kernel<__nv_bfloat16, 256, true, 1> : hash_block64_kernel<__nv_bfloat16, 256, false, 1>);
+    } else {
+        set_error("block-diagonal backward: unknown x dtype %d", x_dtype);
+        return LFFN_ERR_INVALID_ARG;
+    }
+    LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k));
+    kern<<<(unsigned)grid, wide ? 512 : 256, smem_k, st>>>(a);
     LFFN_CHECK_CUDA(cudaGetLastError());
     return LFFN_OK;
 }

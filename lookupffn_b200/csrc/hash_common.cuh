@@ -26,6 +26,11 @@ struct HashArgs {
     const float *ln_g;
     const float *ln_b;
     float ln_eps;
+    // training's backward pass through a block-diagonal projection (hash_block64_kernel modes 1 and 2, proj_bwd.cu)
+    float *act_out;    // [S][tiles][D][32]: stage inputs (mode 1) or transformed stage-output gradients (mode 2)
+    const float *dz;   // mode 2: upstream gradient [N, dz_cols]
+    int dz_cols;
+    float *du_out;     // mode 2: gradient with respect to the rotation's input, [tiles][D][32]
 };
 
 // LayerNorm statistics of one row held by a warp: `sum` and then `sq` are this lane's partial sums.
@@ -42,6 +47,45 @@ __device__ __forceinline__ float ln_apply(float x, float mean, float rstd, float
 // ulp of e^x, plus |x| * 2^-24 relative from rounding x * log2(e), which matters only where e^x is tiny) moves
 // 1 + e^x by no more than the two-ulp bound of the library expf does, at a quarter of the instructions.
 __device__ __forceinline__ float exp_nonpos(float x) { return __expf(x); }
+
+// ---- a token's row spread over a warp: coordinate e = j * 32 + lane in register j ("scalar layout") ----------------
+template <int V, typename XT>
+__device__ __forceinline__ void load_row(float (&v)[V], const XT *row, int d_in, int lane) {
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+        const int e = j * 32 + lane;
+        v[j] = e < d_in ? Elem<XT>::load1(row + e) : 0.f;
+    }
+}
+
+// mean and 1/sqrt(var + eps) of a row spread over a warp as in load_row (two passes over the registers)
+template <int V>
+__device__ __forceinline__ void row_stats(const float (&v)[V], int d_in, int lane, float eps, float &mean, float &rstd) {
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; j++) s += v[j];  // padding columns hold zeros
+    mean = warp_sum(s) / (float)d_in;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+        const float c = (j * 32 + lane < d_in) ? v[j] - mean : 0.f;
+        q = fmaf(c, c, q);
+    }
+    rstd = 1.f / sqrtf(warp_sum(q) / (float)d_in + eps);
+}
+
+template <int V>
+__device__ __forceinline__ void row_normalise(float (&v)[V], int d_in, int lane, float mean, float rstd,
+                                              const float *__restrict__ g, const float *__restrict__ b) {
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+        const int e = j * 32 + lane;
+        if (e < d_in) v[j] = ln_apply(v[j], mean, rstd, __ldg(g + e), b != nullptr ? __ldg(b + e) : 0.f);
+    }
+}
+
+// the kernel of hash_diag_t.cu; returns false when the request is outside what it covers
+bool try_launch_hash_transposing(const HashArgs &a, int x_dtype, cudaStream_t st, int *rc);
 
 // ---- codes and weights of one table from its k coordinates ------------------------------------
 // `get(j)` returns coordinate j of the table.  Writes m = 1 or k+1 (idx, w) pairs.

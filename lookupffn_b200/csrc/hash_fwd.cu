@@ -50,41 +50,6 @@ __device__ __forceinline__ void fwht_regs(float (&v)[V], int lane) {
 }
 
 template <int V, typename XT>
-__device__ __forceinline__ void load_row(float (&v)[V], const XT *row, int d_in, int lane) {
-#pragma unroll
-    for (int j = 0; j < V; j++) {
-        const int e = j * 32 + lane;
-        v[j] = e < d_in ? Elem<XT>::load1(row + e) : 0.f;
-    }
-}
-
-// mean and 1/sqrt(var + eps) of a row spread over a warp as in load_row (two passes over the registers)
-template <int V>
-__device__ __forceinline__ void row_stats(const float (&v)[V], int d_in, int lane, float eps, float &mean, float &rstd) {
-    float s = 0.f;
-#pragma unroll
-    for (int j = 0; j < V; j++) s += v[j];  // padding columns hold zeros
-    mean = warp_sum(s) / (float)d_in;
-    float q = 0.f;
-#pragma unroll
-    for (int j = 0; j < V; j++) {
-        const float c = (j * 32 + lane < d_in) ? v[j] - mean : 0.f;
-        q = fmaf(c, c, q);
-    }
-    rstd = 1.f / sqrtf(warp_sum(q) / (float)d_in + eps);
-}
-
-template <int V>
-__device__ __forceinline__ void row_normalise(float (&v)[V], int d_in, int lane, float mean, float rstd,
-                                              const float *__restrict__ g, const float *__restrict__ b) {
-#pragma unroll
-    for (int j = 0; j < V; j++) {
-        const int e = j * 32 + lane;
-        if (e < d_in) v[j] = ln_apply(v[j], mean, rstd, __ldg(g + e), b != nullptr ? __ldg(b + e) : 0.f);
-    }
-}
-
-template <int V, typename XT>
 __global__ void __launch_bounds__(256) fwht_kernel(const XT *__restrict__ x, XT *__restrict__ out, long long N,
                                                    float scale) {
     constexpr int D = V * 32;
@@ -565,6 +530,8 @@ static int launch_hash_vec8_n(const HashArgs &a, cudaStream_t st) {
 
 template <typename XT>
 static int launch_hash_diag_t(const HashArgs &a, cudaStream_t st) {
+    int rc_t = LFFN_OK;
+    if (try_launch_hash_transposing(a, sizeof(XT) == 2 ? LFFN_BF16 : LFFN_F32, st, &rc_t)) return rc_t;
     const bool w_aligned = (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0;
     if (w_aligned && (a.k == 1 || a.k == 2 || a.k == 4 || a.k == 8)) {  // vector layout
         switch (a.D) {
@@ -592,6 +559,10 @@ int launch_hash_fwd(const lffn_hash_desc &h, const void *x, int x_dtype, int64_t
                     int32_t *idx_out, float *w_out, float *z_out, const float *ln_g, const float *ln_b, float ln_eps,
                     cudaStream_t st) {
     HashArgs a;
+    a.act_out = nullptr;
+    a.dz = nullptr;
+    a.dz_cols = 0;
+    a.du_out = nullptr;
     a.ln_g = ln_g;
     a.ln_b = ln_b;
     a.ln_eps = ln_eps;

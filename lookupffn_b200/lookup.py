@@ -132,6 +132,19 @@ class Hashing(nn.Module):
         """True when the projection runs in this package's hash kernel, which can apply the LayerNorm in its load."""
         return not isinstance(self.projection, nn.Linear)
 
+    @torch.no_grad()
+    def project(self, x, layer_norm=None):
+        """The projected coordinates z [N, T*k] alone, through the same kernels as forward (diagnostics: which
+        coordinates sit near zero).  layer_norm as in forward."""
+        p = self.projection
+        if isinstance(p, nn.Linear):
+            return p(x).float()
+        wk, tw = p.kernel_weight()
+        desc = ops.make_hash_desc(self.hidden_size, wk, p.bias.detach().contiguous(), self.num_table,
+                                  self.code_length, transpose_w=tw, had_scale=p.had_scale, mix_a=p.mix[0],
+                                  mix_b=p.mix[1], bit_order=self.bit_order, weight_mode=self.weight_mode, tau=self.tau)
+        return ops.hash_fwd(x, desc, want_z=True, want_codes=False, layer_norm=layer_norm)[2]
+
     def forward(self, x, t_begin=0, t_count=None, layer_norm=None):
         """x [N, hidden] -> (row indices int32 [N, T*m] with table offsets added, weights fp32 [N, T*m]).
         layer_norm = (weight, bias, eps): x is the un-normalised input and the kernel applies the LayerNorm

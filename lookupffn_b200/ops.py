@@ -186,11 +186,35 @@ class CodeScore(torch.autograd.Function):
         return code_weights_bwd(z, dw, ctx.weight_mode, ctx.tau), None, None, None
 
 
+def proj_bwd(x, weight, kernel_weight, out_dim, dz, had_scale, mix_a, mix_b, need_dw=True, need_dbias=True):
+    """Backward of z = BH4(x) for 64 x 64 blocks through lffn_proj_bwd: returns (du [N, D], dweight in the parameter's
+    layout or None, dbias or None).  weight [R, S, NB, 64(o), 64(i)] is the parameter, kernel_weight its [.., i, o]
+    copy that the forward fast path streams."""
+    R, S, NB, BS, _ = weight.shape
+    D = NB * BS
+    N = x.shape[0]
+    dev = x.device
+    desc = make_hash_desc(x.shape[1], kernel_weight, None, out_dim, 1, transpose_w=True, had_scale=had_scale,
+                          mix_a=mix_a, mix_b=mix_b, weight_mode=WEIGHT_ONES)
+    w_oi = _contig(weight.detach().float())
+    dz = _contig(dz.float())
+    du = torch.empty((N, D), dtype=torch.float32, device=dev)
+    dw = torch.empty(weight.shape, dtype=torch.float32, device=dev) if need_dw else None
+    dbias = torch.empty(out_dim, dtype=torch.float32, device=dev) if need_dbias else None
+    lib = L.lib()
+    nbytes = lib.lffn_proj_bwd_ws_bytes(C.byref(desc), N)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        L.check(lib.lffn_proj_bwd(C.byref(desc), L.ptr(w_oi), L.ptr(x), L.dtype_code(x.dtype), N, L.ptr(dz), L.ptr(du),
+                                  L.ptr(dw), L.ptr(dbias), L.ptr(ws), nbytes, L.stream_ptr(dev)))
+    return du, dw, dbias
+
+
 class Projection(torch.autograd.Function):
-    """z = BH4(x): forward by the fused hash kernel (projection only); backward recomputes the S stage inputs
-    per rotation and walks them in reverse with the Hadamard kernel (the transform is symmetric) and batched
-    64 x 64 library GEMMs (torch.einsum) for the block-diagonal factors -- the reference's own backward is
-    autograd over the same einsum/hadamard chain (bh4/kernel.py:23-36)."""
+    """z = BH4(x): forward by the fused hash kernel (projection only).  Backward for the reference's shape (64 x 64
+    blocks, D a multiple of 256) is lffn_proj_bwd: the stage inputs are recomputed and the chain walked in reverse by
+    this library's own kernels.  Other block sizes walk the same chain with the Hadamard kernel and torch.einsum for
+    the block-diagonal factors, as the reference's autograd does (bh4/kernel.py:23-36)."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, had_scale, mix_a, mix_b, kernel_weight, kernel_transposed):
@@ -200,16 +224,27 @@ class Projection(torch.autograd.Function):
         desc = make_hash_desc(x.shape[1], kernel_weight, _contig(bias.detach().float()), out_dim, 1,
                               transpose_w=kernel_transposed, had_scale=had_scale, mix_a=mix_a, mix_b=mix_b,
                               weight_mode=WEIGHT_ONES)
+        if x.dtype == torch.float16:
+            x = x.float()
+        x = _contig(x)
         _, _, z = hash_fwd(x, desc, want_z=True, want_codes=False)
-        ctx.save_for_backward(x, weight)
-        ctx.meta = (D, BS, S, R, out_dim, had_scale, mix_a, mix_b)
+        fast = BS == 64 and D % 256 == 0 and D <= 1024 and kernel_transposed
+        ctx.save_for_backward(x, weight, kernel_weight if fast else None)
+        ctx.meta = (D, BS, S, R, out_dim, had_scale, mix_a, mix_b, fast)
         return z
 
     @staticmethod
     def backward(ctx, dz):
-        x, weight = ctx.saved_tensors
-        D, BS, S, R, out_dim, had_scale, mix_a, mix_b = ctx.meta
+        x, weight, kernel_weight = ctx.saved_tensors
+        D, BS, S, R, out_dim, had_scale, mix_a, mix_b, fast = ctx.meta
         N, d_in = x.shape
+        if fast:
+            du, dweight, dbias = proj_bwd(x, weight, kernel_weight, out_dim, dz, had_scale, mix_a, mix_b,
+                                          need_dw=ctx.needs_input_grad[1], need_dbias=ctx.needs_input_grad[2])
+            dx = du[:, :d_in].to(x.dtype) if ctx.needs_input_grad[0] else None
+            if dweight is not None:
+                dweight = dweight.to(weight.dtype)
+            return dx, dweight, dbias, None, None, None, None, None
         NB = D // BS
         dz = _contig(dz.float())
         dbias = dz.sum(0) if ctx.needs_input_grad[2] else None

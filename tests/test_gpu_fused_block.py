@@ -77,6 +77,12 @@ def test_hash_with_layernorm_prologue_matches_oracle(dev, case):
     u_t = torch.nn.functional.layer_norm(xt, (d_in,), ln[0], ln[1], eps)
     _, _, z_t = ops.hash_fwd(u_t, desc, want_z=True)
     assert rel_err(z, z_t.cpu().numpy()) < 5e-6
+    # codes and weights alone (no z: for the diagonal shapes this is the transposing-layout kernel, whose
+    # LayerNorm sums the row in another order): same codes wherever no coordinate is tiny, weights to 1e-5
+    idx_c, w_c, _ = ops.hash_fwd(xt, desc, layer_norm=ln)
+    clean = ~(np.abs(z_ref) < PAR.V_EPS).reshape(N, T, k).any(axis=-1)
+    np.testing.assert_array_equal(idx_c.cpu().numpy()[clean], idx.cpu().numpy()[clean])
+    assert rel_err(w_c.cpu().numpy()[clean], w.cpu().numpy()[clean]) < 1e-5
     # without codes (projection only) the same z comes out
     _, _, z_only = ops.hash_fwd(xt, desc, want_z=True, want_codes=False, layer_norm=ln)
     np.testing.assert_array_equal(z_only.cpu().numpy(), z)
@@ -194,3 +200,79 @@ def test_layer_fwd_ln_residual_entry_point(dev):
     assert torch.equal(out.view(torch.int16), want.view(torch.int16))
     assert torch.equal(iw, idx)
     assert L.device_status(dev) == 0
+
+
+T_CASES = [
+    # N, d_in, D, T, k, weight_mode, bit_order, bias, (t_begin, t_count)
+    (65, 768, 1024, 512, 8, O.WEIGHT_SCORE, O.MSB_FIRST, False, None),
+    (33, 1000, 1024, 300, 8, O.WEIGHT_SCORE, O.LSB_FIRST, True, (64, 170)),
+    (20, 1024, 1024, 100, 16, O.WEIGHT_SCORE, O.MSB_FIRST, True, (3, 90)),
+    (17, 500, 512, 250, 4, O.WEIGHT_ONES, O.MSB_FIRST, True, (8, 200)),
+    (29, 512, 512, 128, 8, O.WEIGHT_SOFT_FLIP, O.MSB_FIRST, False, None),
+    (31, 200, 256, 500, 2, O.WEIGHT_SCORE, O.LSB_FIRST, True, None),
+    (9, 256, 256, 700, 1, O.WEIGHT_SCORE, O.MSB_FIRST, False, (1, 650)),
+    (40, 300, 512, 40, 16, O.WEIGHT_SOFT_FLIP, O.LSB_FIRST, True, (5, 30)),
+    (50, 512, 512, 64, 8, O.WEIGHT_SCORE, O.MSB_FIRST, True, (12, 40)),     # range not a multiple of four tables
+]
+
+
+@pytest.mark.parametrize("case", T_CASES, ids=[f"t{i}" for i in range(len(T_CASES))])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_transposing_hash_layout_matches_the_other_layouts_and_oracle(dev, case, bf16):
+    """Codes-and-weights requests without z run the kernel that changes layout through shared memory in the middle
+    of each transform; asking for z as well selects the shuffle kernels.  Same butterfly order, same operation
+    order in the weights: indices and weights must be bit-identical, and the indices equal the oracle's."""
+    from lookupffn_b200 import ops
+
+    N, d_in, D, T, k, wm, bo, with_bias, rng_t = case
+    rng = np.random.RandomState(N + T + k)
+    R = max(1, -(-T * k // D))
+    pw = (2.0 * rng.randint(0, 2, size=(R, 2, D, 1, 1)) - 1.0).astype(np.float32)
+    pbias = (0.05 * rng.randn(T * k)).astype(np.float32) if with_bias else None
+    x = rng.randn(N, d_in).astype(np.float32)
+    hs = float(1.0 / np.sqrt(D))
+    if bf16:
+        xb = O.f32_to_bf16_bits(x)
+        xt = torch.from_numpy(xb.view(np.int16)).to(dev).view(torch.bfloat16)
+        x = O.bf16_bits_to_f32(xb)
+    else:
+        xt = torch.from_numpy(x).to(dev)
+    tb, tc = (0, T) if rng_t is None else rng_t
+    desc = ops.make_hash_desc(d_in, torch.from_numpy(pw).to(dev), None if pbias is None else torch.from_numpy(pbias).to(dev),
+                              T, k, had_scale=hs, mix_a=1.0, mix_b=0.0, bit_order=bo, weight_mode=wm, tau=0.5)
+    idx, w, _ = ops.hash_fwd(xt, desc, t_begin=tb, t_count=tc)                       # transposing layout
+    idx2, w2, z = ops.hash_fwd(xt, desc, t_begin=tb, t_count=tc, want_z=True)        # shuffle layouts
+    assert torch.equal(idx, idx2)
+    assert torch.equal(w.view(torch.int32), w2.view(torch.int32))
+    z_ref = O.project(x, pw, T * k, had_scale=hs, mix_a=1.0, mix_b=0.0, bias=pbias)[:, tb * k:(tb + tc) * k]
+    np.testing.assert_array_equal(z.cpu().numpy(), z_ref)
+    idx_ref, w_ref = O.code_weights(z_ref, tc, k, bit_order=bo, weight_mode=wm, tau=0.5)
+    np.testing.assert_array_equal(idx.cpu().numpy(), idx_ref)
+    assert rel_err(w.cpu().numpy(), w_ref) < 1e-5
+
+
+def test_tracing_stage_times_and_nvtx_ranges(dev):
+    """Tracing is off by default; with LFFN_TRACE_STAGE_TIMES a whole-layer call leaves the durations of its two
+    kernels, and with LFFN_TRACE_NVTX the calls still work (the ranges go to whatever tool is attached, or nowhere)."""
+    from lookupffn_b200 import _lib as L
+    from lookupffn_b200 import ops
+
+    lib = L.lib()
+    h, g = C.c_float(-1), C.c_float(-1)
+    N, d_in, D, T, k, d_out = 4096, 512, 512, 128, 8, 512
+    gen = torch.Generator(device=dev).manual_seed(2)
+    x = torch.randn(N, d_in, generator=gen, device=dev)
+    tables = 0.02 * torch.randn(T << k, d_out, generator=gen, device=dev)
+    signs = (2 * torch.randint(0, 2, (2, 2, D, 1, 1), generator=gen, device=dev) - 1).float()
+    desc = ops.make_hash_desc(d_in, signs, None, T, k, had_scale=1 / 16, mix_a=1.0, mix_b=0.0)
+    base = ops.layer_fwd(x, desc, tables)
+    try:
+        assert lib.lffn_trace_configure(L.TRACE_NVTX | L.TRACE_STAGE_TIMES) == 0
+        y = ops.layer_fwd(x, desc, tables)
+        with torch.cuda.device(dev):
+            L.check(lib.lffn_trace_last_layer_times(C.byref(h), C.byref(g)))
+        assert 0 < h.value < 50 and 0 < g.value < 50
+        assert torch.equal(y, base)
+        assert lib.lffn_trace_configure(8) == -1  # unknown flag
+    finally:
+        assert lib.lffn_trace_configure(0) == 0

@@ -696,18 +696,20 @@ def test_module_bf16_tables_and_leading_dims(dev):
     x = torch.randn(2, 3, 5, 768, device=dev)
     with torch.no_grad():
         y = mod(x)
-        u = mod.LayerNorm(x.reshape(-1, 768))
-        idx, w = mod.hash(u)
+        # the module's inference path: LayerNorm inside the hash kernel
+        idx, w = mod.hash(x.reshape(-1, 768), layer_norm=(mod.LayerNorm.weight, mod.LayerNorm.bias, 1e-5))
     assert y.shape == (2, 3, 5, 768) and y.dtype == torch.bfloat16
     ref = O.gather(t2n(idx), t2n(w), t2n(mod.tables.detach().reshape(-1, 768)), bias=t2n(mod.bias.detach()),
                    out_bf16=True)
     np.testing.assert_array_equal(t2n(y.reshape(-1, 768)), ref)
-    # codes from the oracle's projection of the same layer-normed input
+    # codes from the oracle's LayerNorm (accumulated in double) and projection: equal wherever no coordinate is tiny
     p = mod.hash.projection
-    z_ref = O.project(t2n(u), t2n(p.weight.detach()), 64 * 8, had_scale=float(np.float32(p.had_scale)), mix_a=1.0,
+    u = O.layernorm(t2n(x.reshape(-1, 768)), t2n(mod.LayerNorm.weight.detach()), t2n(mod.LayerNorm.bias.detach()), 1e-5)
+    z_ref = O.project(u, t2n(p.weight.detach()), 64 * 8, had_scale=float(np.float32(p.had_scale)), mix_a=1.0,
                       mix_b=0.0, bias=t2n(p.bias.detach()))
     idx_ref, _ = O.code_weights(z_ref, 64, 8)
-    np.testing.assert_array_equal(t2n(idx), idx_ref)
+    clean = ~(np.abs(z_ref) < PAR.V_EPS).reshape(-1, 64, 8).any(axis=-1)
+    np.testing.assert_array_equal(t2n(idx)[clean], idx_ref[clean])
 
 
 def test_sliced_index_lists_are_bit_exact(dev):

@@ -1,0 +1,114 @@
+"""Backward pass of the block-diagonal projection (lffn_proj_bwd) against fp64 autograd over the reference's own
+formulation: per rotation and stage torch.einsum("bni,noi->bno") then a product with the Sylvester matrix
+(bh4/kernel.py:23-36), then 0.7 * P + 0.3 * tile(x_pad), slice, + bias (lookup.py:29-39).  Bar: gradients within
+1e-3 relative (the fp32 bound of the task); measured agreement is about 1e-6.  The kernels use no atomics, so two
+runs must give the same bits."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from lookupffn_b200 import _lib
+
+    _lib.lib()
+    return torch.device("cuda:0")
+
+
+def rel(a, b):
+    return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+
+
+def reference_fp64(x, weight, bias, out_dim, had_scale, mix_a, mix_b):
+    N, d_in = x.shape
+    R, S, NB, BS, _ = weight.shape
+    D = NB * BS
+    H = torch.ones(1, 1, dtype=torch.float64, device=x.device)
+    while H.shape[0] < D:
+        H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
+    up = torch.nn.functional.pad(x, (0, D - d_in))
+    outs = []
+    for r in range(R):
+        y = up
+        for s in range(S):
+            y = torch.einsum("bni,noi->bno", y.reshape(N, NB, BS), weight[r, s]).reshape(N, D)
+            y = (y @ H) * had_scale
+        outs.append(y)
+    z = mix_a * torch.cat(outs, -1) + mix_b * up.repeat(1, R)
+    return z[:, :out_dim] + bias
+
+
+CASES = [
+    # N, d_in, D, S, out_dim, had_scale, (mix_a, mix_b)
+    (100, 512, 512, 4, 1024, 1.0, (0.7, 0.3)),          # the reference layer: t128, 8 bits, hidden 512
+    (77, 200, 256, 4, 600, 1.0, (0.7, 0.3)),            # padded input, ragged tile, out_dim not a multiple of D
+    (300, 768, 1024, 4, 2048, 1.0 / 32, (1.0, 0.0)),    # D = 1024: the narrow tile pipeline, normalised transform
+    (64, 512, 512, 2, 512, 1.0, (0.7, 0.3)),            # two stages, one rotation
+    (1, 256, 256, 4, 256, 1.0, (0.7, 0.3)),             # a single token
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[f"p{i}" for i in range(len(CASES))])
+def test_proj_bwd_matches_fp64_autograd(dev, case):
+    from lookupffn_b200 import ops
+
+    N, d_in, D, S, out_dim, hs, (mix_a, mix_b) = case
+    R = max(1, -(-out_dim // D))
+    g = torch.Generator(device=dev).manual_seed(N + D)
+    x = torch.randn(N, d_in, generator=g, device=dev)
+    # of order one through the stages whatever had_scale is
+    weight = torch.randn(R, S, D // 64, 64, 64, generator=g, device=dev) / (np.sqrt(64.0) * (np.sqrt(D) * hs if hs != 1.0 else np.sqrt(D)))
+    bias = 0.05 * torch.randn(out_dim, generator=g, device=dev)
+    dz = torch.randn(N, out_dim, generator=g, device=dev)
+    wt = weight.transpose(-1, -2).contiguous()
+    du, dw, db = ops.proj_bwd(x, weight, wt, out_dim, dz, hs, mix_a, mix_b)
+    du2, dw2, db2 = ops.proj_bwd(x, weight, wt, out_dim, dz, hs, mix_a, mix_b)
+    assert torch.equal(du, du2) and torch.equal(dw, dw2) and torch.equal(db, db2)
+
+    x64 = x.double().requires_grad_(True)
+    w64 = weight.double().requires_grad_(True)
+    b64 = bias.double().requires_grad_(True)
+    z = reference_fp64(x64, w64, b64, out_dim, float(np.float32(hs)), float(np.float32(mix_a)), float(np.float32(mix_b)))
+    z.backward(dz.double())
+    assert rel(du[:, :d_in], x64.grad) < 1e-4
+    if d_in < D:  # the padded columns receive a gradient too; nothing reads it
+        assert torch.isfinite(du).all()
+    assert rel(dw, w64.grad) < 1e-4
+    assert rel(db, b64.grad) < 1e-5
+    from lookupffn_b200 import _lib as L
+
+    assert L.device_status(dev) == 0
+
+
+def test_projection_autograd_function_uses_the_kernels(dev):
+    """ops.Projection (what Hashing.forward runs in training) end to end: forward z and all three gradients against
+    fp64 autograd, with partial requires_grad combinations."""
+    from lookupffn_b200 import ops
+    from lookupffn_b200.lookup import BH4
+
+    torch.manual_seed(0)
+    mod = BH4(500, 1500, 64).to(dev)
+    with torch.no_grad():
+        mod.bias.normal_(0, 0.05)
+    x = torch.randn(90, 500, device=dev, requires_grad=True)
+    wk, tw = mod.kernel_weight()
+    z = ops.Projection.apply(x, mod.weight, mod.bias, mod.had_scale, mod.mix[0], mod.mix[1], wk, tw)
+    dz = torch.randn_like(z)
+    z.backward(dz)
+    x64 = x.detach().double().requires_grad_(True)
+    w64 = mod.weight.detach().double().requires_grad_(True)
+    b64 = mod.bias.detach().double().requires_grad_(True)
+    z64 = reference_fp64(x64, w64, b64, 1500, 1.0, float(np.float32(0.7)), float(np.float32(1 - 0.7)))
+    z64.backward(dz.double())
+    assert rel(z.detach(), z64.detach()) < 1e-5
+    assert rel(x.grad, x64.grad) < 1e-4 and rel(mod.weight.grad, w64.grad) < 1e-4 and rel(mod.bias.grad, b64.grad) < 1e-5
+    # only the input needs a gradient (frozen projection)
+    mod.weight.requires_grad_(False)
+    mod.bias.requires_grad_(False)
+    x3 = x.detach().clone().requires_grad_(True)
+    ops.Projection.apply(x3, mod.weight, mod.bias, mod.had_scale, mod.mix[0], mod.mix[1], wk, tw).backward(dz)
+    assert torch.equal(x3.grad, x.grad)
