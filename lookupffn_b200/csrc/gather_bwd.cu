@@ -291,6 +291,7 @@ int launch_gather_bwd_tables(const int32_t *idx, const float *w, const float *dy
 // ---- dtables, layer-structured index list: stable per-table counting sort + segmented reduction ----
 constexpr int SORT_THREADS = 512;
 constexpr int SORT_MAX_ROWS = 16384;
+constexpr int SORT_WARP_RANGE_ROWS = 2048;  // up to here every warp keeps its own counters: 16 x rows x 4 B of shared memory
 
 // scratch layout: seg int2[T*rows] | ent_n int32[T*Ne] | ent_w float[T*Ne],  Ne = N*m
 struct SortedScratch {
@@ -316,34 +317,66 @@ static SortedScratch carve(void *scratch, int64_t N, int T, int m, int rows) {
 }
 
 // One CTA sorts the N*m entries of one table by row, keeping ascending (n, c) order inside a row.
+//
+// WARP_RANGES (rows <= SORT_WARP_RANGE_ROWS): every warp owns one contiguous range of the table's entries.  The
+// counting pass fills counts[warp][row]; an exclusive scan over (row, warp) turns them into the first output slot of
+// each warp's entries of each row; the placement pass then runs without any CTA-wide barrier, every warp walking its
+// range in order with its own cursors.  Stability: a warp's entries all come after those of the warps before it,
+// and inside a warp the 32 entries of a step are ranked by lane.
+// Otherwise (many rows: the per-warp counters would not fit in shared memory) one shared cursor per row and the
+// warps take turns, in entry order, 512 entries per step.
+template <bool WARP_RANGES>
 __global__ void __launch_bounds__(SORT_THREADS) sort_table_entries_kernel(const int32_t *__restrict__ idx,
                                                                           const float *__restrict__ w, long long N,
                                                                           int T, int m, int rows, int2 *seg,
                                                                           int32_t *ent_n, float *ent_w,
                                                                           uint32_t *status) {
-    extern __shared__ int cursor[];  // [rows] counts, then running write offsets
+    extern __shared__ int cursor[];  // WARP_RANGES: [NW][rows] counts, then write offsets; else [rows]
     __shared__ int warp_sums[SORT_THREADS / 32];
+    constexpr int NW = SORT_THREADS / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long Ne = N * m;
     const int I = T * m;
     bool bad = false;
+    // entries [e_lo, e_hi) of every table belong to this warp (WARP_RANGES); multiples of 32 except at the end
+    const long long per_warp = ((Ne + NW - 1) / NW + 31) / 32 * 32;
+    const long long e_lo = min(Ne, per_warp * warp), e_hi = min(Ne, e_lo + per_warp);
+    const int ncnt = WARP_RANGES ? NW * rows : rows;
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
-        for (int i = tid; i < rows; i += SORT_THREADS) cursor[i] = 0;
+        for (int i = tid; i < ncnt; i += SORT_THREADS) cursor[i] = 0;
         __syncthreads();
         const int32_t *col = idx + (long long)t * m;
-        for (long long e = tid; e < Ne; e += SORT_THREADS) {
-            const long long n = e / m;
-            const int c = (int)(e - n * m);
-            const int key = __ldg(col + n * I + c) - t * rows;
-            if ((unsigned)key < (unsigned)rows) atomicAdd(&cursor[key], 1);
-            else bad = true;
+        if constexpr (WARP_RANGES) {
+            int *mine = cursor + warp * rows;
+            for (long long e = e_lo + lane; e < e_hi; e += 32) {
+                const long long n = e / m;
+                const int c = (int)(e - n * m);
+                const int key = __ldg(col + n * I + c) - t * rows;
+                if ((unsigned)key < (unsigned)rows) atomicAdd(&mine[key], 1);
+                else bad = true;
+            }
+        } else {
+            for (long long e = tid; e < Ne; e += SORT_THREADS) {
+                const long long n = e / m;
+                const int c = (int)(e - n * m);
+                const int key = __ldg(col + n * I + c) - t * rows;
+                if ((unsigned)key < (unsigned)rows) atomicAdd(&cursor[key], 1);
+                else bad = true;
+            }
         }
         __syncthreads();
-        // exclusive scan of cursor[0..rows): each thread owns a contiguous chunk
+        // exclusive scan over the rows: each thread owns a contiguous chunk of rows (all warps' counts of a row
+        // are consecutive in the order of the scan)
         const int chunk = (rows + SORT_THREADS - 1) / SORT_THREADS;
         const int b = min(tid * chunk, rows), e2 = min(b + chunk, rows);
         int local = 0;
-        for (int i = b; i < e2; i++) local += cursor[i];
+        for (int i = b; i < e2; i++) {
+            if constexpr (WARP_RANGES) {
+                for (int ws = 0; ws < NW; ws++) local += cursor[ws * rows + i];
+            } else {
+                local += cursor[i];
+            }
+        }
         int incl = local;
 #pragma unroll
         for (int s = 1; s < 32; s <<= 1) {
@@ -353,55 +386,99 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_table_entries_kernel(const 
         if (lane == 31) warp_sums[warp] = incl;
         __syncthreads();
         if (warp == 0) {
-            int v = lane < SORT_THREADS / 32 ? warp_sums[lane] : 0;
+            int v = lane < NW ? warp_sums[lane] : 0;
 #pragma unroll
             for (int s = 1; s < 32; s <<= 1) {
                 const int u = __shfl_up_sync(FULL, v, s);
                 if (lane >= s) v += u;
             }
-            if (lane < SORT_THREADS / 32) warp_sums[lane] = v;  // inclusive sums of warps
+            if (lane < NW) warp_sums[lane] = v;  // inclusive sums of warps
         }
         __syncthreads();
         int run = incl - local + (warp > 0 ? warp_sums[warp - 1] : 0);
         const long long tbase = (long long)t * Ne;
         for (int i = b; i < e2; i++) {
-            const int cnt = cursor[i];
-            seg[(long long)t * rows + i] = make_int2((int)(tbase + run), cnt);
-            cursor[i] = run;
-            run += cnt;
+            if constexpr (WARP_RANGES) {
+                const int first = run;
+                for (int ws = 0; ws < NW; ws++) {
+                    const int cnt = cursor[ws * rows + i];
+                    cursor[ws * rows + i] = run;
+                    run += cnt;
+                }
+                seg[(long long)t * rows + i] = make_int2((int)(tbase + first), run - first);
+            } else {
+                const int cnt = cursor[i];
+                seg[(long long)t * rows + i] = make_int2((int)(tbase + run), cnt);
+                cursor[i] = run;
+                run += cnt;
+            }
         }
         __syncthreads();
-        // stable placement, SORT_THREADS entries per step in entry order
-        for (long long base = 0; base < Ne; base += SORT_THREADS) {
-            const long long e = base + tid;
-            long long n = 0;
-            int key = -1 - lane;  // unique per lane: matches nobody
-            float ww = 0.f;
-            if (e < Ne) {
-                n = e / m;
-                const int c = (int)(e - n * m);
-                const int kk = __ldg(col + n * I + c) - t * rows;
-                if ((unsigned)kk < (unsigned)rows) {
-                    key = kk;
-                    ww = __ldg(w + n * I + (long long)t * m + c);
+        if constexpr (WARP_RANGES) {
+            int *mine = cursor + warp * rows;
+            for (long long base = e_lo; base < e_hi; base += 32) {
+                const long long e = base + lane;
+                long long n = 0;
+                int key = -1 - lane;  // unique per lane: matches nobody
+                float ww = 0.f;
+                if (e < e_hi) {
+                    n = e / m;
+                    const int c = (int)(e - n * m);
+                    const int kk = __ldg(col + n * I + c) - t * rows;
+                    if ((unsigned)kk < (unsigned)rows) {
+                        key = kk;
+                        ww = __ldg(w + n * I + (long long)t * m + c);
+                    }
+                }
+                const unsigned peers = __match_any_sync(FULL, key);
+                const int rank = __popc(peers & ((1u << lane) - 1u));
+                const int leader = __ffs(peers) - 1;
+                int basepos = 0;
+                if (key >= 0 && rank == 0) {
+                    basepos = mine[key];
+                    mine[key] = basepos + __popc(peers);
+                }
+                __syncwarp();
+                basepos = __shfl_sync(FULL, basepos, leader);
+                if (key >= 0) {
+                    const long long pos = tbase + basepos + rank;
+                    ent_n[pos] = (int32_t)n;
+                    ent_w[pos] = ww;
                 }
             }
-            const unsigned peers = __match_any_sync(FULL, key);
-            const int rank = __popc(peers & ((1u << lane) - 1u));
-            const int leader = __ffs(peers) - 1;
-            int basepos = 0;
-            for (int ws = 0; ws < SORT_THREADS / 32; ws++) {  // warps take their turn in entry order
-                if (warp == ws && key >= 0 && rank == 0) {
-                    basepos = cursor[key];
-                    cursor[key] = basepos + __popc(peers);
+        } else {
+            // stable placement, SORT_THREADS entries per step in entry order
+            for (long long base = 0; base < Ne; base += SORT_THREADS) {
+                const long long e = base + tid;
+                long long n = 0;
+                int key = -1 - lane;  // unique per lane: matches nobody
+                float ww = 0.f;
+                if (e < Ne) {
+                    n = e / m;
+                    const int c = (int)(e - n * m);
+                    const int kk = __ldg(col + n * I + c) - t * rows;
+                    if ((unsigned)kk < (unsigned)rows) {
+                        key = kk;
+                        ww = __ldg(w + n * I + (long long)t * m + c);
+                    }
                 }
-                __syncthreads();
-            }
-            basepos = __shfl_sync(FULL, basepos, leader);
-            if (key >= 0) {
-                const long long pos = tbase + basepos + rank;
-                ent_n[pos] = (int32_t)n;
-                ent_w[pos] = ww;
+                const unsigned peers = __match_any_sync(FULL, key);
+                const int rank = __popc(peers & ((1u << lane) - 1u));
+                const int leader = __ffs(peers) - 1;
+                int basepos = 0;
+                for (int ws = 0; ws < NW; ws++) {  // warps take their turn in entry order
+                    if (warp == ws && key >= 0 && rank == 0) {
+                        basepos = cursor[key];
+                        cursor[key] = basepos + __popc(peers);
+                    }
+                    __syncthreads();
+                }
+                basepos = __shfl_sync(FULL, basepos, leader);
+                if (key >= 0) {
+                    const long long pos = tbase + basepos + rank;
+                    ent_n[pos] = (int32_t)n;
+                    ent_w[pos] = ww;
+                }
             }
         }
         __syncthreads();
@@ -427,14 +504,14 @@ int launch_gather_bwd_tables_sorted(const int32_t *idx, const float *w, const fl
         return LFFN_ERR_SCRATCH;
     }
     SortedScratch s = carve(scratch, N, T, m, rows);
-    const size_t smem = (size_t)rows * sizeof(int);
-    if (smem > 48 * 1024)
-        LFFN_CHECK_CUDA(cudaFuncSetAttribute(sort_table_entries_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem));
+    const bool warp_ranges = rows <= SORT_WARP_RANGE_ROWS;
+    const size_t smem = (size_t)rows * sizeof(int) * (warp_ranges ? SORT_THREADS / 32 : 1);
+    auto kern = warp_ranges ? sort_table_entries_kernel<true> : sort_table_entries_kernel<false>;
+    if (smem > 48 * 1024) LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int grid = T < 4 * num_sms() ? T : 4 * num_sms();
     uint32_t *status = status_word();
     LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
-    sort_table_entries_kernel<<<grid, SORT_THREADS, smem, st>>>(idx, w, N, T, m, rows, s.seg, s.ent_n, s.ent_w, status);
+    kern<<<grid, SORT_THREADS, smem, st>>>(idx, w, N, T, m, rows, s.seg, s.ent_n, s.ent_w, status);
     LFFN_CHECK_CUDA(cudaGetLastError());
     return launch_gather_segmented(s.ent_n, s.ent_w, dy, dtables, (int64_t)T * rows, s.seg, N, d, st);
 }

@@ -365,7 +365,8 @@ def test_gather_bwd_tables_any_index_list(dev, N, I, S, d):
 
 
 @pytest.mark.parametrize("N,T,m,rows,d", [(1, 1, 1, 2, 4), (50, 6, 1, 256, 64), (300, 5, 9, 256, 768),
-                                           (700, 3, 1, 64, 512), (64, 4, 7, 4096, 128), (2000, 2, 1, 16, 1024)])
+                                           (700, 3, 1, 64, 512), (64, 4, 7, 4096, 128), (2000, 2, 1, 16, 1024),
+                                           (5000, 2, 3, 2048, 64), (33, 3, 2, 2049, 32)])
 def test_gather_bwd_tables_sorted_bit_exact_and_deterministic(dev, N, T, m, rows, d):
     from lookupffn_b200 import ops
 
