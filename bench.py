@@ -45,7 +45,7 @@ WORKLOADS = {
 # dram__bytes_write.sum, lts__t_sector_hit_rate.pct), per launch.  c3: captured on a 16384-token launch and
 # scaled by 4 to the 65536-token launch, DRAM traffic being proportional to the waves of tokens (the tables are
 # re-fetched once per wave of resident warps).  `commit` is the source revision the capture was taken from.
-NCU_PROFILE = {"c3": {"traffic_bytes_per_launch": 4 * 1.5135e9, "l2_hit_rate": 0.77, "commit": "0b851ed",
+NCU_PROFILE = {"c3": {"traffic_bytes_per_launch": 4 * 1.4847e9, "l2_hit_rate": 0.772, "commit": "7daaef8",
                       "capture": "ncu --set full, 16384-token launch of the same kernel, traffic x 4"}}
 
 
@@ -1120,6 +1120,77 @@ def cpu_path(args, budget_s):
             "ms_per_pass": med * 1e3}
 
 
+def reference_cpu_own_shape(local):
+    """The reference's CPU inference path on the one shape its CPU kernels are written for (bh4/cpu/kernel.py:57-62,
+    gather/cpu/kernel.py:73-76: 64 x 512 tokens, hidden 512, 128 tables of 256 rows, 64 x 64 blocks) -- its three C++
+    extensions compiled unmodified (the BH4 one against a stand-in libxsmm header: plain-loop GEMM) -- timed on
+    this box's host cores beside this library's layer forward on the same shape on the GPU."""
+    from lookupffn_b200 import ops
+    from oracle import build as obuild
+
+    mods = {n: obuild.load_ref_module(n) for n in ("sbdht_cpu", "ccs_cpu", "gather_add_cpu")}
+    if any(m is None for m in mods.values()):
+        return None
+    N, D, BS, T, k, d = 64 * 512, 512, 64, 128, 8, 512
+    R = T * k // D
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(N, D, generator=g)
+    w = torch.randn(R, 4, D // BS, BS, BS, generator=g) / float(np.sqrt(BS * D))
+    tables = 0.02 * torch.randn(T << k, d, generator=g)
+    offsets = (torch.arange(T, dtype=torch.int32) << k)[None]
+    cores = os.cpu_count()
+    torch.set_num_threads(cores)
+    # the extension announces itself on the C++ side's stdout; this program's stdout carries one JSON line only
+    sys.stdout.flush()
+    saved = os.dup(1)
+    devnull = os.open(os.devnull, os.O_WRONLY)
+    try:
+        os.dup2(devnull, 1)
+        mods["sbdht_cpu"].setup_xsmm_kernel_float_avx2(BS, BS, BS, D, BS, D)
+    finally:
+        os.dup2(saved, 1)
+        os.close(saved)
+        os.close(devnull)
+
+    def one():
+        outs = []
+        for r in range(R):  # bh4/cpu/kernel.py:45-52
+            xc = x.clone()
+            mods["sbdht_cpu"].sbdht(xc, w[r])
+            outs.append(xc)
+        z = 0.7 * torch.cat(outs, dim=-1) + (1 - 0.7) * x.repeat(1, R)  # lookup.py:36-37 (bias is zero at init)
+        codes = torch.empty(N, T, dtype=torch.int32)
+        scores = torch.empty(N, T, dtype=torch.float32)
+        mods["ccs_cpu"].compute_code_score(z.reshape(N, T, k), codes, scores)
+        return mods["gather_add_cpu"].weighted_vector_gather_add_avx2_par(codes + offsets, tables, scores)
+
+    one()
+    times = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        one()
+        times.append(time.perf_counter() - t0)
+    cpu_s = statistics.median(times)
+    # the same layer on the GPU: CPU convention of the projection (x . W per block, H / D)
+    device = torch.device("cuda", local)
+    xd, wd, td = x.to(device), w.to(device), tables.to(device)
+    desc = ops.make_hash_desc(D, wd, None, T, k, transpose_w=True, had_scale=1.0 / D, mix_a=0.7, mix_b=1 - 0.7)
+    for _ in range(3):
+        ops.layer_fwd(xd, desc, td)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        y = ops.layer_fwd(xd, desc, td)
+    e1.record()
+    torch.cuda.synchronize()
+    gpu_s = e0.elapsed_time(e1) * 1e-3 / 10
+    return {"shape": f"N={N}, hidden {D}, T={T}, k={k}, d_out={d}, bh4 64x64, fp32: the only shape the reference's CPU "
+                     "kernels accept", "reference_cpu_tokens_per_s": N / cpu_s, "reference_cpu_ms": cpu_s * 1e3,
+            "cores": cores, "sample": "whole shape, median of 3 passes; BH4 GEMM = stand-in for libxsmm (plain loops)",
+            "this_library_gpu_tokens_per_s": N / gpu_s, "this_library_gpu_ms": gpu_s * 1e3}
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return None
@@ -1217,6 +1288,8 @@ def main():
     if out is not None:
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_path(args, 15.0)
+            if args.workload == "c3" and not args.tokens:
+                out["cpu_baseline"]["reference_cpu_path_on_its_own_shape"] = reference_cpu_own_shape(local)
         if world == 1 and args.workload == "c3" and not args.tokens and not args.no_encoder:
             # the second half of the headline metric: RoBERTa-small encoder inference (config 2), a short run
             enc_args = argparse.Namespace(**vars(args))

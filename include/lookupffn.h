@@ -191,13 +191,22 @@ int lffn_code_weights_bwd(const float *z, const float *dw, int64_t N, int32_t T,
  *   x          [N, d_in] of x_dtype, the input of the forward call;   dz  fp32 [N, T*k], the upstream gradient
  *   du         fp32 [N, D]: gradient with respect to the zero-padded input (its first d_in columns are dx), or NULL
  *   dw         fp32 [R, S, D/64, 64, 64] in the parameter's order, or NULL;   dbias  fp32 [T*k], or NULL
+ *   saved_acts the stage inputs kept by lffn_proj_fwd_train for the same x, or NULL: they are then recomputed
  *   ws         workspace of lffn_proj_bwd_ws_bytes(desc, N) bytes, 256-byte aligned
- * The stage inputs are recomputed, not kept from the forward pass.  fp32 fused multiply-adds throughout, no
- * atomics: results are the same from run to run.
+ * fp32 fused multiply-adds throughout, no atomics: results are the same from run to run.
+ *
+ * lffn_proj_fwd_train is the forward pass for training: z [N, T*k] (= lffn_hash_fwd with z_out only, desc->proj_bias
+ * added) and, in `acts` (lffn_proj_acts_bytes(desc, N) bytes: R * S * ceil(N/32) tiles of [D][32] fp32), the input of
+ * every stage, which is what autograd keeps for the reference's einsum chain.  Handing them to lffn_proj_bwd saves
+ * the recomputation (about a tenth of a training step of the layer) at the price of that memory.
  */
 size_t lffn_proj_bwd_ws_bytes(const lffn_hash_desc *desc, int64_t N);
+size_t lffn_proj_acts_bytes(const lffn_hash_desc *desc, int64_t N);
+int lffn_proj_fwd_train(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, float *z, float *acts,
+                        size_t acts_bytes, lffn_stream_t stream);
 int lffn_proj_bwd(const lffn_hash_desc *desc, const float *proj_w_oi, const void *x, int32_t x_dtype, int64_t N,
-                  const float *dz, float *du, float *dw, float *dbias, void *ws, size_t ws_bytes, lffn_stream_t stream);
+                  const float *dz, float *du, float *dw, float *dbias, const float *saved_acts, void *ws,
+                  size_t ws_bytes, lffn_stream_t stream);
 
 /*
  * out[n, :] = sum_i w[n, i] * tables[idx[n, i], :] (+ bias): replaces

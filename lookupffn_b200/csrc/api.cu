@@ -381,7 +381,10 @@ int lffn_layer_fwd_ln_residual(const lffn_hash_desc *desc, const float *ln_gamma
     return rc;
 }
 
-constexpr int HOST_LANES = 3;  // streams alternating over token chunks in lffn_layer_fwd_host
+#ifndef LFFN_HOST_LANES
+#define LFFN_HOST_LANES 3
+#endif
+constexpr int HOST_LANES = LFFN_HOST_LANES;  // streams alternating over token chunks in lffn_layer_fwd_host
 static size_t esize(int dtype) { return dtype == LFFN_BF16 ? 2 : 4; }
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 

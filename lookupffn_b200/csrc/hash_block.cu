@@ -392,13 +392,14 @@ constexpr int HF_BAR_FLOATS = 4 * HF_NBUF;     // a full and an empty mbarrier p
 //
 // MODE selects what the tile pipeline is used for:
 //   0  the hashing stage itself (codes, weights, optionally z)
-//   1  the same forward walk for training's backward pass: the input y_s of every stage s is saved to
-//      a.act_out[s][tile] ([D][32] per tile, the shared-memory layout without its padding); no codes
+//   1  the same forward walk for training: the input y_s of every stage s of rotation r is saved to
+//      a.act_out[r - r_lo][s][tile] ([D][32] per tile, the shared-memory layout without its padding); z too when
+//      a.z_out is given, no codes
 //   2  the backward walk of one rotation: g = mix_a * dz, then for s = S-1 .. 0: g <- H g * had_scale, saved to
 //      a.act_out[s][tile] (this is the gradient at the output of stage s's multiply), g <- g W[r, s] (a.w is then
 //      the parameter in its own [o][i] order, which is input-major for this product); the result, the gradient
 //      with respect to the rotation's input, goes to a.du_out[tile]
-// Modes 1 and 2 are launched for one rotation at a time (r_lo == r_hi).
+// Mode 2 is launched for one rotation at a time (r_lo == r_hi).
 template <int THREADS>
 __device__ __forceinline__ void tile_save(const float *Y, float *dst, int D) {
     for (int i = threadIdx.x; i < D * HB_M; i += THREADS) dst[i] = Y[(i >> 5) * HB_MP + (i & 31)];
@@ -584,7 +585,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
             for (int sb = 0; sb < a.S; sb++) {
                 const int s = a.S - 1 - sb;
                 fwht_tile<NW>(Y, D, a.had_scale, warp, lane);  // ends with a CTA barrier
-                tile_save<THREADS>(Y, a.act_out + ((size_t)s * ntiles + tile) * tile_floats, D);
+                tile_save<THREADS>(Y, a.act_out + ((size_t)((r - a.r_lo) * a.S + s) * ntiles + tile) * tile_floats, D);
                 __syncthreads();  // the saved values have been read before the multiply overwrites them
                 if (!multiply_stage(Y)) return;
                 __syncthreads();
@@ -594,7 +595,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
             for (int s = 0; s < a.S; s++) {
                 const float *ysrc = (X0 && s == 0) ? Xs : Y;
                 if constexpr (MODE == 1) {
-                    tile_save<THREADS>(ysrc, a.act_out + ((size_t)s * ntiles + tile) * tile_floats, D);
+                    tile_save<THREADS>(ysrc, a.act_out + ((size_t)((r - a.r_lo) * a.S + s) * ntiles + tile) * tile_floats, D);
                     __syncthreads();
                 }
                 if (!multiply_stage(ysrc)) return;
@@ -603,7 +604,8 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
                 fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
                 HB_MARK(HB_PH_HADAMARD);
             }
-            if constexpr (MODE == 0) tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r, lnstat, Xs);
+            // mode 1 may be asked for z as well (training's forward pass keeps the stage inputs for its backward)
+            if (MODE == 0 || a.z_out != nullptr) tile_end_rotation<XT, THREADS>(Y, carry, a, n0, mt, D, r, lnstat, Xs);
         }
 #ifdef LFFN_HB_PHASE_CLOCKS
         __syncthreads();
@@ -641,10 +643,12 @@ int launch_bounded_wait_selftest(int poll_limit, cudaStream_t st) {
 int launch_hash_block64_mode(const HashArgs &a, int mode, int x_dtype, cudaStream_t st) {
     LFFN_REQUIRE(a.D % 256 == 0 && a.D >= 256 && a.D <= 1024 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0,
                  LFFN_ERR_UNSUPPORTED, "block-diagonal backward: D = %d must be 256, 512 or 1024 and the weights 16-byte aligned", a.D);
-    LFFN_REQUIRE(a.r_lo == a.r_hi && (mode == 1 || mode == 2), LFFN_ERR_INVALID_ARG, "block-diagonal backward: one rotation per launch");
+    LFFN_REQUIRE((mode == 1 || (mode == 2 && a.r_lo == a.r_hi)) && a.k == 1, LFFN_ERR_INVALID_ARG,
+                 "block-diagonal backward: mode 1, or mode 2 with one rotation per launch; k = 1");
     const long long ntiles = (a.N + HB_M - 1) / HB_M;
+    const long long groups = ntiles * (a.r_hi - a.r_lo + 1);  // (tile, rotation) work units
     long long grid = num_sms();
-    if (grid > ntiles) grid = ntiles;
+    if (grid > groups) grid = groups;
     if (grid < 1) grid = 1;
     const bool wide = a.D % 512 == 0;
     const size_t smem_b = ((size_t)a.D * HB_MP + HB_WFLOATS + HB_CARRY * HB_MP + HB_LN_FLOATS + HF_BAR_FLOATS) * sizeof(float);

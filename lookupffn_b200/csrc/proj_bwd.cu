@@ -14,7 +14,7 @@
 //   3. proj_dw_partial_kernel: for every (s, block) the 64 x 64 sum over tokens of gt_s (x) y_s, split over token
 //      ranges into partial sums; proj_dw_reduce_kernel adds the partials in a fixed order (deterministic)
 //   4. proj_du_kernel: g_0 back to row-major, accumulated over the rotations, plus the mix_b term
-// and one proj_dbias_kernel.  All fp32 FMA, no tensor cores, no atomics.
+// and proj_dbias_partial_kernel + the same fixed-order reduce for the bias gradient.  All fp32 FMA, no tensor cores, no atomics.
 #include "common.cuh"
 #include "hash_common.cuh"
 
@@ -129,21 +129,24 @@ __global__ void __launch_bounds__(256) proj_du_kernel(const float *__restrict__ 
     }
 }
 
-// dbias[c] = sum_n dz[n][c]: 32 columns per CTA, eight row groups summed in a fixed order
-__global__ void __launch_bounds__(256) proj_dbias_kernel(const float *__restrict__ dz, float *__restrict__ dbias, long long N,
-                                                        int cols) {
+// partial[split][c] = sum over the split's rows of dz[n][c]: 32 columns x one row range per CTA, eight row groups
+// summed in a fixed order; proj_dw_reduce_kernel then adds the DBIAS_SPLITS partial rows in split order
+constexpr int DBIAS_SPLITS = 64;
+__global__ void __launch_bounds__(256) proj_dbias_partial_kernel(const float *__restrict__ dz, float *__restrict__ partial,
+                                                                long long N, int cols) {
     __shared__ float part[8][32];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + tx;
+    const long long n_lo = N * blockIdx.y / DBIAS_SPLITS, n_hi = N * (blockIdx.y + 1) / DBIAS_SPLITS;
     float v = 0.f;
     if (c < cols)
-        for (long long n = ty; n < N; n += 8) v += __ldg(dz + n * cols + c);
+        for (long long n = n_lo + ty; n < n_hi; n += 8) v += __ldg(dz + n * cols + c);
     part[ty][tx] = v;
     __syncthreads();
     if (ty == 0 && c < cols) {
         float t = 0.f;
         for (int j = 0; j < 8; j++) t += part[j][tx];
-        dbias[c] = t;
+        partial[(size_t)blockIdx.y * cols + c] = t;
     }
 }
 
@@ -156,15 +159,67 @@ static int dw_splits(long long ntiles) {
 }
 
 // workspace: acts_y [S][ntiles][D][32] | acts_g (same) | g0 [ntiles][D][32] | partial [splits][S][NB][64][64]
+//            | dbias partial [DBIAS_SPLITS][T*k]
 size_t proj_bwd_ws_bytes(int D, int S, int64_t N) {
     const long long ntiles = (N + TILE_M - 1) / TILE_M;
     const size_t tile_bytes = (size_t)D * TILE_M * sizeof(float);
     return 2 * up256((size_t)S * ntiles * tile_bytes) + up256((size_t)ntiles * tile_bytes) +
            up256((size_t)dw_splits(ntiles) * S * (D / 64) * 4096 * sizeof(float));
 }
+static size_t dbias_ws_bytes(int out_dim) { return up256((size_t)DBIAS_SPLITS * out_dim * sizeof(float)); }
+
+static void fill_args(HashArgs &a, const lffn_hash_desc &h, const void *x, int64_t N) {
+    a.x = x;
+    a.N = N;
+    a.d_in = h.d_in;
+    a.D = h.D;
+    a.S = h.S;
+    a.R = h.R;
+    a.had_scale = h.had_scale;
+    a.mix_a = h.mix_a;
+    a.mix_b = h.mix_b;
+    a.bias = nullptr;
+    a.T = h.T * h.k;  // every output column its own "table": z [N, T*k]
+    a.k = 1;          // no codes here; k = 1 divides every D, which keeps the (tile, rotation) work units independent
+    a.bit_order = h.bit_order;
+    a.weight_mode = LFFN_WEIGHT_ONES;
+    a.tau = h.tau;
+    a.t_begin = 0;
+    a.t_count = a.T;
+    a.idx_out = nullptr;
+    a.w_out = nullptr;
+    a.z_out = nullptr;
+    a.status = status_word();
+    a.ln_g = nullptr;
+    a.ln_b = nullptr;
+    a.ln_eps = 0.f;
+    a.act_out = nullptr;
+    a.dz = nullptr;
+    a.dz_cols = 0;
+    a.du_out = nullptr;
+}
+
+size_t proj_acts_bytes(int D, int S, int R, int64_t N) {
+    const long long ntiles = (N + TILE_M - 1) / TILE_M;
+    return (size_t)R * S * ntiles * D * TILE_M * sizeof(float);
+}
+
+// training's forward pass: z for all rotations in one launch, every stage's input kept in `acts`
+int launch_proj_fwd_train(const lffn_hash_desc &h, const void *x, int x_dtype, int64_t N, float *z, float *acts,
+                          cudaStream_t st) {
+    HashArgs a;
+    fill_args(a, h, x, N);
+    a.bias = h.proj_bias;
+    a.w = h.proj_w;
+    a.r_lo = 0;
+    a.r_hi = h.R - 1;  // every rotation the backward pass will walk
+    a.z_out = z;
+    a.act_out = acts;
+    return launch_hash_block64_mode(a, 1, x_dtype, st);
+}
 
 int launch_proj_bwd(const lffn_hash_desc &h, const float *w_oi, const void *x, int x_dtype, int64_t N, const float *dz,
-                    float *du, float *dw, float *dbias, void *ws, cudaStream_t st) {
+                    float *du, float *dw, float *dbias, const float *saved_acts, void *ws, cudaStream_t st) {
     const int D = h.D, S = h.S, NB = D / 64;
     const long long ntiles = (N + TILE_M - 1) / TILE_M;
     const size_t tile_bytes = (size_t)D * TILE_M * sizeof(float);
@@ -178,47 +233,33 @@ int launch_proj_bwd(const lffn_hash_desc &h, const float *w_oi, const void *x, i
     float *partial = reinterpret_cast<float *>(p);
     const int splits = dw_splits(ntiles);
     const int out_dim = h.T * h.k;
+    p += up256((size_t)splits * S * NB * 4096 * sizeof(float));
+    float *dbias_partial = reinterpret_cast<float *>(p);
 
     HashArgs a;
-    a.x = x;
-    a.N = N;
-    a.d_in = h.d_in;
-    a.D = D;
-    a.S = S;
-    a.R = h.R;
-    a.had_scale = h.had_scale;
-    a.mix_a = h.mix_a;
-    a.mix_b = h.mix_b;
-    a.bias = nullptr;
-    a.T = h.T;
-    a.k = 1;  // no codes here; k = 1 divides every D, which keeps the (tile, rotation) work units independent
-    a.bit_order = h.bit_order;
-    a.weight_mode = LFFN_WEIGHT_ONES;
-    a.tau = h.tau;
-    a.t_begin = 0;
-    a.t_count = h.T;
-    a.idx_out = nullptr;
-    a.w_out = nullptr;
-    a.z_out = nullptr;
-    a.status = status_word();
-    a.ln_g = nullptr;
-    a.ln_b = nullptr;
-    a.ln_eps = 0.f;
+    fill_args(a, h, x, N);
     a.dz = dz;
     a.dz_cols = out_dim;
     a.du_out = g0;
+    const size_t rot_floats = (size_t)S * ntiles * D * TILE_M;
     for (int r = 0; r < h.R; r++) {
         a.r_lo = a.r_hi = r;
-        a.w = h.proj_w;  // [i][o]: input-major for the forward product
-        a.act_out = acts_y;
-        int rc = launch_hash_block64_mode(a, 1, x_dtype, st);
-        if (rc != LFFN_OK) return rc;
+        int rc = LFFN_OK;
+        const float *ys = acts_y;
+        if (saved_acts != nullptr) {
+            ys = saved_acts + (size_t)r * rot_floats;  // kept by the forward pass
+        } else {
+            a.w = h.proj_w;  // [i][o]: input-major for the forward product
+            a.act_out = acts_y;
+            rc = launch_hash_block64_mode(a, 1, x_dtype, st);
+            if (rc != LFFN_OK) return rc;
+        }
         a.w = w_oi;  // [o][i]: input-major for the backward product
         a.act_out = acts_g;
         rc = launch_hash_block64_mode(a, 2, x_dtype, st);
         if (rc != LFFN_OK) return rc;
         if (dw != nullptr) {
-            proj_dw_partial_kernel<<<dim3(S * NB, splits), DW_THREADS, 0, st>>>(acts_g, acts_y, partial, ntiles, D, splits);
+            proj_dw_partial_kernel<<<dim3(S * NB, splits), DW_THREADS, 0, st>>>(acts_g, ys, partial, ntiles, D, splits);
             LFFN_CHECK_CUDA(cudaGetLastError());
             const long long n = (long long)S * NB * 4096;
             proj_dw_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(partial, dw + (size_t)r * n, n, splits);
@@ -230,7 +271,9 @@ int launch_proj_bwd(const lffn_hash_desc &h, const float *w_oi, const void *x, i
         }
     }
     if (dbias != nullptr) {
-        proj_dbias_kernel<<<(out_dim + 31) / 32, 256, 0, st>>>(dz, dbias, N, out_dim);
+        proj_dbias_partial_kernel<<<dim3((out_dim + 31) / 32, DBIAS_SPLITS), 256, 0, st>>>(dz, dbias_partial, N, out_dim);
+        LFFN_CHECK_CUDA(cudaGetLastError());
+        proj_dw_reduce_kernel<<<(out_dim + 255) / 256, 256, 0, st>>>(dbias_partial, dbias, out_dim, DBIAS_SPLITS);
         LFFN_CHECK_CUDA(cudaGetLastError());
     }
     return LFFN_OK;
@@ -242,27 +285,52 @@ using namespace lffn;
 
 extern "C" size_t lffn_proj_bwd_ws_bytes(const lffn_hash_desc *desc, int64_t N) {
     if (desc == nullptr || N < 1 || desc->BS != 64 || desc->D % 256 != 0 || desc->S < 1) return 0;
-    return proj_bwd_ws_bytes(desc->D, desc->S, N);
+    return proj_bwd_ws_bytes(desc->D, desc->S, N) + dbias_ws_bytes(desc->T * desc->k);
+}
+
+static int check_proj_desc(const lffn_hash_desc *desc, const char *who) {
+    LFFN_REQUIRE(desc != nullptr && desc->proj_w != nullptr, LFFN_ERR_INVALID_ARG, "%s: NULL descriptor or weights", who);
+    LFFN_REQUIRE(desc->BS == 64 && desc->transpose_w == 1 && desc->D % 256 == 0 && desc->D >= 256 && desc->D <= 1024,
+                 LFFN_ERR_UNSUPPORTED,
+                 "%s: covers 64 x 64 blocks with D in {256, 512, 1024} and desc->proj_w in [i][o] order "
+                 "(transpose_w = 1); got BS = %d, D = %d, transpose_w = %d", who, desc->BS, desc->D, desc->transpose_w);
+    LFFN_REQUIRE(desc->d_in >= 1 && desc->d_in <= desc->D && desc->S >= 1 && desc->R >= 1 && desc->T >= 1 && desc->k >= 1 &&
+                     (long long)desc->R * desc->D >= (long long)desc->T * desc->k,
+                 LFFN_ERR_INVALID_ARG, "%s: inconsistent descriptor", who);
+    return LFFN_OK;
+}
+
+extern "C" size_t lffn_proj_acts_bytes(const lffn_hash_desc *desc, int64_t N) {
+    if (desc == nullptr || N < 1 || desc->BS != 64 || desc->D % 256 != 0 || desc->S < 1 || desc->R < 1) return 0;
+    return proj_acts_bytes(desc->D, desc->S, desc->R, N);
+}
+
+extern "C" int lffn_proj_fwd_train(const lffn_hash_desc *desc, const void *x, int32_t x_dtype, int64_t N, float *z,
+                                   float *acts, size_t acts_bytes, lffn_stream_t stream) {
+    int rc = check_proj_desc(desc, "proj_fwd_train");
+    if (rc != LFFN_OK) return rc;
+    LFFN_REQUIRE(N >= 0, LFFN_ERR_INVALID_ARG, "proj_fwd_train: N = %lld", (long long)N);
+    if (N == 0) return LFFN_OK;
+    LFFN_REQUIRE(x != nullptr && z != nullptr && acts != nullptr, LFFN_ERR_INVALID_ARG, "proj_fwd_train: NULL buffer");
+    LFFN_REQUIRE(acts_bytes >= proj_acts_bytes(desc->D, desc->S, desc->R, N), LFFN_ERR_SCRATCH,
+                 "proj_fwd_train: %zu bytes needed for the stage inputs, %zu given",
+                 proj_acts_bytes(desc->D, desc->S, desc->R, N), acts_bytes);
+    return launch_proj_fwd_train(*desc, x, x_dtype, N, z, acts, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int lffn_proj_bwd(const lffn_hash_desc *desc, const float *proj_w_oi, const void *x, int32_t x_dtype, int64_t N,
-                             const float *dz, float *du, float *dw, float *dbias, void *ws, size_t ws_bytes,
-                             lffn_stream_t stream) {
-    LFFN_REQUIRE(desc != nullptr && desc->proj_w != nullptr && proj_w_oi != nullptr, LFFN_ERR_INVALID_ARG,
-                 "proj_bwd: NULL descriptor or weights");
-    LFFN_REQUIRE(desc->BS == 64 && desc->transpose_w == 1 && desc->D % 256 == 0 && desc->D >= 256 && desc->D <= 1024,
-                 LFFN_ERR_UNSUPPORTED,
-                 "proj_bwd: covers 64 x 64 blocks with D in {256, 512, 1024} and desc->proj_w in [i][o] order "
-                 "(transpose_w = 1); got BS = %d, D = %d, transpose_w = %d", desc->BS, desc->D, desc->transpose_w);
-    LFFN_REQUIRE(desc->d_in >= 1 && desc->d_in <= desc->D && desc->S >= 1 && desc->R >= 1 && desc->T >= 1 && desc->k >= 1 &&
-                     (long long)desc->R * desc->D >= (long long)desc->T * desc->k,
-                 LFFN_ERR_INVALID_ARG, "proj_bwd: inconsistent descriptor");
+                             const float *dz, float *du, float *dw, float *dbias, const float *saved_acts, void *ws,
+                             size_t ws_bytes, lffn_stream_t stream) {
+    int rcd = check_proj_desc(desc, "proj_bwd");
+    if (rcd != LFFN_OK) return rcd;
+    LFFN_REQUIRE(proj_w_oi != nullptr, LFFN_ERR_INVALID_ARG, "proj_bwd: NULL weights");
     LFFN_REQUIRE(N >= 0, LFFN_ERR_INVALID_ARG, "proj_bwd: N = %lld", (long long)N);
     if (N == 0) return LFFN_OK;
     LFFN_REQUIRE(x != nullptr && dz != nullptr && ws != nullptr, LFFN_ERR_INVALID_ARG, "proj_bwd: NULL buffer");
-    LFFN_REQUIRE(ws_bytes >= proj_bwd_ws_bytes(desc->D, desc->S, N), LFFN_ERR_SCRATCH,
-                 "proj_bwd: workspace of %zu bytes needed, %zu given", proj_bwd_ws_bytes(desc->D, desc->S, N), ws_bytes);
+    const size_t need = proj_bwd_ws_bytes(desc->D, desc->S, N) + dbias_ws_bytes(desc->T * desc->k);
+    LFFN_REQUIRE(ws_bytes >= need, LFFN_ERR_SCRATCH, "proj_bwd: workspace of %zu bytes needed, %zu given", need, ws_bytes);
     LFFN_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0 && (reinterpret_cast<uintptr_t>(proj_w_oi) & 15u) == 0,
                  LFFN_ERR_INVALID_ARG, "proj_bwd: ws must be 256-byte aligned, the weights 16-byte aligned");
-    return launch_proj_bwd(*desc, proj_w_oi, x, x_dtype, N, dz, du, dw, dbias, ws, static_cast<cudaStream_t>(stream));
+    return launch_proj_bwd(*desc, proj_w_oi, x, x_dtype, N, dz, du, dw, dbias, saved_acts, ws,
+                           static_cast<cudaStream_t>(stream));
 }

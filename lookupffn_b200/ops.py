@@ -186,10 +186,30 @@ class CodeScore(torch.autograd.Function):
         return code_weights_bwd(z, dw, ctx.weight_mode, ctx.tau), None, None, None
 
 
-def proj_bwd(x, weight, kernel_weight, out_dim, dz, had_scale, mix_a, mix_b, need_dw=True, need_dbias=True):
+# Stage inputs kept by the training forward for the backward pass (what the reference's autograd keeps for its einsum
+# chain): up to this many bytes per call; above it the backward pass recomputes them.
+PROJECTION_SAVE_LIMIT_BYTES = 2 << 30
+
+
+def proj_fwd_train(x, kernel_weight, bias, out_dim, had_scale, mix_a, mix_b):
+    """z = BH4(x) [N, out_dim] through lffn_proj_fwd_train, plus the stage inputs for proj_bwd (64 x 64 blocks)."""
+    N = x.shape[0]
+    desc = make_hash_desc(x.shape[1], kernel_weight, bias, out_dim, 1, transpose_w=True, had_scale=had_scale,
+                          mix_a=mix_a, mix_b=mix_b, weight_mode=WEIGHT_ONES)
+    lib = L.lib()
+    nbytes = lib.lffn_proj_acts_bytes(C.byref(desc), N)
+    acts = torch.empty(nbytes // 4, dtype=torch.float32, device=x.device)
+    z = torch.empty((N, out_dim), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        L.check(lib.lffn_proj_fwd_train(C.byref(desc), L.ptr(x), L.dtype_code(x.dtype), N, L.ptr(z), L.ptr(acts), nbytes,
+                                        L.stream_ptr(x.device)))
+    return z, acts
+
+
+def proj_bwd(x, weight, kernel_weight, out_dim, dz, had_scale, mix_a, mix_b, need_dw=True, need_dbias=True, acts=None):
     """Backward of z = BH4(x) for 64 x 64 blocks through lffn_proj_bwd: returns (du [N, D], dweight in the parameter's
     layout or None, dbias or None).  weight [R, S, NB, 64(o), 64(i)] is the parameter, kernel_weight its [.., i, o]
-    copy that the forward fast path streams."""
+    copy that the forward fast path streams, acts the stage inputs from proj_fwd_train (None: recomputed)."""
     R, S, NB, BS, _ = weight.shape
     D = NB * BS
     N = x.shape[0]
@@ -206,7 +226,7 @@ def proj_bwd(x, weight, kernel_weight, out_dim, dz, had_scale, mix_a, mix_b, nee
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         L.check(lib.lffn_proj_bwd(C.byref(desc), L.ptr(w_oi), L.ptr(x), L.dtype_code(x.dtype), N, L.ptr(dz), L.ptr(du),
-                                  L.ptr(dw), L.ptr(dbias), L.ptr(ws), nbytes, L.stream_ptr(dev)))
+                                  L.ptr(dw), L.ptr(dbias), L.ptr(acts), L.ptr(ws), nbytes, L.stream_ptr(dev)))
     return du, dw, dbias
 
 
@@ -227,20 +247,24 @@ class Projection(torch.autograd.Function):
         if x.dtype == torch.float16:
             x = x.float()
         x = _contig(x)
-        _, _, z = hash_fwd(x, desc, want_z=True, want_codes=False)
         fast = BS == 64 and D % 256 == 0 and D <= 1024 and kernel_transposed
-        ctx.save_for_backward(x, weight, kernel_weight if fast else None)
+        acts = None
+        if fast and R * S * (-(-x.shape[0] // 32)) * D * 32 * 4 <= PROJECTION_SAVE_LIMIT_BYTES:
+            z, acts = proj_fwd_train(x, kernel_weight, _contig(bias.detach().float()), out_dim, had_scale, mix_a, mix_b)
+        else:
+            _, _, z = hash_fwd(x, desc, want_z=True, want_codes=False)
+        ctx.save_for_backward(x, weight, kernel_weight if fast else None, acts)
         ctx.meta = (D, BS, S, R, out_dim, had_scale, mix_a, mix_b, fast)
         return z
 
     @staticmethod
     def backward(ctx, dz):
-        x, weight, kernel_weight = ctx.saved_tensors
+        x, weight, kernel_weight, acts = ctx.saved_tensors
         D, BS, S, R, out_dim, had_scale, mix_a, mix_b, fast = ctx.meta
         N, d_in = x.shape
         if fast:
             du, dweight, dbias = proj_bwd(x, weight, kernel_weight, out_dim, dz, had_scale, mix_a, mix_b,
-                                          need_dw=ctx.needs_input_grad[1], need_dbias=ctx.needs_input_grad[2])
+                                          need_dw=ctx.needs_input_grad[1], need_dbias=ctx.needs_input_grad[2], acts=acts)
             dx = du[:, :d_in].to(x.dtype) if ctx.needs_input_grad[0] else None
             if dweight is not None:
                 dweight = dweight.to(weight.dtype)

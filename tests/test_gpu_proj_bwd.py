@@ -68,6 +68,13 @@ def test_proj_bwd_matches_fp64_autograd(dev, case):
     du, dw, db = ops.proj_bwd(x, weight, wt, out_dim, dz, hs, mix_a, mix_b)
     du2, dw2, db2 = ops.proj_bwd(x, weight, wt, out_dim, dz, hs, mix_a, mix_b)
     assert torch.equal(du, du2) and torch.equal(dw, dw2) and torch.equal(db, db2)
+    # the training forward keeps the stage inputs: same z as the plain kernel, same gradients as recomputing
+    z_t, acts = ops.proj_fwd_train(x, wt, bias, out_dim, hs, mix_a, mix_b)
+    desc = ops.make_hash_desc(d_in, wt, bias, out_dim, 1, transpose_w=True, had_scale=hs, mix_a=mix_a, mix_b=mix_b,
+                              weight_mode=ops.WEIGHT_ONES)
+    assert torch.equal(z_t, ops.hash_fwd(x, desc, want_z=True, want_codes=False)[2])
+    du3, dw3, db3 = ops.proj_bwd(x, weight, wt, out_dim, dz, hs, mix_a, mix_b, acts=acts)
+    assert torch.equal(du, du3) and torch.equal(dw, dw3) and torch.equal(db, db3)
 
     x64 = x.double().requires_grad_(True)
     w64 = weight.double().requires_grad_(True)
