@@ -80,7 +80,11 @@ __global__ void __launch_bounds__(LFFN_BWW_THREADS, LFFN_BWW_MINBLOCKS)
             const int cnt = min(32, icnt - g0);
             const int my_i = next_i;
             if (g0 + 32 + lane < icnt) next_i = __ldg(ip + g0 + 32 + lane);
-            // branch-free: rows past the list end or out of range read a substitute row; their sums are discarded
+            // branch-free: rows past the list end or out of range read a substitute row (row 0) and their sums are
+            // discarded; every lane checks the one index it loaded, the loop broadcasts checked indices only
+            const bool mine_in_range = (unsigned long long)(long long)my_i < (unsigned long long)S;
+            bad |= (lane < cnt) && !mine_in_range;
+            const int san_i = mine_in_range ? my_i : 0;
             float p[32];
 #pragma unroll
             for (int j0 = 0; j0 < 32; j0 += U) {
@@ -88,10 +92,7 @@ __global__ void __launch_bounds__(LFFN_BWW_THREADS, LFFN_BWW_MINBLOCKS)
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     const int j = j0 + u;
-                    int r = __shfl_sync(FULL, my_i, j);
-                    const bool in_range = (unsigned long long)(long long)r < (unsigned long long)S;
-                    bad |= (j < cnt) && !in_range;
-                    r = in_range ? r : 0;
+                    const int r = __shfl_sync(FULL, san_i, j);
                     const uint4 *row = tv + (long long)r * row_vecs;
 #pragma unroll
                     for (int v = 0; v < VPL; v++) {

@@ -128,11 +128,17 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
                 my_w = ld_stream_f32(wp + g0 + 32 + lane, pol_stream);
             }
             const int cnt = min(32, In - g0);
-            // The loop body is branch-free: an entry past the end of the list, or with an index outside
-            // [0, S), is replaced by (the group's first row, weight 0).  That row is part of the sum anyway,
-            // so the substitute adds exactly nothing even when the row holds Inf or NaN.
+            // The loop body is branch-free and free of per-row checks: every lane sanitises the one (index, weight)
+            // pair it loaded -- an entry past the end of the list, or with an index outside [0, S), becomes (the
+            // group's first row, weight 0); that row is part of the sum anyway, so the substitute adds exactly nothing
+            // even when the row holds Inf or NaN -- and the loop only broadcasts sanitised pairs.
             int safe = __shfl_sync(FULL, cur_i, 0);
             safe = (unsigned long long)(long long)safe < (unsigned long long)S ? safe : 0;
+            const bool mine_listed = lane < cnt;
+            const bool mine_in_range = (unsigned long long)(long long)cur_i < (unsigned long long)S;
+            bad |= mine_listed && !mine_in_range;
+            const int san_i = (mine_listed && mine_in_range) ? cur_i : safe;
+            const float san_w = (mine_listed && mine_in_range) ? cur_w : 0.f;
 #pragma unroll 1
             for (int j0 = 0; j0 < cnt; j0 += U) {
                 uint4 buf[U][VPL];
@@ -140,14 +146,10 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     const int j = j0 + u;
-                    int r = __shfl_sync(FULL, cur_i, j & 31);
-                    float wj = __shfl_sync(FULL, cur_w, j & 31);
-                    const bool in_list = j < cnt;
-                    const bool in_range = (unsigned long long)(long long)r < (unsigned long long)S;
-                    bad |= in_list && !in_range;
-                    const bool ok = in_list && in_range;
-                    r = ok ? r : safe;
-                    ww[u] = ok ? wj : 0.f;
+                    const int r = __shfl_sync(FULL, san_i, j & 31);
+                    const float wj = __shfl_sync(FULL, san_w, j & 31);
+                    if constexpr (32 % U != 0) ww[u] = j < 32 ? wj : 0.f;  // a step that runs past lane 31 wraps around
+                    else ww[u] = wj;
                     const uint4 *row = tv + (long long)r * row_vecs;
 #pragma unroll
                     for (int v = 0; v < VPL; v++) {

@@ -165,3 +165,21 @@ def test_cpu_bh4_convention_matches_reference_cpu_extension():
     other = O.project(x, w, out.shape[1], transpose_w=False, had_scale=1.0 / D, mix_a=1.0, mix_b=0.0)
     assert rel_err(other, out) > 0.5       # the CUDA convention is a different function of the same weights
     assert rel_err(O.fwht(g["fwht_x"], 1.0 / D), g["fwht_out"]) < 1e-6
+
+
+def test_sign_mismatch_report_bins_by_magnitude():
+    z_ref = np.array([[0.5, -2e-7, 3e-8, -4e-6, 0.2, -0.3]], dtype=np.float32)
+    z = z_ref.copy()
+    z[0, 1] = 1e-7      # flipped, |v| = 2e-7: exempt
+    z[0, 2] = -1e-8     # flipped, |v| = 3e-8: exempt
+    z[0, 3] = 1e-6      # flipped, |v| = 4e-6: not exempt
+    rep = PAR.sign_mismatch_report(z, z_ref)
+    assert rep["coordinates_checked"] == 6 and rep["sign_mismatches"] == 3
+    assert rep["mismatches_with_abs_v_below_1e-6"] == 2 and rep["mismatches_with_abs_v_at_or_above_1e-6"] == 1
+    assert rep["mismatches_by_abs_v"] == {"[0, 1e-07)": 1, "[1e-07, 1e-06)": 1, "[1e-06, 1e-05)": 1, "[1e-05, 0.0001)": 0,
+                                          "[0.0001, inf)": 0}
+    with pytest.raises(AssertionError):
+        PAR.assert_codes_match_up_to_tiny_coordinates(z, z_ref)
+    z[0, 3] = z_ref[0, 3]
+    rep2, mask = PAR.assert_codes_match_up_to_tiny_coordinates(z, z_ref)
+    assert mask.sum() == 2 and rep2["largest_abs_v_of_a_mismatch"] < 1e-6
