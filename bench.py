@@ -303,22 +303,24 @@ def run_ours(args, rank, world, local):
     l2_resident_ms = ev_l2[0].elapsed_time(ev_l2[1]) / 3
     del idx_l2, y_l2
 
-    # Hardware ceiling of that access pattern: plain coalesced 16-byte reads of a 32 MiB buffer that stays in L2
-    # (lffn_probe_read), in three configurations of loads in flight per SM; the best one is the ceiling.  Outside
-    # the timed region.  One launch reads about as many bytes as the gather launch does.
-    probe_bytes = min(32 << 20, tables.numel() * tables.element_size()) // 16 * 16
-    reps = max(8, int(algorithmic_bytes_per_token(w) * N // probe_bytes))
+    # Hardware ceiling of that access pattern: plain coalesced 16-byte reads of a 32 or 64 MiB buffer that stays in L2
+    # (lffn_probe_read), in four configurations of loads in flight per SM; the best one is the ceiling.  Outside the
+    # timed region.  One launch reads about as many bytes as the gather launch does.
     sink = torch.zeros(1, dtype=torch.int32, device=device)
     l2_probe = {}
-    for mode, name in ((0, "12_loads_per_thread_gather_residency"), (1, "8_loads_per_thread_full_occupancy"),
-                       (2, "16_loads_per_thread_full_occupancy")):
-        L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, 4, mode, L.ptr(sink), sp))
-        ev_p = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-        ev_p[0].record(stream)
-        L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, reps, mode, L.ptr(sink), sp))
-        ev_p[1].record(stream)
-        torch.cuda.synchronize()
-        l2_probe[name] = probe_bytes * reps / (ev_p[0].elapsed_time(ev_p[1]) * 1e-3) / 1e9  # GB/s
+    for mbytes in (32, 64):
+        probe_bytes = min(mbytes << 20, tables.numel() * tables.element_size()) // 16 * 16
+        for mode, name in ((0, "12_loads_per_thread_gather_residency"), (1, "8_loads_per_thread"),
+                           (2, "16_loads_per_thread"), (3, "4_loads_per_thread_64_warps")):
+            got = C.c_size_t(0)
+            L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, 4, mode, L.ptr(sink), C.byref(got), sp))
+            reps = max(8, int(algorithmic_bytes_per_token(w) * N // max(1, got.value)))
+            ev_p = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            ev_p[0].record(stream)
+            L.check(lib.lffn_probe_read(L.ptr(tables), probe_bytes, reps, mode, L.ptr(sink), C.byref(got), sp))
+            ev_p[1].record(stream)
+            torch.cuda.synchronize()
+            l2_probe[f"{name}_{mbytes}MiB"] = got.value * reps / (ev_p[0].elapsed_time(ev_p[1]) * 1e-3) / 1e9  # GB/s
     l2_read_peak = max(l2_probe.values())
 
     if args.no_e2e:  # profiling runs: device path only
@@ -433,8 +435,8 @@ def run_ours(args, rank, world, local):
                      "dram_frac": traffic / (gather_ms * 1e-3) / 1e9 / peak if traffic else None,
                      "l2_hit_rate": prof["l2_hit_rate"] if prof else None,
                      "l2_read_peak": l2_read_peak, "frac_of_l2_read_peak": achieved / l2_read_peak,
-                     "l2_read_peak_source": "lffn_probe_read: 16-byte loads of an L2-resident 32 MiB buffer, best of "
-                                            "three configurations, measured in this run",
+                     "l2_read_peak_source": "lffn_probe_read: 16-byte loads of an L2-resident 32 / 64 MiB buffer, best of "
+                                            "eight configurations, measured in this run",
                      "l2_read_probe_GBps": l2_probe,
                      # the same launch with all indices folded into an L2-resident band of 32 tables:
                      "l2_resident_launch_ms": l2_resident_ms, "frac_of_l2_resident_launch": l2_resident_ms / gather_ms},

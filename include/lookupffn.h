@@ -122,16 +122,18 @@ int lffn_device_status(uint32_t *status_out, lffn_stream_t stream);
 int lffn_selftest_bounded_wait(int32_t poll_limit, lffn_stream_t stream);
 
 /*
- * Measurement probe (no reference counterpart; not on the layer's path): reads `bytes` bytes at `buf` `repeats`
- * times with the gather kernel's kind of access -- coalesced 16-byte read-only loads that bypass L1.  With a
- * buffer that fits L2 and several repeats, bytes * repeats / elapsed time is an L2 read bandwidth.  How much an SM
- * keeps in flight decides the rate, so there are three configurations: mode 0 = 12 loads per thread at the gather
- * kernel's own residency (4 CTAs of 128 threads per SM), mode 1 = 8 and mode 2 = 16 loads per thread at full
- * occupancy.  The benchmark quotes the gather against the best of them.  `sink` is one device word that keeps the
- * loads observable (it is practically never written).
+ * Measurement probe (no reference counterpart; not on the layer's path): reads the bytes at `buf` `repeats`
+ * times with the gather kernel's kind of access -- coalesced 16-byte read-only loads that bypass L1 -- and nothing
+ * else in the loop.  With a buffer that fits L2 and several repeats, bytes read / elapsed time is an L2 read
+ * bandwidth.  How much an SM keeps in flight decides the rate, so there are four configurations: mode 0 = 12 loads
+ * per thread at the gather kernel's own residency (4 CTAs of 128 threads per SM); modes 1, 2, 3 = 8, 16, 4 loads
+ * per thread with as many CTAs per SM as fit.  The benchmark quotes the gather against the best of them.  A launch
+ * reads the largest whole number of grid-wide slabs that fits in `bytes`; *bytes_read_per_repeat (host pointer, may
+ * be NULL) receives that amount.  `sink` is one device word that keeps the loads observable (practically never
+ * written).
  */
 int lffn_probe_read(const void *buf, size_t bytes, int32_t repeats, int32_t mode, uint32_t *sink,
-                    lffn_stream_t stream);
+                    size_t *bytes_read_per_repeat, lffn_stream_t stream);
 
 /*
  * Walsh-Hadamard transform of each row, out = x H_D * scale.  Replaces

@@ -45,7 +45,8 @@ _SIGNATURES = {
     "lffn_trace_last_layer_times": (C.c_int, [C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "lffn_device_status": (C.c_int, [C.POINTER(C.c_uint32), C.c_void_p]),
     "lffn_selftest_bounded_wait": (C.c_int, [C.c_int32, C.c_void_p]),
-    "lffn_probe_read": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "lffn_probe_read": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int32, C.c_int32, C.c_void_p, C.POINTER(C.c_size_t),
+                                  C.c_void_p]),
     "lffn_fwht": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]),
     "lffn_hash_fwd": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
