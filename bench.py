@@ -1234,8 +1234,9 @@ def main():
     ap.add_argument("--projection", default="bh4", choices=["bh4", "sign_hadamard", "dense"],
                     help="projection of the c2enc workload (bh4 = the reference configs)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--e2e-chunk", type=int, default=2368,
-                    help="tokens per chunk of the host-buffer call; 2368 = one resident wave of the gather kernel (148 SMs x 16 warps)")
+    ap.add_argument("--e2e-chunk", type=int, default=4736,
+                    help="tokens per chunk of the host-buffer call; 4736 = two resident waves of the gather kernel "
+                         "(148 SMs x 16 warps each); the call itself halves the first two and the last two chunks")
     ap.add_argument("--cpu-tokens", type=int, default=4096)
     ap.add_argument("--shard", default="tokens", choices=["tokens", "tables"],
                     help="tokens: each rank its own tokens, tables replicated (default); tables: tables split by T, "

@@ -337,7 +337,8 @@ int lffn_layer_fwd_ln_residual(const lffn_hash_desc *desc, const float *ln_gamma
 /*
  * The same forward for callers that hold HOST buffers (the shape of the reference's CPU
  * inference path, compare.py:23-37): x_host [N, d_in] and out_host [N, d_out] are host pointers
- * (pinned memory makes the copies asynchronous).  Tokens are cut into chunks that three internal
+ * (pinned memory makes the copies asynchronous).  Tokens are cut into chunks of chunk_tokens (the first
+ * two and the last two chunks half as long, to shorten the copies nothing can overlap) that three internal
  * streams take in turn, so the copy-in of later chunks and the copy-out of earlier ones overlap the kernels.  Parameters
  * (desc->proj_w, proj_bias, tables, bias) stay on the device.  `ws` is a device workspace of
  * lffn_layer_fwd_host_ws_bytes(...) bytes.  Synchronous: returns when out_host is complete.

@@ -384,6 +384,9 @@ int lffn_layer_fwd_ln_residual(const lffn_hash_desc *desc, const float *ln_gamma
 #ifndef LFFN_HOST_LANES
 #define LFFN_HOST_LANES 3
 #endif
+#ifndef LFFN_HOST_RAMP
+#define LFFN_HOST_RAMP 1
+#endif
 constexpr int HOST_LANES = LFFN_HOST_LANES;  // streams alternating over token chunks in lffn_layer_fwd_host
 static size_t esize(int dtype) { return dtype == LFFN_BF16 ? 2 : 4; }
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -474,10 +477,20 @@ int lffn_layer_fwd_host(const lffn_hash_desc *desc, const void *x_host, int32_t 
         if (_e != cudaSuccess) return finish(cuda_fail(_e, #expr));   \
     } while (0)
     for (int i = 0; i < HOST_LANES; i++) LFFN_HOST_CUDA(cudaStreamWaitEvent(L.s[i], L.start, 0));
-    int64_t c = 0;
-    for (int64_t n0 = 0; n0 < N; n0 += chunk_tokens, c++) {
+    // Chunks are chunk_tokens long, except at the two ends of the call: the first two and the last two are half as
+    // long, so that the first copy-in and the last copy-out, which nothing can overlap, are short while the chunks in
+    // between amortise their launches.
+    const int64_t half = (chunk_tokens + 1) / 2;
+    int64_t c = 0, nt = 0;
+    for (int64_t n0 = 0; n0 < N; n0 += nt, c++) {
         const int lane = (int)(c % HOST_LANES);
-        const int64_t nt = (N - n0 < chunk_tokens) ? (N - n0) : chunk_tokens;
+        const int64_t left = N - n0;
+#if LFFN_HOST_RAMP
+        nt = (c < 2 || left <= chunk_tokens) ? half : chunk_tokens;
+#else
+        nt = chunk_tokens;
+#endif
+        if (nt > left) nt = left;
         char *base = static_cast<char *>(ws) + lane * per_lane;
         void *xd = base;
         void *od = base + xb;

@@ -233,10 +233,13 @@ class PeerOutput:
         self.handle = symm_mem.rendezvous(self.local, self.group)
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.ptr_array = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self._flag = torch.zeros(1, dtype=torch.float32, device=device)
 
     def _rank_barrier(self):
-        torch.cuda.current_stream().synchronize()
-        dist.barrier(self.group)
+        """Orders the ranks on the device, without stopping the host: a one-element all-reduce enqueued on every
+        rank's stream.  It completes on a rank only after every rank has reached it, i.e. after everything each rank
+        enqueued before it has finished; what this rank enqueues afterwards waits for it."""
+        dist.all_reduce(self._flag, group=self.group)
 
     def reset(self, bias=None):
         """Before a step.  "add": the owner writes the initial value (zeros or the bias) of its rows.  Both
