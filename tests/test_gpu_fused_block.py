@@ -213,6 +213,13 @@ T_CASES = [
     (9, 256, 256, 700, 1, O.WEIGHT_SCORE, O.MSB_FIRST, False, (1, 650)),
     (40, 300, 512, 40, 16, O.WEIGHT_SOFT_FLIP, O.LSB_FIRST, True, (5, 30)),
     (50, 512, 512, 64, 8, O.WEIGHT_SCORE, O.MSB_FIRST, True, (12, 40)),     # range not a multiple of four tables
+    # code lengths that do not divide D / 32: tables straddle lanes and rotations
+    (33, 1000, 1024, 700, 6, O.WEIGHT_SCORE, O.MSB_FIRST, True, (100, 400)),
+    (21, 1024, 1024, 1365, 6, O.WEIGHT_SCORE, O.MSB_FIRST, False, (1024, 341)),   # a rank's share of a large layer
+    (19, 512, 512, 100, 10, O.WEIGHT_SCORE, O.LSB_FIRST, True, None),
+    (14, 300, 512, 64, 12, O.WEIGHT_SOFT_FLIP, O.MSB_FIRST, False, (7, 50)),
+    (27, 256, 256, 90, 3, O.WEIGHT_ONES, O.MSB_FIRST, True, (1, 88)),
+    (11, 768, 1024, 40, 13, O.WEIGHT_SCORE, O.MSB_FIRST, True, None),
 ]
 
 
