@@ -528,7 +528,7 @@ def table_sharded_record(args, rank, world, local):
     NVLink) with both exchanges, beside the same per-GPU shape without any exchange.  k = 8 at every N; k = 6 and
     k = 12 too at 8 GPUs.  Every rank runs it; rank 0 reports."""
     device = torch.device("cuda", local)
-    ks = ["c5k8"] + (["c5k12", "c5k6"] if world >= 8 else [])
+    ks = args.table_sharded_ks.split(",") if args.table_sharded_ks else ["c5k8"] + (["c5k12", "c5k6"] if world >= 8 else [])
     steps, warmup = 5, 3
     rec = {"what": "tables sharded by T, all tokens on every GPU, fp32 partial sums reduce-scattered over tokens",
            "nccl_ranks": torch.distributed.get_world_size(), "steps": steps, "warmup": warmup, "runs": {}}
@@ -1245,6 +1245,9 @@ def main():
     ap.add_argument("--rs", default="nccl", choices=["nccl", "fused", "fused-store"],
                     help="--shard tables: combine partial sums with NCCL reduce-scatter, or inside the gather kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--table-sharded-ks", default="",
+                    help="comma-separated config-5 workloads of the table-sharded record (default: c5k8, plus c5k12 and "
+                         "c5k6 at 8 GPUs)")
     ap.add_argument("--no-table-sharded", action="store_true",
                     help="skip the short table-sharded run appended to the line when more than one GPU runs")
     ap.add_argument("--no-encoder", action="store_true", help="skip the short config-2 encoder run appended at N=1")

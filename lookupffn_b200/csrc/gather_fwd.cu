@@ -51,7 +51,9 @@ __device__ __forceinline__ void red_add_v4_f32(float *p, float a, float b, float
 // peers[] holding every rank's buffer address (peer-mapped over NVLink): either added in place (vector
 // reductions) or stored into this rank's slab of the owner's staging buffer.  Gather and the exchange step of the
 // reduce-scatter become one kernel; the partial sums are never written to this GPU's HBM.
-template <typename TableT, typename OutT, int VPL, int U, bool FULLV, bool SCATTER = false>
+// SMODE: 0 = store the row locally; 1 / 2 / 3 = the scatter forms (bulk add, vector add, slab store), one
+// instantiation each so that every kernel carries only its own epilogue
+template <typename TableT, typename OutT, int VPL, int U, bool FULLV, int SMODE = 0>
 __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) gather_fwd_kernel(const int32_t *__restrict__ idx, const float *__restrict__ w,
                                                          const TableT *__restrict__ tables, OutT *__restrict__ out,
                                                          long long N, int I, long long S, int d, int col0,
@@ -59,6 +61,7 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
                                                          int i0, int icnt, int resume, int finish, uint32_t *status,
                                                          float *const *__restrict__ peers, long long rows_per_owner,
                                                          int slab, long long rot, const OutT *residual) {
+    constexpr bool SCATTER = SMODE != 0;
     // i0/icnt: the slice of each token's index list this launch consumes; resume: start from the fp32 partial
     // sums already in `out`; finish: last slice, add the bias and convert (see launch_vpl_f on why lists are sliced)
     // residual (may be null, may be `out` itself): [N, d] added after the bias, out = fl(fl(acc + bias) + residual),
@@ -177,7 +180,7 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
             // `slab` of the owner's [n_ranks, rows_per_owner, d] staging buffer (the owner sums the slabs afterwards)
             const long long row = (slab < 0 ? 0 : (long long)slab * rows_per_owner) + n % rows_per_owner;
             float *prow = peers[n / rows_per_owner] + row * d + (long long)col0 * EPV;
-            if (slab == LFFN_SLAB_BULK_ADD) {
+            if constexpr (SMODE == 1) {
                 // One bulk reduction per row instead of 16-byte ones: the warp parks its fp32 row in shared memory
                 // and lane 0 hands it to the TMA unit, which adds it into the owner's row (cp.reduce.async.bulk,
                 // f32 add) as one transfer of up to 8 KB -- far fewer, larger packets on NVLink.
@@ -213,7 +216,7 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
                 if (c < nvec) {
 #pragma unroll
                     for (int q = 0; q < EPV / 4; q++) {
-                        if (slab < 0)
+                        if constexpr (SMODE == 2)
                             red_add_v4_f32(prow + c * EPV + 4 * q, acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2],
                                            acc[v][4 * q + 3]);
                         else
@@ -266,7 +269,7 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
     }
     if constexpr (SCATTER) {
         // the bulk reductions of this thread have left shared memory and completed before the CTA exits
-        if (slab == LFFN_SLAB_BULK_ADD && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (SMODE == 1 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     if (bad) atomicOr(status, LFFN_STATUS_INDEX_RANGE);
 }
@@ -319,7 +322,7 @@ static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, 
     return LFFN_OK;
 }
 
-template <typename TableT, int VPL, bool FULLV>
+template <typename TableT, int VPL, bool FULLV, int SMODE>
 static int launch_scatter_f(const int32_t *idx, const float *w, const void *tables, float *const *peers,
                             long long rows_per_owner, int slab, long long rot, int64_t N, int I, int64_t S, int d, int col0,
                             cudaStream_t st) {
@@ -328,7 +331,7 @@ static int launch_scatter_f(const int32_t *idx, const float *w, const void *tabl
                       : (VPL == 4 && sizeof(TableT) == 2) ? 3
                       : (VPL <= 6 ? LFFN_GATHER_U_MEDIUM : LFFN_GATHER_U_WIDE);
     constexpr int THREADS = LFFN_GATHER_THREADS;
-    auto kern = gather_fwd_kernel<TableT, float, VPL, U, FULLV, true>;
+    auto kern = gather_fwd_kernel<TableT, float, VPL, U, FULLV, SMODE>;
     int per_sm = 0;
     LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, 0));
     if (per_sm < 1) per_sm = 1;
@@ -339,7 +342,7 @@ static int launch_scatter_f(const int32_t *idx, const float *w, const void *tabl
     uint32_t *status = status_word();
     LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
     const int slab_k = slab;
-    const size_t smem = slab_k == LFFN_SLAB_BULK_ADD ? (size_t)(THREADS / 32) * VPL * 32 * Elem<TableT>::PER_VEC * sizeof(float) : 0;
+    const size_t smem = SMODE == 1 ? (size_t)(THREADS / 32) * VPL * 32 * Elem<TableT>::PER_VEC * sizeof(float) : 0;
     if (smem > 48 * 1024) LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem));
     if (per_sm < 1) per_sm = 1;
@@ -363,9 +366,11 @@ static int launch_scatter_typed(const int32_t *idx, const float *w, const void *
         const int vpl = (nvec + 31) / 32;
         const bool full = nvec == vpl * 32;
         int rc;
-#define LFFN_SCATTER_CASE(V)                                                                                              \
-    rc = full ? launch_scatter_f<TableT, V, true>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st)      \
-              : launch_scatter_f<TableT, V, false>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st)
+#define LFFN_SCATTER_MODE(V, F)                                                                                              \
+    (slab == LFFN_SLAB_BULK_ADD     ? launch_scatter_f<TableT, V, F, 1>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st) \
+     : slab == LFFN_SLAB_VECTOR_ADD ? launch_scatter_f<TableT, V, F, 2>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st) \
+                                    : launch_scatter_f<TableT, V, F, 3>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st))
+#define LFFN_SCATTER_CASE(V) rc = full ? LFFN_SCATTER_MODE(V, true) : LFFN_SCATTER_MODE(V, false)
         switch (vpl) {
             case 1: LFFN_SCATTER_CASE(1); break;
             case 2: LFFN_SCATTER_CASE(2); break;
@@ -376,6 +381,7 @@ static int launch_scatter_typed(const int32_t *idx, const float *w, const void *
             default: LFFN_SCATTER_CASE(8); break;
         }
 #undef LFFN_SCATTER_CASE
+#undef LFFN_SCATTER_MODE
         if (rc != LFFN_OK) return rc;
     }
     return LFFN_OK;
