@@ -478,8 +478,8 @@ def table_sharded_setup(w, rank, world, device):
 
 def table_sharded_step_fn(S, rs, chunk, world, device):
     """One step of the table-sharded forward with exchange `rs`: "nccl" (chunked NCCL reduce-scatter), "fused" (one
-    bulk reduction per row from the gather kernel into the owner's buffer over NVLink), "fused-store" (peer stores
-    into slabs), or "none" (no exchange: the rank's partial sums stay local -- the one-GPU pace of the same shape)."""
+    bulk reduction per row from the gather kernel into the owner's buffer over NVLink), "fused-store" (one bulk copy
+    per row into the rank's slab of the owner's buffer, the owner sums its slabs in rank order), or "none" (no exchange: the rank's partial sums stay local -- the one-GPU pace of the same shape)."""
     from lookupffn_b200 import ops, sharded
 
     x, tables, bias, desc = S["x"], S["tables"], S["bias"], S["desc"]
@@ -539,14 +539,16 @@ def table_sharded_record(args, rank, world, local):
         run = {"tokens": N, "tables_per_gpu": w["T"], "k": w["k"], "d": d_out,
                "reduce_scattered_bytes_per_gpu": N * d_out * 4,
                "bytes_leaving_each_gpu_over_nvlink": N * d_out * 4 * (world - 1) // world}
-        for rs in ("none", "nccl", "fused"):
+        keys = {"none": "one_gpu_pace_no_exchange", "nccl": "nccl_reduce_scatter", "fused": "fused_in_gather_kernel",
+                "fused-store": "fused_in_gather_kernel_slabs"}
+        for rs in ("none", "nccl", "fused", "fused-store"):
             step, peers = table_sharded_step_fn(S, rs, args.rs_chunk, world, device)
             ms, _ = time_steps(step, steps, warmup, device, world)
-            key = {"none": "one_gpu_pace_no_exchange", "nccl": "nccl_reduce_scatter", "fused": "fused_in_gather_kernel"}[rs]
-            run[key] = {"ms_per_step": ms, "tokens_per_s": N / (ms * 1e-3)}
+            run[keys[rs]] = {"ms_per_step": ms, "tokens_per_s": N / (ms * 1e-3)}
             del step, peers
+            torch.cuda.empty_cache()
         base = run["one_gpu_pace_no_exchange"]["ms_per_step"]
-        for key in ("nccl_reduce_scatter", "fused_in_gather_kernel"):
+        for key in list(keys.values())[1:]:
             run[key]["pace_vs_no_exchange"] = base / run[key]["ms_per_step"]
         rec["runs"][name] = run
         del S

@@ -245,8 +245,10 @@ int lffn_gather_fwd_residual(const int32_t *idx, const float *w, const void *tab
  *              of summation across ranks is not fixed.
  *   slab = -2: the same in-place add, carried out with 16-byte vector reductions (red.global.add.v4.f32): many
  *              small packets instead of one large one (slower over NVLink; kept for comparison).
- *   slab >= 0: buffers are [n_owners, rows_per_owner, d]; the row is STORED (plain 16-byte stores) into slab
- *              `slab` (the caller's rank).  The owner then sums its slabs in rank order: deterministic.
+ *   slab >= 0: buffers are [n_owners, rows_per_owner, d]; the row is STORED into slab `slab` (the caller's rank):
+ *              with plain 16-byte stores, or, when LFFN_SCATTER_SLAB_BULK is or-ed into `slab`, as one bulk copy
+ *              (cp.async.bulk) from the row parked in shared memory.  The owner then sums its slabs in rank order:
+ *              deterministic, and no read-modify-write on the remote side.
  * first_owner in [0, n_owners): the call walks the tokens starting with those of this owner and wraps around.
  * Ranks that run at the same time should pass different values ((rank + 1) % n_owners): then at any moment every
  * rank sends to a different owner and all NVLink ports are busy, instead of all ranks converging on one owner.
@@ -254,6 +256,7 @@ int lffn_gather_fwd_residual(const int32_t *idx, const float *w, const void *tab
  * Either way a buffer is complete once every rank's call has finished: the caller synchronises the ranks on the
  * host; the kernel itself never waits on a peer.
  */
+#define LFFN_SCATTER_SLAB_BULK 0x40000000
 int lffn_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tables, int32_t table_dtype,
                             float *const *out_ptrs, int32_t n_owners, int64_t rows_per_owner, int32_t slab,
                             int32_t first_owner, int64_t N, int32_t I, int64_t S, int32_t d, lffn_stream_t stream);

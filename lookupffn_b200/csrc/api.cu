@@ -301,7 +301,7 @@ int lffn_gather_fwd_scatter(const int32_t *idx, const float *w, const void *tabl
     LFFN_REQUIRE(tables != nullptr && out_ptrs != nullptr && (I == 0 || (idx != nullptr && w != nullptr)),
                  LFFN_ERR_INVALID_ARG, "gather_fwd_scatter: NULL buffer");
     LFFN_REQUIRE(aligned16(tables), LFFN_ERR_INVALID_ARG, "gather_fwd_scatter: tables must be 16-byte aligned");
-    LFFN_REQUIRE(slab >= -2 && slab < n_owners, LFFN_ERR_INVALID_ARG,
+    LFFN_REQUIRE(slab >= -2 && (slab < 0 || (slab & ~LFFN_SCATTER_SLAB_BULK) < n_owners), LFFN_ERR_INVALID_ARG,
                  "gather_fwd_scatter: slab %d is neither an add mode (-1, -2) nor a slab in [0, %d)", slab, n_owners);
     LFFN_REQUIRE(first_owner >= 0 && first_owner < n_owners, LFFN_ERR_INVALID_ARG,
                  "gather_fwd_scatter: first_owner %d outside [0, %d)", first_owner, n_owners);

@@ -38,7 +38,8 @@
 
 namespace lffn {
 
-// values of `slab` below zero select how a row is added into the owner's buffer (lffn_gather_fwd_scatter):
+// values of `slab` below zero select how a row is added into the owner's buffer (lffn_gather_fwd_scatter); a slab
+// index >= 0 may carry LFFN_SCATTER_SLAB_BULK:
 constexpr int LFFN_SLAB_BULK_ADD = -1;    // one bulk reduction per row
 constexpr int LFFN_SLAB_VECTOR_ADD = -2;  // 16-byte vector reductions
 
@@ -51,8 +52,8 @@ __device__ __forceinline__ void red_add_v4_f32(float *p, float a, float b, float
 // peers[] holding every rank's buffer address (peer-mapped over NVLink): either added in place (vector
 // reductions) or stored into this rank's slab of the owner's staging buffer.  Gather and the exchange step of the
 // reduce-scatter become one kernel; the partial sums are never written to this GPU's HBM.
-// SMODE: 0 = store the row locally; 1 / 2 / 3 = the scatter forms (bulk add, vector add, slab store), one
-// instantiation each so that every kernel carries only its own epilogue
+// SMODE: 0 = store the row locally; 1 / 2 / 3 / 4 = the scatter forms (bulk add, vector add, slab store with 16-byte
+// stores, slab store as one bulk copy), one instantiation each so that every kernel carries only its own epilogue
 template <typename TableT, typename OutT, int VPL, int U, bool FULLV, int SMODE = 0>
 __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) gather_fwd_kernel(const int32_t *__restrict__ idx, const float *__restrict__ w,
                                                          const TableT *__restrict__ tables, OutT *__restrict__ out,
@@ -180,10 +181,11 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
             // `slab` of the owner's [n_ranks, rows_per_owner, d] staging buffer (the owner sums the slabs afterwards)
             const long long row = (slab < 0 ? 0 : (long long)slab * rows_per_owner) + n % rows_per_owner;
             float *prow = peers[n / rows_per_owner] + row * d + (long long)col0 * EPV;
-            if constexpr (SMODE == 1) {
-                // One bulk reduction per row instead of 16-byte ones: the warp parks its fp32 row in shared memory
-                // and lane 0 hands it to the TMA unit, which adds it into the owner's row (cp.reduce.async.bulk,
-                // f32 add) as one transfer of up to 8 KB -- far fewer, larger packets on NVLink.
+            if constexpr (SMODE == 1 || SMODE == 4) {
+                // One bulk transfer per row instead of 16-byte ones: the warp parks its fp32 row in shared memory and
+                // lane 0 hands it to the TMA unit, which adds it into the owner's row (mode 1: cp.reduce.async.bulk,
+                // f32 add) or stores it into this rank's slab of the owner's buffer (mode 4: cp.async.bulk) as one
+                // transfer of up to 8 KB -- far fewer, larger packets on NVLink.
                 extern __shared__ __align__(16) float stage_all[];
                 float *stage = stage_all + (threadIdx.x >> 5) * (VPL * 32 * EPV);
                 if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous row left smem
@@ -202,10 +204,16 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
                 __syncwarp();
                 if (lane == 0) {
                     const unsigned bytes = (unsigned)(nvec * EPV * sizeof(float));
-                    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(
-                                     __cvta_generic_to_global(prow)),
-                                 "r"((unsigned)__cvta_generic_to_shared(stage)), "r"(bytes)
-                                 : "memory");
+                    if constexpr (SMODE == 1)
+                        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(
+                                         __cvta_generic_to_global(prow)),
+                                     "r"((unsigned)__cvta_generic_to_shared(stage)), "r"(bytes)
+                                     : "memory");
+                    else
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                                         __cvta_generic_to_global(prow)),
+                                     "r"((unsigned)__cvta_generic_to_shared(stage)), "r"(bytes)
+                                     : "memory");
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
                 continue;
@@ -269,7 +277,7 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
     }
     if constexpr (SCATTER) {
         // the bulk reductions of this thread have left shared memory and completed before the CTA exits
-        if (SMODE == 1 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if ((SMODE == 1 || SMODE == 4) && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     if (bad) atomicOr(status, LFFN_STATUS_INDEX_RANGE);
 }
@@ -342,7 +350,7 @@ static int launch_scatter_f(const int32_t *idx, const float *w, const void *tabl
     uint32_t *status = status_word();
     LFFN_REQUIRE(status != nullptr, LFFN_ERR_CUDA, "cannot locate the device status word");
     const int slab_k = slab;
-    const size_t smem = SMODE == 1 ? (size_t)(THREADS / 32) * VPL * 32 * Elem<TableT>::PER_VEC * sizeof(float) : 0;
+    const size_t smem = (SMODE == 1 || SMODE == 4) ? (size_t)(THREADS / 32) * VPL * 32 * Elem<TableT>::PER_VEC * sizeof(float) : 0;
     if (smem > 48 * 1024) LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     LFFN_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem));
     if (per_sm < 1) per_sm = 1;
@@ -357,7 +365,8 @@ static int launch_scatter_f(const int32_t *idx, const float *w, const void *tabl
 
 template <typename TableT>
 static int launch_scatter_typed(const int32_t *idx, const float *w, const void *tables, float *const *peers,
-                                long long rows_per_owner, int slab, long long rot, int64_t N, int I, int64_t S, int d, cudaStream_t st) {
+                                long long rows_per_owner, int slab, bool bulk_store, long long rot, int64_t N, int I, int64_t S,
+                                int d, cudaStream_t st) {
     constexpr int EPV = Elem<TableT>::PER_VEC;
     const int row_vecs = d / EPV;
     constexpr int MAXV = 8;
@@ -369,6 +378,7 @@ static int launch_scatter_typed(const int32_t *idx, const float *w, const void *
 #define LFFN_SCATTER_MODE(V, F)                                                                                              \
     (slab == LFFN_SLAB_BULK_ADD     ? launch_scatter_f<TableT, V, F, 1>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st) \
      : slab == LFFN_SLAB_VECTOR_ADD ? launch_scatter_f<TableT, V, F, 2>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st) \
+     : bulk_store                   ? launch_scatter_f<TableT, V, F, 4>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st) \
                                     : launch_scatter_f<TableT, V, F, 3>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, col0, st))
 #define LFFN_SCATTER_CASE(V) rc = full ? LFFN_SCATTER_MODE(V, true) : LFFN_SCATTER_MODE(V, false)
         switch (vpl) {
@@ -391,10 +401,12 @@ int launch_gather_fwd_scatter(const int32_t *idx, const float *w, const void *ta
                               float *const *peers, long long rows_per_owner, int slab, int first_owner, int64_t N, int I,
                               int64_t S, int d, cudaStream_t st) {
     const long long rot = N > 0 ? ((long long)first_owner * rows_per_owner) % N : 0;
+    const bool bulk_store = slab >= 0 && (slab & LFFN_SCATTER_SLAB_BULK) != 0;
+    if (slab >= 0) slab &= ~LFFN_SCATTER_SLAB_BULK;
     if (table_dtype == LFFN_F32)
-        return launch_scatter_typed<float>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, st);
+        return launch_scatter_typed<float>(idx, w, tables, peers, rows_per_owner, slab, bulk_store, rot, N, I, S, d, st);
     if (table_dtype == LFFN_BF16)
-        return launch_scatter_typed<__nv_bfloat16>(idx, w, tables, peers, rows_per_owner, slab, rot, N, I, S, d, st);
+        return launch_scatter_typed<__nv_bfloat16>(idx, w, tables, peers, rows_per_owner, slab, bulk_store, rot, N, I, S, d, st);
     set_error("gather_fwd_scatter: unknown table dtype %d", table_dtype);
     return LFFN_ERR_INVALID_ARG;
 }

@@ -17,6 +17,8 @@ import torch.nn as nn
 
 from . import ops
 
+SCATTER_SLAB_BULK = 0x40000000  # lookupffn.h: store a row into its slab as one bulk copy
+
 
 def token_range(N, rank, world):
     """Contiguous split of N tokens; the first N % world ranks take one more."""
@@ -277,7 +279,7 @@ def lookup_forward_table_sharded_fused(x, desc, tables_local, t_begin, t_count, 
     idx, w, _ = ops.hash_fwd(x, desc, t_begin=t_begin, t_count=t_count)
     tables_local = tables_local if tables_local.is_contiguous() else tables_local.contiguous()
     S, d = tables_local.shape
-    slab = peers.rank if peers.mode == "store" else -1
+    slab = (peers.rank | SCATTER_SLAB_BULK) if peers.mode == "store" else -1
     with torch.cuda.device(x.device):
         L.check(L.lib().lffn_gather_fwd_scatter(L.ptr(idx), L.ptr(w), L.ptr(tables_local),
                                                 L.dtype_code(tables_local.dtype), L.ptr(peers.ptr_array), peers.world,

@@ -94,7 +94,8 @@ def test_scatter_add_modes_match_oracle_partials(dev, case, mode):
 
 
 @pytest.mark.parametrize("case", CASES[:4], ids=[f"s{i}" for i in range(4)])
-def test_scatter_slab_mode_is_exact(dev, case):
+@pytest.mark.parametrize("bulk", [0, 0x40000000], ids=["stores16", "bulk_copy"])
+def test_scatter_slab_mode_is_exact(dev, case, bulk):
     from lookupffn_b200 import _lib as L
 
     N, I, S, d, n_owners, bf16 = case
@@ -104,7 +105,7 @@ def test_scatter_slab_mode_is_exact(dev, case):
     bufs = [torch.full((n_owners, rows, d), float("nan"), device=dev) for _ in range(n_owners)]
     ptr_array = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
     for r, (idx, w, tb, _) in enumerate(ranks):
-        _scatter_call(L, _to_dev(idx, dev), _to_dev(w, dev), _to_dev(tb, dev, bf16), ptr_array, n_owners, rows, r,
+        _scatter_call(L, _to_dev(idx, dev), _to_dev(w, dev), _to_dev(tb, dev, bf16), ptr_array, n_owners, rows, r | bulk,
                       (r + 1) % n_owners, N, dev)
     torch.cuda.synchronize()
     for r, (idx, w, _, t32) in enumerate(ranks):
