@@ -104,5 +104,10 @@ def test_random_shapes_against_oracle(seed):
         check("hash idx", np.array_equal(t2n(idx), idx_ref[:, tb_ * m:(tb_ + tc_) * m] - tb_ * (1 << k)), info)
         wr = w_ref[:, tb_ * m:(tb_ + tc_) * m]
         check("hash w", np.abs(t2n(wg) - wr).max() <= 1e-5 * max(np.abs(wr).max(), 1e-20), info)
+        # the same request without z takes other kernels (codes straight from registers, mix folded into the code
+        # step): same codes, same weights
+        idx2, wg2, _ = ops.hash_fwd(xt, desc, t_begin=tb_, t_count=tc_)
+        check("hash idx (no z)", np.array_equal(t2n(idx2), t2n(idx)), info)
+        check("hash w (no z)", np.abs(t2n(wg2) - wr).max() <= 1e-5 * max(np.abs(wr).max(), 1e-20), info)
     assert L.device_status(dev) == 0
     assert not failures, failures[:5]
