@@ -25,6 +25,59 @@ namespace lffn {
 __device__ __forceinline__ int tbuf_addr(int e) { return e + ((e >> 5) << 2); }
 __host__ __device__ constexpr int tbuf_words(int D) { return D + D / 8; }
 
+// Packed fp32 arithmetic (add / sub / mul / fma .rn.f32x2): one instruction carries two independent IEEE
+// round-to-nearest operations on an aligned register pair, so the results equal the scalar forms bit for bit while
+// the instruction count of an issue-bound kernel halves.  Values 2i and 2i+1 of a lane's array form the pairs.
+#ifndef LFFN_HASH_T_SCALAR
+#define LFFN_F32X2_OP(name, op)                                                                                         \
+    __device__ __forceinline__ void name(float &r0, float &r1, float a0, float a1, float b0, float b1) {               \
+        asm("{ .reg .b64 ra, rb, rc; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; " op " rc, ra, rb; mov.b64 {%0,%1}, rc; }" \
+            : "=f"(r0), "=f"(r1)                                                                                        \
+            : "f"(a0), "f"(a1), "f"(b0), "f"(b1));                                                                      \
+    }
+LFFN_F32X2_OP(add2, "add.rn.f32x2")
+LFFN_F32X2_OP(sub2, "sub.rn.f32x2")
+LFFN_F32X2_OP(mul2, "mul.rn.f32x2")
+#undef LFFN_F32X2_OP
+__device__ __forceinline__ void fma2(float &r0, float &r1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{ .reg .b64 ra, rb, rc, rd; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; mov.b64 rc, {%6,%7}; "
+        "fma.rn.f32x2 rd, ra, rb, rc; mov.b64 {%0,%1}, rd; }"
+        : "=f"(r0), "=f"(r1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+#else
+__device__ __forceinline__ void add2(float &r0, float &r1, float a0, float a1, float b0, float b1) { r0 = __fadd_rn(a0, b0); r1 = __fadd_rn(a1, b1); }
+__device__ __forceinline__ void sub2(float &r0, float &r1, float a0, float a1, float b0, float b1) { r0 = __fsub_rn(a0, b0); r1 = __fsub_rn(a1, b1); }
+__device__ __forceinline__ void mul2(float &r0, float &r1, float a0, float a1, float b0, float b1) { r0 = __fmul_rn(a0, b0); r1 = __fmul_rn(a1, b1); }
+__device__ __forceinline__ void fma2(float &r0, float &r1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    r0 = __fmaf_rn(a0, b0, c0);
+    r1 = __fmaf_rn(a1, b1, c1);
+}
+#endif
+
+// butterfly stages over the register index, strides V/2 down to 1: pairs of butterflies as packed operations while the
+// stride keeps both members of a register pair on the same side, scalar for the last stage
+template <int V>
+__device__ __forceinline__ void reg_butterflies(float (&v)[V]) {
+#pragma unroll
+    for (int s = V / 2; s >= 2; s >>= 1) {
+#pragma unroll
+        for (int j = 0; j < V; j += 2) {
+            if ((j & s) == 0) {
+                const float a0 = v[j], a1 = v[j + 1], b0 = v[j + s], b1 = v[j + s + 1];
+                add2(v[j], v[j + 1], a0, a1, b0, b1);
+                sub2(v[j + s], v[j + s + 1], a0, a1, b0, b1);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < V; j += 2) {
+        const float a = v[j], b = v[j + 1];
+        v[j] = __fadd_rn(a, b);
+        v[j + 1] = __fsub_rn(a, b);
+    }
+}
+
 template <int V>
 __device__ __forceinline__ void regs_to_layout_b(float (&v)[V], float *buf, int lane) {
 #pragma unroll
@@ -53,38 +106,18 @@ __device__ __forceinline__ void regs_to_layout_a(float (&v)[V], float *buf, int 
 // one transform: in layout A on entry, in layout B on exit
 template <int V>
 __device__ __forceinline__ void fwht_a_to_b(float (&v)[V], float *buf, int lane) {
-#pragma unroll
-    for (int s = V / 2; s >= 1; s >>= 1) {  // strides 32 s
-#pragma unroll
-        for (int j = 0; j < V; j++) {
-            if ((j & s) == 0) {
-                const float a = v[j], b = v[j + s];
-                v[j] = __fadd_rn(a, b);
-                v[j + s] = __fsub_rn(a, b);
-            }
-        }
-    }
+    reg_butterflies<V>(v);  // strides 32 s, s = V/2 .. 1
 #pragma unroll
     for (int s = 16; s >= V; s >>= 1) {  // strides 16 .. V (none for V = 32): lane pairs
         const float sg = (lane & s) ? -1.f : 1.f;
 #pragma unroll
-        for (int j = 0; j < V; j++) {
-            const float p = __shfl_xor_sync(FULL, v[j], s);
-            v[j] = __fmaf_rn(v[j], sg, p);  // lower lane: v + p, upper lane: p - v
+        for (int j = 0; j < V; j += 2) {
+            const float p0 = __shfl_xor_sync(FULL, v[j], s), p1 = __shfl_xor_sync(FULL, v[j + 1], s);
+            fma2(v[j], v[j + 1], v[j], v[j + 1], sg, sg, p0, p1);  // lower lane: v + p, upper lane: p - v
         }
     }
     regs_to_layout_b<V>(v, buf, lane);
-#pragma unroll
-    for (int s = V / 2; s >= 1; s >>= 1) {  // strides V/2 .. 1
-#pragma unroll
-        for (int c = 0; c < V; c++) {
-            if ((c & s) == 0) {
-                const float a = v[c], b = v[c + s];
-                v[c] = __fadd_rn(a, b);
-                v[c + s] = __fsub_rn(a, b);
-            }
-        }
-    }
+    reg_butterflies<V>(v);  // strides V/2 .. 1
 }
 
 // codes and weights of the table whose K coordinates are z[0..K) (registers); operation order = emit_table
@@ -177,32 +210,32 @@ __global__ void __launch_bounds__(HT_WARPS * 32, 4) hash_diag_t_kernel(HashArgs 
                 const float *ws = a.w + ((long long)r * a.S + s) * D;
                 if (s == 0) {
 #pragma unroll
-                    for (int j = 0; j < V; j++) v[j] = __fmul_rn(xr[j], __ldg(ws + j * 32 + lane));
+                    for (int j = 0; j < V; j += 2)
+                        mul2(v[j], v[j + 1], xr[j], xr[j + 1], __ldg(ws + j * 32 + lane), __ldg(ws + (j + 1) * 32 + lane));
                 } else {
                     regs_to_layout_a<V>(v, buf, lane);
 #pragma unroll
-                    for (int j = 0; j < V; j++) v[j] = __fmul_rn(v[j], __ldg(ws + j * 32 + lane));
+                    for (int j = 0; j < V; j += 2)
+                        mul2(v[j], v[j + 1], v[j], v[j + 1], __ldg(ws + j * 32 + lane), __ldg(ws + (j + 1) * 32 + lane));
                 }
                 fwht_a_to_b<V>(v, buf, lane);
                 if (a.had_scale != 1.f) {
 #pragma unroll
-                    for (int c = 0; c < V; c++) v[c] = __fmul_rn(v[c], a.had_scale);
+                    for (int c = 0; c < V; c += 2) mul2(v[c], v[c + 1], v[c], v[c + 1], a.had_scale, a.had_scale);
                 }
             }
             // layout B: v[c] is coordinate r * D + lane * V + c.  z = fl(mix_a * y) (+ 0) + bias
             if (a.mix_a != 1.f) {
 #pragma unroll
-                for (int c = 0; c < V; c++) v[c] = __fmul_rn(a.mix_a, v[c]);
+                for (int c = 0; c < V; c += 2) mul2(v[c], v[c + 1], a.mix_a, a.mix_a, v[c], v[c + 1]);
             }
             if (a.bias != nullptr) {
                 const float *sb = sbias + (r - a.r_lo) * tbuf_words(D);
 #pragma unroll
                 for (int q = 0; q < V / 4; q++) {
                     const float4 b = *reinterpret_cast<const float4 *>(sb + tbuf_addr(lane * V + 4 * q));
-                    v[4 * q] = __fadd_rn(v[4 * q], b.x);
-                    v[4 * q + 1] = __fadd_rn(v[4 * q + 1], b.y);
-                    v[4 * q + 2] = __fadd_rn(v[4 * q + 2], b.z);
-                    v[4 * q + 3] = __fadd_rn(v[4 * q + 3], b.w);
+                    add2(v[4 * q], v[4 * q + 1], v[4 * q], v[4 * q + 1], b.x, b.y);
+                    add2(v[4 * q + 2], v[4 * q + 3], v[4 * q + 2], v[4 * q + 3], b.z, b.w);
                 }
             }
             if constexpr (K == 0) {
