@@ -46,6 +46,7 @@ constexpr int HB_LN_FLOATS = 2 * HB_M;  // LayerNorm statistics (mean, 1/sigma) 
 
 template <int RADIX>
 __device__ __forceinline__ void radix_butterflies(float (&v)[RADIX]) {
+#ifdef LFFN_HB_SCALAR_BUTTERFLIES
 #pragma unroll
     for (int s = RADIX / 2; s >= 1; s >>= 1) {
 #pragma unroll
@@ -57,6 +58,9 @@ __device__ __forceinline__ void radix_butterflies(float (&v)[RADIX]) {
             }
         }
     }
+#else
+    reg_butterflies<RADIX>(v);  // two butterflies per packed instruction, same roundings
+#endif
 }
 
 // One pass of the transform over bits [lo, lo+nb) of the coordinate index, RADIX = 2^nb.
@@ -71,11 +75,12 @@ __device__ __forceinline__ void fwht_pass(float *Y, int D, int lo, float scale, 
         for (int q = 0; q < RADIX; q++) v[q] = Y[(base + (q << lo)) * HB_MP + lane];
         radix_butterflies<RADIX>(v);
 #pragma unroll
-        for (int q = 0; q < RADIX; q++) {
-            float o = v[q];
-            if (scale != 1.f) o = __fmul_rn(o, scale);
-            Y[(base + (q << lo)) * HB_MP + lane] = o;
+        if (scale != 1.f) {
+#pragma unroll
+            for (int q = 0; q < RADIX; q += 2) mul2(v[q], v[q + 1], v[q], v[q + 1], scale, scale);
         }
+#pragma unroll
+        for (int q = 0; q < RADIX; q++) Y[(base + (q << lo)) * HB_MP + lane] = v[q];
     }
 }
 
@@ -213,9 +218,43 @@ __device__ __forceinline__ void tile_end_rotation(float *Y, const float *carry, 
             };
             emit_table(get, k, a.bit_order, wm, a.tau, (int32_t)((t - a.t_begin) << k), false, 0, io, wo);
         };
+        // the common case (8-bit codes, mix folded in, input tile in shared memory): the table's coordinates go to
+        // registers two at a time with packed multiplies and adds, same roundings as `get` above
+        auto emit8 = [&](long long t, int wm, int32_t *io, float *wo) {
+            const int local0 = (int)(t * 8 - c_lo);
+            float z[8];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const int e = local0 + j;
+                // scalar multiplies: a packed product feeding a packed add would be contracted (see mul2)
+                const float p0 = __fmul_rn(a.mix_a, Y[e * HB_MP + lane]), p1 = __fmul_rn(a.mix_a, Y[(e + 1) * HB_MP + lane]);
+                const float q0 = __fmul_rn(a.mix_b, Xs[e * HB_MP + lane]), q1 = __fmul_rn(a.mix_b, Xs[(e + 1) * HB_MP + lane]);
+                add2(z[j], z[j + 1], p0, p1, q0, q1);
+                if (a.bias != nullptr) add2(z[j], z[j + 1], z[j], z[j + 1], __ldg(a.bias + c_lo + e), __ldg(a.bias + c_lo + e + 1));
+            }
+            emit_table_k<8>(z, a.bit_order, wm, a.tau, (int32_t)((t - a.t_begin) << 8), io, wo);
+        };
         const bool vec4 = m == 1 && (out_pitch & 3) == 0 && ((reinterpret_cast<uintptr_t>(a.idx_out) & 15u) == 0) &&
                           ((reinterpret_cast<uintptr_t>(a.w_out) & 15u) == 0);
-        if (vec4) {
+        if (vec4 && fused && k == 8 && Xs != nullptr) {
+            const int wm = a.weight_mode == LFFN_WEIGHT_ONES ? LFFN_WEIGHT_ONES : LFFN_WEIGHT_SCORE;
+            const long long q_first = (t_first - a.t_begin) >> 2, q_end = (t_end - a.t_begin + 3) >> 2;
+            for (long long q = q_first + warp; q < q_end; q += THREADS / 32) {
+                const long long tb = a.t_begin + q * 4;
+                const long long o = (n0 + lane) * out_pitch + q * 4;
+                if (tb >= t_first && tb + 4 <= t_end) {
+                    int32_t ci[4];
+                    float cw[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) emit8(tb + u, wm, ci + u, cw + u);
+                    *reinterpret_cast<int4 *>(a.idx_out + o) = make_int4(ci[0], ci[1], ci[2], ci[3]);
+                    *reinterpret_cast<float4 *>(a.w_out + o) = make_float4(cw[0], cw[1], cw[2], cw[3]);
+                } else {
+                    for (int u = 0; u < 4; u++)
+                        if (tb + u >= t_first && tb + u < t_end) emit8(tb + u, wm, a.idx_out + o + u, a.w_out + o + u);
+                }
+            }
+        } else if (vec4) {
             // m == 1 rules out the soft-flip mode: naming the two remaining modes lets the compiler drop that branch
             const int wm = a.weight_mode == LFFN_WEIGHT_ONES ? LFFN_WEIGHT_ONES : LFFN_WEIGHT_SCORE;
             // a warp takes four consecutive tables at a time and each lane (token) writes their codes and weights

@@ -25,59 +25,6 @@ namespace lffn {
 __device__ __forceinline__ int tbuf_addr(int e) { return e + ((e >> 5) << 2); }
 __host__ __device__ constexpr int tbuf_words(int D) { return D + D / 8; }
 
-// Packed fp32 arithmetic (add / sub / mul / fma .rn.f32x2): one instruction carries two independent IEEE
-// round-to-nearest operations on an aligned register pair, so the results equal the scalar forms bit for bit while
-// the instruction count of an issue-bound kernel halves.  Values 2i and 2i+1 of a lane's array form the pairs.
-#ifndef LFFN_HASH_T_SCALAR
-#define LFFN_F32X2_OP(name, op)                                                                                         \
-    __device__ __forceinline__ void name(float &r0, float &r1, float a0, float a1, float b0, float b1) {               \
-        asm("{ .reg .b64 ra, rb, rc; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; " op " rc, ra, rb; mov.b64 {%0,%1}, rc; }" \
-            : "=f"(r0), "=f"(r1)                                                                                        \
-            : "f"(a0), "f"(a1), "f"(b0), "f"(b1));                                                                      \
-    }
-LFFN_F32X2_OP(add2, "add.rn.f32x2")
-LFFN_F32X2_OP(sub2, "sub.rn.f32x2")
-LFFN_F32X2_OP(mul2, "mul.rn.f32x2")
-#undef LFFN_F32X2_OP
-__device__ __forceinline__ void fma2(float &r0, float &r1, float a0, float a1, float b0, float b1, float c0, float c1) {
-    asm("{ .reg .b64 ra, rb, rc, rd; mov.b64 ra, {%2,%3}; mov.b64 rb, {%4,%5}; mov.b64 rc, {%6,%7}; "
-        "fma.rn.f32x2 rd, ra, rb, rc; mov.b64 {%0,%1}, rd; }"
-        : "=f"(r0), "=f"(r1)
-        : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
-}
-#else
-__device__ __forceinline__ void add2(float &r0, float &r1, float a0, float a1, float b0, float b1) { r0 = __fadd_rn(a0, b0); r1 = __fadd_rn(a1, b1); }
-__device__ __forceinline__ void sub2(float &r0, float &r1, float a0, float a1, float b0, float b1) { r0 = __fsub_rn(a0, b0); r1 = __fsub_rn(a1, b1); }
-__device__ __forceinline__ void mul2(float &r0, float &r1, float a0, float a1, float b0, float b1) { r0 = __fmul_rn(a0, b0); r1 = __fmul_rn(a1, b1); }
-__device__ __forceinline__ void fma2(float &r0, float &r1, float a0, float a1, float b0, float b1, float c0, float c1) {
-    r0 = __fmaf_rn(a0, b0, c0);
-    r1 = __fmaf_rn(a1, b1, c1);
-}
-#endif
-
-// butterfly stages over the register index, strides V/2 down to 1: pairs of butterflies as packed operations while the
-// stride keeps both members of a register pair on the same side, scalar for the last stage
-template <int V>
-__device__ __forceinline__ void reg_butterflies(float (&v)[V]) {
-#pragma unroll
-    for (int s = V / 2; s >= 2; s >>= 1) {
-#pragma unroll
-        for (int j = 0; j < V; j += 2) {
-            if ((j & s) == 0) {
-                const float a0 = v[j], a1 = v[j + 1], b0 = v[j + s], b1 = v[j + s + 1];
-                add2(v[j], v[j + 1], a0, a1, b0, b1);
-                sub2(v[j + s], v[j + s + 1], a0, a1, b0, b1);
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < V; j += 2) {
-        const float a = v[j], b = v[j + 1];
-        v[j] = __fadd_rn(a, b);
-        v[j + 1] = __fsub_rn(a, b);
-    }
-}
-
 template <int V>
 __device__ __forceinline__ void regs_to_layout_b(float (&v)[V], float *buf, int lane) {
 #pragma unroll
@@ -118,46 +65,6 @@ __device__ __forceinline__ void fwht_a_to_b(float (&v)[V], float *buf, int lane)
     }
     regs_to_layout_b<V>(v, buf, lane);
     reg_butterflies<V>(v);  // strides V/2 .. 1
-}
-
-// codes and weights of the table whose K coordinates are z[0..K) (registers); operation order = emit_table
-template <int K>
-__device__ __forceinline__ void emit_table_k(const float *z, int bit_order, int weight_mode, float tau, int32_t offset,
-                                             int32_t *io, float *wo) {
-    int32_t code = 0;
-#pragma unroll
-    for (int j = 0; j < K; j++)
-        if (z[j] > 0.f) code |= 1 << j;
-    if (weight_mode == LFFN_WEIGHT_SCORE) {
-        float num = 0.f, den = 1.f;
-#pragma unroll
-        for (int j = 0; j < K; j++) {
-            const float a = fabsf(z[j]);
-            num = __fadd_rn(num, a);
-            den = __fmul_rn(den, __fadd_rn(1.f, exp_nonpos(__fmul_rn(-2.f, a))));
-        }
-        if (bit_order == LFFN_BIT_MSB_FIRST) code = (int32_t)(__brev((unsigned)code) >> (32 - K));
-        io[0] = code + offset;
-        wo[0] = __fdiv_rn(num, den);
-    } else if (weight_mode == LFFN_WEIGHT_ONES) {
-        if (bit_order == LFFN_BIT_MSB_FIRST) code = (int32_t)(__brev((unsigned)code) >> (32 - K));
-        io[0] = code + offset;
-        wo[0] = 1.f;
-    } else {
-        float s[K];
-#pragma unroll
-        for (int j = 0; j < K; j++) s[j] = __fdiv_rn(1.f, __fadd_rn(1.f, exp_nonpos(__fdiv_rn(-fabsf(z[j]), tau))));
-#pragma unroll
-        for (int c = 0; c <= K; c++) {
-            float p = 1.f;
-#pragma unroll
-            for (int j = 0; j < K; j++) p = __fmul_rn(p, (c == j + 1) ? __fsub_rn(1.f, s[j]) : s[j]);
-            int32_t cc = c == 0 ? code : (code ^ (1 << (c - 1)));
-            if (bit_order == LFFN_BIT_MSB_FIRST) cc = (int32_t)(__brev((unsigned)cc) >> (32 - K));
-            io[c] = cc + offset;
-            wo[c] = p;
-        }
-    }
 }
 
 constexpr int HT_WARPS = 4;
@@ -208,26 +115,30 @@ __global__ void __launch_bounds__(HT_WARPS * 32, 4) hash_diag_t_kernel(HashArgs 
             float v[V];
             for (int s = 0; s < a.S; s++) {
                 const float *ws = a.w + ((long long)r * a.S + s) * D;
+                // the products below feed the butterflies' adds: scalar multiplies (see the rule beside mul2)
                 if (s == 0) {
 #pragma unroll
-                    for (int j = 0; j < V; j += 2)
-                        mul2(v[j], v[j + 1], xr[j], xr[j + 1], __ldg(ws + j * 32 + lane), __ldg(ws + (j + 1) * 32 + lane));
+                    for (int j = 0; j < V; j++) v[j] = __fmul_rn(xr[j], __ldg(ws + j * 32 + lane));
                 } else {
                     regs_to_layout_a<V>(v, buf, lane);
 #pragma unroll
-                    for (int j = 0; j < V; j += 2)
-                        mul2(v[j], v[j + 1], v[j], v[j + 1], __ldg(ws + j * 32 + lane), __ldg(ws + (j + 1) * 32 + lane));
+                    for (int j = 0; j < V; j++) v[j] = __fmul_rn(v[j], __ldg(ws + j * 32 + lane));
                 }
                 fwht_a_to_b<V>(v, buf, lane);
                 if (a.had_scale != 1.f) {
+                    if (s + 1 < a.S) {  // followed by the next diagonal's multiply: packed
 #pragma unroll
-                    for (int c = 0; c < V; c += 2) mul2(v[c], v[c + 1], v[c], v[c + 1], a.had_scale, a.had_scale);
+                        for (int c = 0; c < V; c += 2) mul2(v[c], v[c + 1], v[c], v[c + 1], a.had_scale, a.had_scale);
+                    } else {            // followed by the bias add: scalar
+#pragma unroll
+                        for (int c = 0; c < V; c++) v[c] = __fmul_rn(v[c], a.had_scale);
+                    }
                 }
             }
             // layout B: v[c] is coordinate r * D + lane * V + c.  z = fl(mix_a * y) (+ 0) + bias
             if (a.mix_a != 1.f) {
 #pragma unroll
-                for (int c = 0; c < V; c += 2) mul2(v[c], v[c + 1], a.mix_a, a.mix_a, v[c], v[c + 1]);
+                for (int c = 0; c < V; c++) v[c] = __fmul_rn(a.mix_a, v[c]);
             }
             if (a.bias != nullptr) {
                 const float *sb = sbias + (r - a.r_lo) * tbuf_words(D);

@@ -170,6 +170,33 @@ def test_hash_block64_without_z_matches_oracle(dev, case):
     assert _lib.device_status(dev) & _lib.STATUS_TIMEOUT == 0
 
 
+@pytest.mark.parametrize("D,k,mix_a", [(256, 4, 1.0), (512, 8, 1.0), (1024, 8, 0.7), (1024, 6, 1.0), (512, 16, 0.9)])
+def test_hash_diagonal_with_general_weights(dev, D, k, mix_a):
+    """A diagonal projection whose entries are arbitrary floats, not signs, with a scale that is no power of two and
+    a bias: every product is rounded before it is added (no contraction into a fused multiply-add anywhere), so z
+    and the codes equal the oracle bit for bit, with z (vector layout) and without (transposing layout)."""
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(D + k)
+    N, d_in, T = 300, D - 3, (2 * D) // k
+    R = max(1, -(-T * k // D))
+    w = rng.randn(R, 2, D, 1, 1).astype(np.float32)
+    bias = (0.05 * rng.randn(T * k)).astype(np.float32)
+    x = rng.randn(N, d_in).astype(np.float32)
+    hs = float(np.float32(1.0 / np.sqrt(D) * 0.9))
+    z_ref = O.project(x, w, T * k, had_scale=hs, mix_a=mix_a, mix_b=0.0, bias=bias)
+    idx_ref, w_ref = O.code_weights(z_ref, T, k)
+    desc = ops.make_hash_desc(d_in, torch.from_numpy(w).to(dev), torch.from_numpy(bias).to(dev), T, k, had_scale=hs,
+                              mix_a=mix_a, mix_b=0.0)
+    xd = torch.from_numpy(x).to(dev)
+    idx, wgt, _ = ops.hash_fwd(xd, desc)
+    np.testing.assert_array_equal(t2n(idx), idx_ref)
+    assert rel_err(t2n(wgt), w_ref) < 1e-5
+    idx2, wgt2, z = ops.hash_fwd(xd, desc, want_z=True)
+    np.testing.assert_array_equal(t2n(z), z_ref)
+    np.testing.assert_array_equal(t2n(idx2), idx_ref)
+
+
 def test_hash_bf16_input(dev):
     from lookupffn_b200 import ops
 
