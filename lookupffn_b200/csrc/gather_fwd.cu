@@ -216,60 +216,60 @@ __global__ void __launch_bounds__(LFFN_GATHER_THREADS, LFFN_GATHER_MINBLOCKS) ga
                                      : "memory");
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
-                continue;
+            } else {
+#pragma unroll
+                for (int v = 0; v < VPL; v++) {
+                    const int c = lane + 32 * v;
+                    if (c < nvec) {
+#pragma unroll
+                        for (int q = 0; q < EPV / 4; q++) {
+                            if constexpr (SMODE == 2)
+                                red_add_v4_f32(prow + c * EPV + 4 * q, acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2],
+                                               acc[v][4 * q + 3]);
+                            else
+                                *reinterpret_cast<float4 *>(prow + c * EPV + 4 * q) =
+                                    make_float4(acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2], acc[v][4 * q + 3]);
+                        }
+                    }
+                }
             }
+        } else {
+            // epilogue: + bias (one rounded add, as `outputs + self.bias`), + residual, convert, 16-byte stores
+            OutT *orow = out + n * d + (long long)col0 * EPV;
 #pragma unroll
             for (int v = 0; v < VPL; v++) {
                 const int c = lane + 32 * v;
                 if (c < nvec) {
+                    if (bias != nullptr && finish) {
 #pragma unroll
-                    for (int q = 0; q < EPV / 4; q++) {
-                        if constexpr (SMODE == 2)
-                            red_add_v4_f32(prow + c * EPV + 4 * q, acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2],
-                                           acc[v][4 * q + 3]);
-                        else
-                            *reinterpret_cast<float4 *>(prow + c * EPV + 4 * q) =
-                                make_float4(acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2], acc[v][4 * q + 3]);
+                        for (int e = 0; e < EPV; e++)
+                            acc[v][e] = __fadd_rn(acc[v][e], __ldg(bias + (long long)(col0 + c) * EPV + e));
                     }
-                }
-            }
-            continue;
-        }
-        // epilogue: + bias (one rounded add, as `outputs + self.bias`), + residual, convert, 16-byte stores
-        OutT *orow = out + n * d + (long long)col0 * EPV;
+                    if (residual != nullptr && finish) {
+                        const OutT *rrow = residual + n * d + (long long)(col0 + c) * EPV;
 #pragma unroll
-        for (int v = 0; v < VPL; v++) {
-            const int c = lane + 32 * v;
-            if (c < nvec) {
-                if (bias != nullptr && finish) {
-#pragma unroll
-                    for (int e = 0; e < EPV; e++)
-                        acc[v][e] = __fadd_rn(acc[v][e], __ldg(bias + (long long)(col0 + c) * EPV + e));
-                }
-                if (residual != nullptr && finish) {
-                    const OutT *rrow = residual + n * d + (long long)(col0 + c) * EPV;
-#pragma unroll
-                    for (int e = 0; e < EPV; e++) acc[v][e] = __fadd_rn(acc[v][e], Elem<OutT>::load1(rrow + e));
-                }
-                if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-                    for (int q = 0; q < EPV / 4; q++) {
-                        float4 o = make_float4(acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2], acc[v][4 * q + 3]);
-                        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(orow) + c * EPV + 4 * q) = o;
+                        for (int e = 0; e < EPV; e++) acc[v][e] = __fadd_rn(acc[v][e], Elem<OutT>::load1(rrow + e));
                     }
-                } else {
-                    if constexpr (EPV == 8) {
-                        uint4 o;
-                        o.x = pack_bf16(acc[v][0], acc[v][1]);
-                        o.y = pack_bf16(acc[v][2], acc[v][3]);
-                        o.z = pack_bf16(acc[v][4], acc[v][5]);
-                        o.w = pack_bf16(acc[v][6], acc[v][7]);
-                        *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(orow) + c * 8) = o;
+                    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+                        for (int q = 0; q < EPV / 4; q++) {
+                            float4 o = make_float4(acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2], acc[v][4 * q + 3]);
+                            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(orow) + c * EPV + 4 * q) = o;
+                        }
                     } else {
-                        uint2 o;
-                        o.x = pack_bf16(acc[v][0], acc[v][1]);
-                        o.y = pack_bf16(acc[v][2], acc[v][3]);
-                        *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(orow) + c * 4) = o;
+                        if constexpr (EPV == 8) {
+                            uint4 o;
+                            o.x = pack_bf16(acc[v][0], acc[v][1]);
+                            o.y = pack_bf16(acc[v][2], acc[v][3]);
+                            o.z = pack_bf16(acc[v][4], acc[v][5]);
+                            o.w = pack_bf16(acc[v][6], acc[v][7]);
+                            *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(orow) + c * 8) = o;
+                        } else {
+                            uint2 o;
+                            o.x = pack_bf16(acc[v][0], acc[v][1]);
+                            o.y = pack_bf16(acc[v][2], acc[v][3]);
+                            *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(orow) + c * 4) = o;
+                        }
                     }
                 }
             }

@@ -74,7 +74,6 @@ __device__ __forceinline__ void fwht_pass(float *Y, int D, int lo, float scale, 
 #pragma unroll
         for (int q = 0; q < RADIX; q++) v[q] = Y[(base + (q << lo)) * HB_MP + lane];
         radix_butterflies<RADIX>(v);
-#pragma unroll
         if (scale != 1.f) {
 #pragma unroll
             for (int q = 0; q < RADIX; q += 2) mul2(v[q], v[q + 1], v[q], v[q + 1], scale, scale);

@@ -259,7 +259,6 @@ static bool try_launch_hash_t(const HashArgs &a, cudaStream_t st, int *rc) {
 #endif
     if (a.z_out != nullptr || a.idx_out == nullptr || a.mix_b != 0.f) return false;
     if (a.D != 256 && a.D != 512 && a.D != 1024) return false;
-    const int V = a.D / 32;
     if (a.k < 1 || a.k > 16) return false;
     const size_t nrot = (size_t)(a.r_hi - a.r_lo + 1);
     const size_t smem = ((size_t)HT_WARPS * (tbuf_words(a.D) + HT_CARRY) + (a.bias != nullptr ? nrot : 0) * tbuf_words(a.D)) * sizeof(float);
