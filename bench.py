@@ -479,7 +479,9 @@ def table_sharded_setup(w, rank, world, device):
 def table_sharded_step_fn(S, rs, chunk, world, device):
     """One step of the table-sharded forward with exchange `rs`: "nccl" (chunked NCCL reduce-scatter), "fused" (one
     bulk reduction per row from the gather kernel into the owner's buffer over NVLink), "fused-store" (one bulk copy
-    per row into the rank's slab of the owner's buffer, the owner sums its slabs in rank order), or "none" (no exchange: the rank's partial sums stay local -- the one-GPU pace of the same shape)."""
+    per row into the rank's slab of the owner's buffer, the owner sums its slabs in rank order), "copy" (the gather
+    writes locally, one owner's rows at a time, and copy-engine transfers move them into the owners' slabs while the
+    next rows are gathered), or "none" (no exchange: the rank's partial sums stay local -- the one-GPU pace of the same shape)."""
     from lookupffn_b200 import ops, sharded
 
     x, tables, bias, desc = S["x"], S["tables"], S["bias"], S["desc"]
@@ -494,9 +496,10 @@ def table_sharded_step_fn(S, rs, chunk, world, device):
                                                         chunk_tokens=chunk, out_dtype=torch.float32)[0]
         return step, None
     peers = sharded.PeerOutput(x.shape[0] // world, tables.shape[1], device, mode="add" if rs == "fused" else "store")
+    fn = sharded.lookup_forward_table_sharded_copy if rs == "copy" else sharded.lookup_forward_table_sharded_fused
 
     def step():
-        return sharded.lookup_forward_table_sharded_fused(x, desc, tables, S["t_begin"], S["t_count"], peers, bias=bias)
+        return fn(x, desc, tables, S["t_begin"], S["t_count"], peers, bias=bias)
     return step, peers
 
 
@@ -540,8 +543,8 @@ def table_sharded_record(args, rank, world, local):
                "reduce_scattered_bytes_per_gpu": N * d_out * 4,
                "bytes_leaving_each_gpu_over_nvlink": N * d_out * 4 * (world - 1) // world}
         keys = {"none": "one_gpu_pace_no_exchange", "nccl": "nccl_reduce_scatter", "fused": "fused_in_gather_kernel",
-                "fused-store": "fused_in_gather_kernel_slabs"}
-        for rs in ("none", "nccl", "fused", "fused-store"):
+                "fused-store": "fused_in_gather_kernel_slabs", "copy": "copy_engine_slabs"}
+        for rs in ("none", "nccl", "fused", "fused-store", "copy"):
             step, peers = table_sharded_step_fn(S, rs, args.rs_chunk, world, device)
             ms, _ = time_steps(step, steps, warmup, device, world)
             run[keys[rs]] = {"ms_per_step": ms, "tokens_per_s": N / (ms * 1e-3)}
@@ -1244,7 +1247,7 @@ def main():
                     help="tokens: each rank its own tokens, tables replicated (default); tables: tables split by T, "
                          "partial sums reduce-scattered")
     ap.add_argument("--rs-chunk", type=int, default=32768, help="tokens per reduce-scatter chunk (--shard tables)")
-    ap.add_argument("--rs", default="nccl", choices=["nccl", "fused", "fused-store"],
+    ap.add_argument("--rs", default="nccl", choices=["nccl", "fused", "fused-store", "copy"],
                     help="--shard tables: combine partial sums with NCCL reduce-scatter, or inside the gather kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--table-sharded-ks", default="",

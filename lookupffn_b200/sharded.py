@@ -107,10 +107,10 @@ class TableShardedLookupFFN(nn.Module):
 
     def __init__(self, full, group=None, chunk_tokens=32768, exchange="auto"):
         """exchange: "nccl" (chunked reduce-scatter), "fused" (one bulk reduction per row from the gather kernel into
-        the owner's buffer) or "auto": fused whenever the tokens divide evenly over the ranks and this rank gathers
-        at least 16 rows per token.  The two exchanges measure within a few percent of each other (262,144 tokens,
-        256 tables per rank, fused vs NCCL: 11.5 vs 11.7 ms on 2 GPUs, 12.4 vs 12.0 ms on 8); the fused one needs no
-        [tokens, d] buffer of partial sums in local memory."""
+        the owner's buffer), "copy" (copy-engine transfers into per-rank slabs, summed in rank order) or "auto": when
+        the tokens divide evenly over the ranks, copy (262,144 tokens, 256 tables per rank: 10.3 ms against 12.4
+        fused and 12.0 NCCL on 8 GPUs, 10.4 / 11.3 / 11.6 on 2), except short gathers on 2 ranks, where fused leads
+        (16 tables per rank: 2.6 ms against 2.9 copy and 3.3 NCCL); NCCL otherwise."""
         super().__init__()
         self.group = group
         self.chunk_tokens = chunk_tokens
@@ -135,8 +135,17 @@ class TableShardedLookupFFN(nn.Module):
         N = u.shape[0]
         flat = self.tables.reshape(self.t_count * self.table_size, self.output_size)
         world = dist.get_world_size(self.group)
+        rows_per_token = self.t_count * self.hash.candidates
+        if self.exchange == "copy" or (self.exchange == "auto" and world > 1 and N % world == 0
+                                       and (rows_per_token >= 128 or world >= 4)):
+            if self._peers is None or self._peers.rows != N // world or self._peers.mode != "store":
+                self._peers = PeerOutput(N // world, self.output_size, u.device, group=self.group, mode="store")
+            rank = dist.get_rank(self.group)
+            y = _copy_exchange(lambda lo, hi: self.hash(u[lo:hi], t_begin=self.t_begin, t_count=self.t_count), N, u.device,
+                               flat, self._peers, self.bias)
+            return y, torch.arange(rank * self._peers.rows, (rank + 1) * self._peers.rows)
         fused = self.exchange == "fused" or (self.exchange == "auto" and world > 1 and N % world == 0
-                                             and self.t_count * self.hash.candidates >= 16)
+                                             and rows_per_token >= 16)
         if fused:
             if self._peers is None or self._peers.rows != N // world:
                 self._peers = PeerOutput(N // world, self.output_size, u.device, group=self.group)
@@ -216,11 +225,11 @@ class ShardedTableAdamW:
 class PeerOutput:
     """Output buffers of all ranks, each mapped into every process (torch symmetric memory: CUDA peer mappings
     over NVLink), plus the device array of their addresses that lffn_gather_fwd_scatter takes.
-    mode "add" (default): every rank owns [N/world, d] fp32 and partial rows are added in place with vector
-    reductions (as fast as the NCCL path; summation order across ranks not fixed).
-    mode "store": every rank owns a staging buffer [world, N/world, d] fp32; rank r stores its partial rows into
-    slab r of the owner's buffer and the owner sums the slabs in rank order (deterministic, but measured about
-    twice slower: fine-grained peer stores).
+    mode "add" (default): every rank owns [N/world, d] fp32 and partial rows are added in place, one bulk
+    reduction per row (summation order across ranks not fixed).
+    mode "store": every rank owns a staging buffer [world, N/world, d] fp32; rank r's partial rows go into slab r
+    of the owner's buffer (one bulk copy per row from the gather kernel, or one copy-engine transfer per owner in
+    lookup_forward_table_sharded_copy) and the owner sums the slabs in rank order (deterministic).
     Allocate once and reuse across steps."""
 
     def __init__(self, rows_per_rank, d, device, group=None, mode="add"):
@@ -237,6 +246,7 @@ class PeerOutput:
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.ptr_array = torch.tensor(ptrs, dtype=torch.int64, device=device)
         self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+        self._copy = None  # lookup_forward_table_sharded_copy: (stream, two staging buffers, their events, peer views)
 
     def _rank_barrier(self):
         """Orders the ranks on the device, without stopping the host: a one-element all-reduce enqueued on every
@@ -263,6 +273,66 @@ class PeerOutput:
         if bias is not None:
             out += bias.to(out.dtype)
         return out
+
+
+def lookup_forward_table_sharded_copy(x, desc, tables_local, t_begin, t_count, peers, bias=None):
+    """The table-sharded forward with the exchange done by the copy engines: the rank gathers the partial rows of
+    one owner at a time into a local staging buffer and a peer-to-peer copy on a second stream moves them into its
+    slab of that owner's buffer while the next owner's rows are gathered; the rank's own rows come last and go
+    straight into its own slab, so no copy is left exposed at the end.  The owner then sums its slabs in rank order
+    (deterministic).  No SM issues a remote store: sending rows from the gather kernel itself slows that kernel by
+    1.2-2.5 ms per GiB sent (2 GPUs, one direction, 256 tables per rank), more than the transfer takes.
+    `peers` is a PeerOutput(mode="store").  Returns this rank's [N/world, d] fp32 rows."""
+    def hash_rows(lo, hi):
+        idx, w, _ = ops.hash_fwd(x[lo:hi], desc, t_begin=t_begin, t_count=t_count)
+        return idx, w
+
+    return _copy_exchange(hash_rows, x.shape[0], x.device, tables_local, peers, bias)
+
+
+def _copy_exchange(hash_rows, N, dev, tables_local, peers, bias):
+    """hash_rows(lo, hi) -> (idx, w) of tokens [lo, hi) for this rank's tables; see lookup_forward_table_sharded_copy."""
+    from . import _lib as L
+
+    if peers.mode != "store":
+        raise ValueError("the copy-engine exchange needs PeerOutput(mode='store')")
+    world, rank, rows = peers.world, peers.rank, peers.rows
+    if N != rows * world:
+        raise ValueError(f"N = {N} tokens but the peer buffers hold {rows} x {world} rows")
+    tables_local = tables_local if tables_local.is_contiguous() else tables_local.contiguous()
+    S, d = tables_local.shape
+    if peers._copy is None:
+        shape = (world, rows, d)
+        peers._copy = (torch.cuda.Stream(device=dev), [torch.empty((rows, d), dtype=torch.float32, device=dev) for _ in range(2)],
+                       [None, None], [peers.handle.get_buffer(o, shape, torch.float32) for o in range(world)])
+    cstream, stage, stage_free, views = peers._copy
+    bias32 = None if bias is None else bias.to(torch.float32).contiguous()
+    main = torch.cuda.current_stream(dev)
+    peers.reset()  # every owner has finished reading its slabs of the previous step
+    for c in range(world):
+        o = (rank + 1 + c) % world  # the rank's own rows last
+        idx, w = hash_rows(o * rows, (o + 1) * rows)
+        if o == rank:
+            dst = peers.local[rank]
+        else:
+            dst = stage[c & 1]
+            if stage_free[c & 1] is not None:
+                main.wait_event(stage_free[c & 1])  # the copy that last read this staging buffer has finished
+        with torch.cuda.device(dev):
+            L.check(L.lib().lffn_gather_fwd(L.ptr(idx), L.ptr(w), L.ptr(tables_local), L.dtype_code(tables_local.dtype),
+                                            L.ptr(dst), L.dtype_code(torch.float32), rows, idx.shape[1], S, d,
+                                            L.ptr(bias32) if o == rank else None, L.stream_ptr(dev)))
+        if o != rank:
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(cstream):
+                cstream.wait_event(ready)
+                views[o][rank].copy_(dst, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(cstream)
+            stage_free[c & 1] = done
+    main.wait_stream(cstream)  # this rank's copies have landed before it enters the barrier of finish()
+    return peers.finish()      # the bias went into the rank's own slab with the gather's epilogue
 
 
 def lookup_forward_table_sharded_fused(x, desc, tables_local, t_begin, t_count, peers, bias=None):

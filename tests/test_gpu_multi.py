@@ -87,10 +87,11 @@ def _fused_worker(rank, world, port, q):
         errs = []
         local = tables[tb << k:(tb + tc) << k].contiguous()
         lo = rank * (N // world)
-        for mode in ("store", "add"):
-            peers = sharded.PeerOutput(N // world, d_out, dev, mode=mode)
-            for _ in range(2):  # twice: the buffers are reused
-                y_loc = sharded.lookup_forward_table_sharded_fused(x, desc, local, tb, tc, peers, bias=bias)
+        for mode in ("store", "add", "copy"):
+            peers = sharded.PeerOutput(N // world, d_out, dev, mode="store" if mode == "copy" else mode)
+            fn = sharded.lookup_forward_table_sharded_copy if mode == "copy" else sharded.lookup_forward_table_sharded_fused
+            for _ in range(3):  # repeatedly: the buffers are reused
+                y_loc = fn(x, desc, local, tb, tc, peers, bias=bias)
                 errs.append(float((y_loc - y_full[lo:lo + N // world]).abs().max() / y_full.abs().max()))
         q.put((rank, max(errs), tuple(y_loc.shape)))
     finally:
@@ -140,7 +141,7 @@ def _module_worker(rank, world, port, q):
         with torch.no_grad():
             y_full = full(x)
         errs = {}
-        for mode in ("nccl", "fused", "auto"):
+        for mode in ("nccl", "fused", "copy", "auto"):
             mod = sharded.TableShardedLookupFFN(full, chunk_tokens=512, exchange=mode)
             y_loc, owned = mod(x)
             errs[mode] = float((y_loc - y_full[owned.to(dev)]).abs().max() / y_full.abs().max())
