@@ -211,6 +211,16 @@ int lffn_proj_bwd(const lffn_hash_desc *desc, const float *proj_w_oi, const void
                   size_t ws_bytes, lffn_stream_t stream);
 
 /*
+ * Backward of the layer's LayerNorm (lookup.py:84,99: torch.nn.LayerNorm over the hidden dimension; in the reference
+ * autograd's native_layer_norm_backward): x, du, dx fp32 [N, d]; gamma, dgamma, dbeta fp32 [d]; d in {256, 512, 768,
+ * 1024}.  The statistics are recomputed from x.  Deterministic (partial column sums added in a fixed order).
+ * ws: lffn_layernorm_bwd_ws_bytes(d) bytes of device scratch.
+ */
+size_t lffn_layernorm_bwd_ws_bytes(int32_t d);
+int lffn_layernorm_bwd(const float *x, const float *du, const float *gamma, int64_t N, int32_t d, float eps, float *dx,
+                       float *dgamma, float *dbeta, void *ws, size_t ws_bytes, lffn_stream_t stream);
+
+/*
  * out[n, :] = sum_i w[n, i] * tables[idx[n, i], :] (+ bias): replaces
  * gather_add.weighted_vector_gather_add_fp32/_fp16 (gather/cuda/extension/torch_extension.cpp:6-33,
  * gather/cuda/kernel.py:22-70) and gather_add_cpu.weighted_vector_gather_add_* (gather/cpu/

@@ -209,7 +209,7 @@ class LookupFFN(nn.Module):
             T, rows, d = self.tables.shape
             return ops.weighted_vector_gather_add(code, self.tables.reshape(T * rows, d), score, bias=self.bias,
                                                   residual=residual)
-        hidden_states = self.LayerNorm(hidden_states)
+        hidden_states = ops.layer_norm(hidden_states, self.LayerNorm)
         code, score = self.hash(hidden_states)
         outputs = self.gather(code, score, self.tables)
         return outputs if residual is None else outputs + residual.reshape(outputs.shape).to(outputs.dtype)

@@ -230,6 +230,55 @@ def proj_bwd(x, weight, kernel_weight, out_dim, dz, had_scale, mix_a, mix_b, nee
     return du, dw, dbias
 
 
+LAYERNORM_BWD_SIZES = (256, 512, 768, 1024)
+
+
+def layernorm_bwd(x, du, gamma, eps):
+    """Gradients of u = LayerNorm(x) * gamma + beta (torch.nn.LayerNorm over the last dimension) through
+    lffn_layernorm_bwd: returns (dx [N, d], dgamma [d], dbeta [d]), fp32, deterministic."""
+    L.require_cuda(x, du, gamma)
+    d = x.shape[-1]
+    x2, du2 = _contig(x.reshape(-1, d).float()), _contig(du.reshape(-1, d).float())
+    g = _contig(gamma.detach().float())
+    N, dev = x2.shape[0], x2.device
+    dx = torch.empty_like(x2)
+    dgamma = torch.empty(d, dtype=torch.float32, device=dev)
+    dbeta = torch.empty(d, dtype=torch.float32, device=dev)
+    lib = L.lib()
+    nbytes = lib.lffn_layernorm_bwd_ws_bytes(d)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        L.check(lib.lffn_layernorm_bwd(L.ptr(x2), L.ptr(du2), L.ptr(g), N, d, float(eps), L.ptr(dx), L.ptr(dgamma),
+                                       L.ptr(dbeta), L.ptr(ws), nbytes, L.stream_ptr(dev)))
+    return dx.reshape(x.shape), dgamma, dbeta
+
+
+class LayerNormFn(torch.autograd.Function):
+    """The layer's LayerNorm for training: torch's forward kernel, this library's backward (lffn_layernorm_bwd), which
+    recomputes the row statistics from x instead of keeping them."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        ctx.save_for_backward(x, weight)
+        ctx.eps = eps
+        return torch.nn.functional.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+
+    @staticmethod
+    def backward(ctx, du):
+        x, weight = ctx.saved_tensors
+        dx, dgamma, dbeta = layernorm_bwd(x, du, weight, ctx.eps)
+        return dx.to(x.dtype), dgamma.to(weight.dtype), dbeta.to(weight.dtype), None
+
+
+def layer_norm(x, ln):
+    """ln(x) for an nn.LayerNorm `ln`; with this library's backward kernel when x is an fp32 CUDA tensor of a covered
+    width and gradients are being recorded, torch's module otherwise."""
+    if (torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.float32 and ln.elementwise_affine and ln.bias is not None
+            and x.shape[-1] in LAYERNORM_BWD_SIZES and (x.requires_grad or ln.weight.requires_grad)):
+        return LayerNormFn.apply(x, ln.weight, ln.bias, ln.eps)
+    return ln(x)
+
+
 class Projection(torch.autograd.Function):
     """z = BH4(x): forward by the fused hash kernel (projection only).  Backward for the reference's shape (64 x 64
     blocks, D a multiple of 256) is lffn_proj_bwd: the stage inputs are recomputed and the chain walked in reverse by

@@ -119,3 +119,48 @@ def test_projection_autograd_function_uses_the_kernels(dev):
     x3 = x.detach().clone().requires_grad_(True)
     ops.Projection.apply(x3, mod.weight, mod.bias, mod.had_scale, mod.mix[0], mod.mix[1], wk, tw).backward(dz)
     assert torch.equal(x3.grad, x.grad)
+
+
+@pytest.mark.parametrize("d", [256, 512, 768, 1024])
+def test_layernorm_backward_matches_fp64_autograd(d):
+    """lffn_layernorm_bwd against torch autograd in fp64 (1e-5 of each gradient's largest value), on a ragged row
+    count, and bit-identical when run twice (fixed summation order)."""
+    from lookupffn_b200 import ops
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(d)
+    N = 4099
+    x = torch.randn(N, d, generator=g, device=dev) * 1.7 + 0.3
+    du = torch.randn(N, d, generator=g, device=dev)
+    gamma = torch.rand(d, generator=g, device=dev) + 0.5
+    beta = torch.randn(d, generator=g, device=dev)
+    x64 = x.double().requires_grad_(True)
+    g64, b64 = gamma.double().requires_grad_(True), beta.double().requires_grad_(True)
+    torch.nn.functional.layer_norm(x64, (d,), g64, b64, 1e-5).backward(du.double())
+    dx, dgamma, dbeta = ops.layernorm_bwd(x, du, gamma, 1e-5)
+    for got, want in ((dx, x64.grad), (dgamma, g64.grad), (dbeta, b64.grad)):
+        assert float((got.double() - want).abs().max() / want.abs().max()) < 1e-5
+    dx2, dgamma2, dbeta2 = ops.layernorm_bwd(x, du, gamma, 1e-5)
+    assert torch.equal(dx, dx2) and torch.equal(dgamma, dgamma2) and torch.equal(dbeta, dbeta2)
+
+
+def test_layer_norm_function_routes_training_through_the_kernel():
+    from lookupffn_b200 import ops
+
+    dev = torch.device("cuda:0")
+    ln = torch.nn.LayerNorm(512, eps=1e-5).to(dev)
+    with torch.no_grad():
+        ln.weight.uniform_(0.5, 1.5)
+        ln.bias.normal_()
+    x = torch.randn(3, 77, 512, device=dev, requires_grad=True)
+    y = ops.layer_norm(x, ln)
+    assert y.grad_fn is not None and "LayerNormFn" in type(y.grad_fn).__name__
+    y.square().sum().backward()
+    got = (x.grad.clone(), ln.weight.grad.clone(), ln.bias.grad.clone())
+    x.grad = None
+    ln.zero_grad()
+    ln(x).square().sum().backward()
+    for a, b in zip(got, (x.grad, ln.weight.grad, ln.bias.grad)):
+        assert float((a - b).abs().max() / b.abs().max()) < 1e-5
+    with torch.no_grad():
+        assert ops.layer_norm(x, ln).grad_fn is None  # inference: torch's module
