@@ -217,6 +217,10 @@ int lffn_proj_bwd(const lffn_hash_desc *desc, const float *proj_w_oi, const void
  * ws: lffn_layernorm_bwd_ws_bytes(d) bytes of device scratch.
  */
 size_t lffn_layernorm_bwd_ws_bytes(int32_t d);
+/* dbias[c] = sum_n dy[n, c]: gradient of the `outputs + self.bias` of lookup.py:108 (autograd's sum in the reference);
+ * dy fp32 [N, cols]; deterministic.  ws: lffn_bias_grad_ws_bytes(cols) bytes of device scratch. */
+size_t lffn_bias_grad_ws_bytes(int32_t cols);
+int lffn_bias_grad(const float *dy, int64_t N, int32_t cols, float *dbias, void *ws, size_t ws_bytes, lffn_stream_t stream);
 int lffn_layernorm_bwd(const float *x, const float *du, const float *gamma, int64_t N, int32_t d, float eps, float *dx,
                        float *dgamma, float *dbeta, void *ws, size_t ws_bytes, lffn_stream_t stream);
 

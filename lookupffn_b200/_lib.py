@@ -62,6 +62,8 @@ _SIGNATURES = {
                                       C.c_size_t, C.c_void_p]),
     "lffn_proj_bwd": (C.c_int, [C.POINTER(HashDesc), C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p,
                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "lffn_bias_grad_ws_bytes": (C.c_size_t, [C.c_int32]),
+    "lffn_bias_grad": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "lffn_layernorm_bwd_ws_bytes": (C.c_size_t, [C.c_int32]),
     "lffn_layernorm_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p,
                                      C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),

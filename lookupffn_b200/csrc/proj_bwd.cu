@@ -334,3 +334,22 @@ extern "C" int lffn_proj_bwd(const lffn_hash_desc *desc, const float *proj_w_oi,
     return launch_proj_bwd(*desc, proj_w_oi, x, x_dtype, N, dz, du, dw, dbias, saved_acts, ws,
                            static_cast<cudaStream_t>(stream));
 }
+
+// Gradient of a bias that was added to every row: out[c] = sum_n dy[n][c], the two kernels of the projection's bias
+// gradient (partial sums over 64 row ranges, added in range order: deterministic).  Replaces the reduction autograd
+// runs for `outputs + self.bias` (lookup.py:108).  ws: lffn_bias_grad_ws_bytes(cols) bytes.
+extern "C" size_t lffn_bias_grad_ws_bytes(int32_t cols) { return dbias_ws_bytes(cols); }
+
+extern "C" int lffn_bias_grad(const float *dy, int64_t N, int32_t cols, float *dbias, void *ws, size_t ws_bytes,
+                              lffn_stream_t stream) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LFFN_REQUIRE(dy != nullptr && dbias != nullptr && N >= 0 && cols > 0, LFFN_ERR_INVALID_ARG, "bias_grad: bad argument");
+    LFFN_REQUIRE(ws != nullptr && ws_bytes >= dbias_ws_bytes(cols), LFFN_ERR_SCRATCH, "bias_grad: workspace of %zu bytes needed",
+                 dbias_ws_bytes(cols));
+    float *partial = static_cast<float *>(ws);
+    proj_dbias_partial_kernel<<<dim3((cols + 31) / 32, DBIAS_SPLITS), 256, 0, st>>>(dy, partial, N, cols);
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    proj_dw_reduce_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, dbias, cols, DBIAS_SPLITS);
+    LFFN_CHECK_CUDA(cudaGetLastError());
+    return LFFN_OK;
+}

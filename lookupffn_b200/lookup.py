@@ -226,12 +226,12 @@ class LookupFFN(nn.Module):
 
     def gather(self, indexes, weights, tables):
         """indexes already hold code + t * table_size (the kernel adds the offsets of reference
-        lookup.py:126).  The bias add of lookup.py:108 is fused into the kernel when no gradient is
-        needed."""
+        lookup.py:126).  The bias add of lookup.py:108 is fused into the kernel; in training its gradient is the
+        column sum of the output gradient (lffn_bias_grad)."""
         num_table, table_size, vector_dim = tables.shape
         flat = tables.reshape(num_table * table_size, vector_dim)
         m = self.hash.candidates
         if torch.is_grad_enabled() and (flat.requires_grad or weights.requires_grad):
-            out = ops.gather(indexes, weights, flat, training=self.training, structure=(num_table, m, table_size))
-            return out + self.bias.to(out.dtype)
+            return ops.gather(indexes, weights, flat, training=self.training, structure=(num_table, m, table_size),
+                              bias=self.bias)
         return ops.weighted_vector_gather_add(indexes, flat, weights, bias=self.bias)

@@ -446,33 +446,52 @@ class WeightedVectorGatherAdd(torch.autograd.Function):
     weights); backward returns (None, grad_source, grad_weights)."""
 
     @staticmethod
-    def forward(ctx, indexes, source, weights, structure=None):
+    def forward(ctx, indexes, source, weights, structure=None, bias=None):
+        """bias (optional, [d]): the `outputs + self.bias` of lookup.py:108 in the kernel's epilogue; its gradient
+        is the column sum of grad_outputs (lffn_bias_grad)."""
         indexes, source, weights = _contig(indexes), _contig(source), _contig(weights)
         ctx.save_for_backward(indexes, source, weights)
         ctx.structure = structure
-        return weighted_vector_gather_add(indexes, source, weights)
+        ctx.bias_dtype = None if bias is None else bias.dtype
+        return weighted_vector_gather_add(indexes, source, weights, bias=bias)
 
     @staticmethod
     def backward(ctx, grad_outputs):
         indexes, source, weights = ctx.saved_tensors
         g = _contig(grad_outputs.float())
-        grad_source = grad_weights = None
+        grad_source = grad_weights = grad_bias = None
         if ctx.needs_input_grad[2]:
             grad_weights = indexed_inner_product(indexes, g, source)
         if ctx.needs_input_grad[1]:
             grad_source = weighted_vector_scatter_add(indexes, g, weights, source.shape[0], ctx.structure)
             grad_source = grad_source.to(source.dtype)
-        return None, grad_source, grad_weights, None
+        if ctx.bias_dtype is not None and ctx.needs_input_grad[4]:
+            grad_bias = bias_grad(g).to(ctx.bias_dtype)
+        return None, grad_source, grad_weights, None, grad_bias
 
 
-def weighted_gather_add(indexes, source, weights, structure=None):
-    return WeightedVectorGatherAdd.apply(indexes, source, weights, structure)
+def bias_grad(dy):
+    """Column sums of dy [N, d] (fp32) through lffn_bias_grad: deterministic."""
+    L.require_cuda(dy)
+    dy = _contig(dy.reshape(-1, dy.shape[-1]).float())
+    N, d = dy.shape
+    out = torch.empty(d, dtype=torch.float32, device=dy.device)
+    lib = L.lib()
+    nbytes = lib.lffn_bias_grad_ws_bytes(d)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dy.device)
+    with torch.cuda.device(dy.device):
+        L.check(lib.lffn_bias_grad(L.ptr(dy), N, d, L.ptr(out), L.ptr(ws), nbytes, L.stream_ptr(dy.device)))
+    return out
 
 
-def gather(indices, weights, tables, training=False, structure=None):
+def weighted_gather_add(indexes, source, weights, structure=None, bias=None):
+    return WeightedVectorGatherAdd.apply(indexes, source, weights, structure, bias)
+
+
+def gather(indices, weights, tables, training=False, structure=None, bias=None):
     """Reference: gather(indices, weights, tables, training) (gather/kernel.py:11-25).  `indices`
-    already carry the table offsets; tables is [S, d]."""
-    return weighted_gather_add(indices, tables, weights, structure)
+    already carry the table offsets; tables is [S, d]; bias (optional) is added in the kernel."""
+    return weighted_gather_add(indices, tables, weights, structure, bias)
 
 
 def padded_dim(d_in):

@@ -164,3 +164,31 @@ def test_layer_norm_function_routes_training_through_the_kernel():
         assert float((a - b).abs().max() / b.abs().max()) < 1e-5
     with torch.no_grad():
         assert ops.layer_norm(x, ln).grad_fn is None  # inference: torch's module
+
+
+def test_bias_gradient_is_the_column_sum_and_rides_through_the_gather_function():
+    from lookupffn_b200 import ops
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(3)
+    dy = torch.randn(5001, 768, generator=g, device=dev)
+    got = ops.bias_grad(dy)
+    want = dy.double().sum(0)
+    assert float((got.double() - want).abs().max() / want.abs().max()) < 1e-6
+    assert torch.equal(got, ops.bias_grad(dy))  # fixed summation order
+    # through the autograd function: forward adds the bias in the kernel, backward returns its gradient
+    S, d, N, I = 300, 64, 257, 7
+    tables = torch.randn(S, d, generator=g, device=dev, requires_grad=True)
+    bias = torch.randn(d, generator=g, device=dev, requires_grad=True)
+    idx = torch.randint(0, S, (N, I), generator=g, device=dev, dtype=torch.int32)
+    w = torch.randn(N, I, generator=g, device=dev, requires_grad=True)
+    out = ops.gather(idx, w, tables, training=True, bias=bias)
+    ref = (tables[idx.long()] * w[..., None]).sum(1) + bias
+    assert float((out - ref).detach().abs().max() / ref.detach().abs().max()) < 1e-5
+    gy = torch.randn(N, d, generator=g, device=dev)
+    out.backward(gy)
+    gb, gw, gt = bias.grad.clone(), w.grad.clone(), tables.grad.clone()
+    bias.grad = w.grad = tables.grad = None
+    ref.backward(gy)
+    for a, b in ((gb, bias.grad), (gw, w.grad), (gt, tables.grad)):
+        assert float((a - b).abs().max() / b.abs().max()) < 1e-5
