@@ -433,6 +433,33 @@ __global__ void __launch_bounds__(256) code_weights_bwd_kernel(const float *__re
     }
 }
 
+// The reference's configuration (8-bit codes, score weights): a thread's table is two 16-byte loads and two 16-byte
+// stores, and every exponential is evaluated once.  Same formulas as the general kernel above.
+__global__ void __launch_bounds__(256) code_weights_bwd_score8_kernel(const float4 *__restrict__ z, const float *__restrict__ dw,
+                                                                      long long NT, float4 *__restrict__ dz) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < NT; i += (long long)gridDim.x * blockDim.x) {
+        const float4 lo = __ldg(z + 2 * i), hi = __ldg(z + 2 * i + 1);
+        const float zz[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float e[8], num = 0.f, den = 1.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float a = fabsf(zz[j]);
+            e[j] = expf(-2.f * a);
+            num += a;
+            den *= 1.f + e[j];
+        }
+        const float score = num / den, g = __ldg(dw + i), inv_den = 1.f / den;
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float sg = zz[j] > 0.f ? 1.f : (zz[j] < 0.f ? -1.f : 0.f);
+            o[j] = g * sg * (inv_den + score * 2.f * e[j] / (1.f + e[j]));
+        }
+        dz[2 * i] = make_float4(o[0], o[1], o[2], o[3]);
+        dz[2 * i + 1] = make_float4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 int launch_code_weights_bwd(const float *z, const float *dw, int64_t N, int T, int k, int weight_mode, float tau,
                             float *dz, cudaStream_t st) {
     const long long NT = (long long)N * T;
@@ -440,6 +467,12 @@ int launch_code_weights_bwd(const float *z, const float *dw, int64_t N, int T, i
     const long long cap = (long long)num_sms() * 8;
     if (grid > cap) grid = cap;
     if (grid < 1) grid = 1;
+    if (k == 8 && weight_mode == LFFN_WEIGHT_SCORE && ((reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(dz)) & 15u) == 0) {
+        code_weights_bwd_score8_kernel<<<(unsigned)grid, 256, 0, st>>>(reinterpret_cast<const float4 *>(z), dw, NT,
+                                                                       reinterpret_cast<float4 *>(dz));
+        LFFN_CHECK_CUDA(cudaGetLastError());
+        return LFFN_OK;
+    }
     code_weights_bwd_kernel<<<(unsigned)grid, 256, 0, st>>>(z, dw, NT, k, weight_mode, tau, dz);
     LFFN_CHECK_CUDA(cudaGetLastError());
     return LFFN_OK;
