@@ -177,10 +177,17 @@ __device__ __forceinline__ void tile_end_rotation(float *Y, const float *carry, 
             float z = __fadd_rn(__fmul_rn(a.mix_a, Y[e * HB_MP + lane]), __fmul_rn(a.mix_b, Xs[e * HB_MP + lane]));
             if (a.bias != nullptr && g < (long long)a.T * k) z = __fadd_rn(z, __ldg(a.bias + g));
             Y[e * HB_MP + lane] = z;
-            if (a.z_out != nullptr && lane < mt && g >= g_lo && g < g_hi)
-                a.z_out[(n0 + lane) * (g_hi - g_lo) + (g - g_lo)] = z;
         }
         __syncthreads();
+        if (a.z_out != nullptr) {  // rows of z with the lanes over coordinates: 128-byte stores
+            for (int mm = warp; mm < mt; mm += THREADS / 32) {
+                float *zrow = a.z_out + (n0 + mm) * (g_hi - g_lo);
+                for (int e = lane; e < D; e += 32) {
+                    const long long g = c_lo + e;
+                    if (g >= g_lo && g < g_hi) zrow[g - g_lo] = Y[e * HB_MP + mm];
+                }
+            }
+        }
     } else if (!fused) {
         for (int mm = warp; mm < HB_M; mm += THREADS / 32) {
             const XT *xrow = static_cast<const XT *>(a.x) + (n0 + mm) * a.d_in;

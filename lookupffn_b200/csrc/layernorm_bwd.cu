@@ -73,7 +73,8 @@ __global__ void layernorm_bwd_reduce_kernel(const float *__restrict__ partial, f
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= 2 * d) return;
     float t = 0.f;
-    for (int b = 0; b < blocks; b++) t += partial[(size_t)b * 2 * d + i];
+#pragma unroll 8
+    for (int b = 0; b < blocks; b++) t += __ldg(partial + (size_t)b * 2 * d + i);  // loads in flight together, adds in order
     if (i < d) dgamma[i] = t;
     else dbeta[i - d] = t;
 }

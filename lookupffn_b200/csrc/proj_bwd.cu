@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(256) proj_dw_reduce_kernel(const float *__rest
                                                             long long n, int splits) {
     for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (long long)gridDim.x * blockDim.x) {
         float v = 0.f;
+#pragma unroll 8
         for (int sp = 0; sp < splits; sp++) v += __ldg(partial + (size_t)sp * n + j);
         dw[j] = v;
     }
