@@ -552,10 +552,15 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
         const bool first_of_tile = u == u_begin || r == a.r_lo;
         if constexpr (MODE == 2) {
             __syncthreads();  // the previous unit has finished with Y
-            for (int mm = warp; mm < HB_M; mm += NW) {
-                const float *grow = a.dz + (n0 + mm) * a.dz_cols + (long long)r * D;
-                for (int e = lane; e < D; e += 32)
-                    Y[e * HB_MP + mm] = (mm < mt && (long long)r * D + e < a.dz_cols) ? __fmul_rn(a.mix_a, __ldg(grow + e)) : 0.f;
+            // every thread issues its D * 32 / THREADS loads back to back (eight in flight at a time), consecutive
+            // threads on consecutive coordinates of a token
+            const int dshift = 31 - __clz(D);
+#pragma unroll 8
+            for (int i = tid; i < D * HB_M; i += THREADS) {
+                const int e = i & (D - 1), mm = i >> dshift;
+                const bool in = mm < mt && (long long)r * D + e < a.dz_cols;
+                const float gv = in ? __ldg(a.dz + (n0 + mm) * a.dz_cols + (long long)r * D + e) : 0.f;
+                Y[e * HB_MP + mm] = in ? __fmul_rn(a.mix_a, gv) : 0.f;
             }
         } else if constexpr (X0) {
             if (first_of_tile) {
