@@ -64,8 +64,10 @@ __device__ __forceinline__ void radix_butterflies(float (&v)[RADIX]) {
 }
 
 // One pass of the transform over bits [lo, lo+nb) of the coordinate index, RADIX = 2^nb.
+// gdst, when given: the transformed tile also goes to global memory as [D][HB_M] (token rows of 128 bytes, written
+// straight from the registers that hold the pass's results).
 template <int RADIX, int NW>
-__device__ __forceinline__ void fwht_pass(float *Y, int D, int lo, float scale, int warp, int lane) {
+__device__ __forceinline__ void fwht_pass(float *Y, int D, int lo, float scale, int warp, int lane, float *gdst = nullptr) {
     const int ngroups = D / RADIX;
     const int lo_mask = (1 << lo) - 1;
     for (int gi = warp; gi < ngroups; gi += NW) {
@@ -80,11 +82,15 @@ __device__ __forceinline__ void fwht_pass(float *Y, int D, int lo, float scale, 
         }
 #pragma unroll
         for (int q = 0; q < RADIX; q++) Y[(base + (q << lo)) * HB_MP + lane] = v[q];
+        if (gdst != nullptr) {
+#pragma unroll
+            for (int q = 0; q < RADIX; q++) gdst[(size_t)(base + (q << lo)) * HB_M + lane] = v[q];
+        }
     }
 }
 
 template <int NW = HB_THREADS / 32>
-__device__ __forceinline__ void fwht_tile(float *Y, int D, float scale, int warp, int lane) {
+__device__ __forceinline__ void fwht_tile(float *Y, int D, float scale, int warp, int lane, float *gdst = nullptr) {
     int bits = 31 - __clz(D);
     // up to 5 bits (radix 32) per pass, split evenly: 10 bits = 5 + 5, 9 = 5 + 4
     while (bits > 0) {
@@ -92,11 +98,12 @@ __device__ __forceinline__ void fwht_tile(float *Y, int D, float scale, int warp
         const int nb = (bits + left - 1) / left;
         const int lo = bits - nb;
         const float sc = lo == 0 ? scale : 1.f;
-        if (nb == 5) fwht_pass<32, NW>(Y, D, lo, sc, warp, lane);
-        else if (nb == 4) fwht_pass<16, NW>(Y, D, lo, sc, warp, lane);
-        else if (nb == 3) fwht_pass<8, NW>(Y, D, lo, sc, warp, lane);
-        else if (nb == 2) fwht_pass<4, NW>(Y, D, lo, sc, warp, lane);
-        else fwht_pass<2, NW>(Y, D, lo, sc, warp, lane);
+        float *gd = lo == 0 ? gdst : nullptr;  // the last pass holds the finished values
+        if (nb == 5) fwht_pass<32, NW>(Y, D, lo, sc, warp, lane, gd);
+        else if (nb == 4) fwht_pass<16, NW>(Y, D, lo, sc, warp, lane, gd);
+        else if (nb == 3) fwht_pass<8, NW>(Y, D, lo, sc, warp, lane, gd);
+        else if (nb == 2) fwht_pass<4, NW>(Y, D, lo, sc, warp, lane, gd);
+        else fwht_pass<2, NW>(Y, D, lo, sc, warp, lane, gd);
         bits = lo;
         __syncthreads();
     }
@@ -413,6 +420,13 @@ __device__ __forceinline__ void bulk_copy_g2s(void *smem_dst, const void *gmem_s
                  "l"(__cvta_generic_to_global(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// 4-byte asynchronous copy global -> shared (zero fill when !valid: nothing is read from gsrc then)
+__device__ __forceinline__ void cp_async4(float *smem_dst, const float *gsrc, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(smem_dst)), "l"(__cvta_generic_to_global(gsrc)),
+                 "r"(valid ? 4u : 0u)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ unsigned long long dup2(float w) {
     unsigned long long r;
     asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(w));
@@ -465,7 +479,7 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     unsigned long long *bars = reinterpret_cast<unsigned long long *>(carry + HB_CARRY * HB_MP);
     unsigned long long *full = bars, *empty = bars + HF_NBUF;  // one pair per weight buffer
     float *lnstat = carry + HB_CARRY * HB_MP + HF_BAR_FLOATS;                // [2][HB_M]
-    float *Xs = X0 ? lnstat + HB_LN_FLOATS : nullptr;                         // [D][HB_MP]
+    float *Xs = X0 ? lnstat + HB_LN_FLOATS : nullptr;                         // [D][HB_MP]; mode 2: the other tile buffer
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int NB = D / 64;
     const int cps = (D / PC) * (64 / CR);            // chunks per stage: passes x row slices
@@ -536,9 +550,25 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
     // either in the normal flow or here.
     auto give_up = [&](long long from, long long to) {
         if (a.status != nullptr) atomicOr(a.status, LFFN_STATUS_TIMEOUT);
+        cp_async_wait_all();  // this thread's share of a prefetched tile (mode 2), if any
         for (long long c = from; c < to && c < total_chunks; c++)
             mbar_wait(&full[c % HF_NBUF], (unsigned)((c / HF_NBUF) & 1));
     };
+
+    // mode 2 with a second tile buffer: asynchronous, transposing fetch of the gradient tile of (tile_, r_)
+    auto request_dz_tile = [&](float *dst, long long tile_, int r_) {
+        const long long n0_ = tile_ * HB_M;
+        const int mt_ = (int)min((long long)HB_M, a.N - n0_);
+        const int dshift = 31 - __clz(D);
+        for (int i = tid; i < D * HB_M; i += THREADS) {
+            const int e = i & (D - 1), mm = i >> dshift;
+            const bool in = mm < mt_ && (long long)r_ * D + e < a.dz_cols;
+            cp_async4(dst + e * HB_MP + mm, in ? a.dz + (n0_ + mm) * a.dz_cols + (long long)r_ * D + e : a.dz, in);
+        }
+    };
+    if constexpr (MODE == 2 && X0) {
+        if (u_begin < u_end) request_dz_tile(Xs, u_begin / nrot, a.r_lo + (int)(u_begin % nrot));
+    }
 
     long long gc = 0;
     HB_MARK(-1);
@@ -551,16 +581,36 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
         const int mt = (int)min((long long)HB_M, a.N - n0);
         const bool first_of_tile = u == u_begin || r == a.r_lo;
         if constexpr (MODE == 2) {
-            __syncthreads();  // the previous unit has finished with Y
-            // every thread issues its D * 32 / THREADS loads back to back (eight in flight at a time), consecutive
-            // threads on consecutive coordinates of a token
-            const int dshift = 31 - __clz(D);
+            if constexpr (X0) {
+                // The gradient tile of this unit was requested during the previous one (asynchronous 4-byte copies into
+                // the second tile buffer, already transposed): wait for it, make that buffer the working tile, and
+                // request the next unit's tile into the buffer the previous unit has just finished with.  Read straight
+                // from global memory these 64 KB cost a quarter of the kernel in exposed latency.
+                cp_async_wait_all();
+                __syncthreads();  // every thread's copies have landed; the previous unit has finished with Y
+                float *t = Y;
+                Y = Xs;
+                Xs = t;
+                if (u + 1 < u_end) {
+                    const int rn = r + 1 > a.r_hi ? a.r_lo : r + 1;
+                    request_dz_tile(Xs, rn == a.r_lo ? tile + 1 : tile, rn);
+                }
+                if (a.mix_a != 1.f) {
+                    for (int i = tid; i < D * HB_M; i += THREADS) {
+                        float *p = Y + (i >> 5) * HB_MP + (i & 31);
+                        *p = __fmul_rn(a.mix_a, *p);
+                    }
+                }
+            } else {
+                __syncthreads();  // the previous unit has finished with Y
+                const int dshift = 31 - __clz(D);
 #pragma unroll 8
-            for (int i = tid; i < D * HB_M; i += THREADS) {
-                const int e = i & (D - 1), mm = i >> dshift;
-                const bool in = mm < mt && (long long)r * D + e < a.dz_cols;
-                const float gv = in ? __ldg(a.dz + (n0 + mm) * a.dz_cols + (long long)r * D + e) : 0.f;
-                Y[e * HB_MP + mm] = in ? __fmul_rn(a.mix_a, gv) : 0.f;
+                for (int i = tid; i < D * HB_M; i += THREADS) {
+                    const int e = i & (D - 1), mm = i >> dshift;
+                    const bool in = mm < mt && (long long)r * D + e < a.dz_cols;
+                    const float gv = in ? __ldg(a.dz + (n0 + mm) * a.dz_cols + (long long)r * D + e) : 0.f;
+                    Y[e * HB_MP + mm] = in ? __fmul_rn(a.mix_a, gv) : 0.f;
+                }
             }
         } else if constexpr (X0) {
             if (first_of_tile) {
@@ -634,24 +684,32 @@ __global__ void __launch_bounds__(THREADS, 1) hash_block64_kernel(HashArgs a) {
         if constexpr (MODE == 2) {
             for (int sb = 0; sb < a.S; sb++) {
                 const int s = a.S - 1 - sb;
-                fwht_tile<NW>(Y, D, a.had_scale, warp, lane);  // ends with a CTA barrier
-                tile_save<THREADS>(Y, a.act_out + ((size_t)((r - a.r_lo) * a.S + s) * ntiles + tile) * tile_floats, D);
-                __syncthreads();  // the saved values have been read before the multiply overwrites them
+                // the transformed gradient is saved by the transform's last pass itself (ends with a CTA barrier)
+                fwht_tile<NW>(Y, D, a.had_scale, warp, lane,
+                              a.act_out + ((size_t)((r - a.r_lo) * a.S + s) * ntiles + tile) * tile_floats);
+                HB_MARK(HB_PH_HADAMARD);
                 if (!multiply_stage(Y)) return;
                 __syncthreads();
+                HB_MARK(HB_PH_WRITEBACK);
             }
             tile_save<THREADS>(Y, a.du_out + (size_t)tile * tile_floats, D);
         } else {
             for (int s = 0; s < a.S; s++) {
                 const float *ysrc = (X0 && s == 0) ? Xs : Y;
                 if constexpr (MODE == 1) {
-                    tile_save<THREADS>(ysrc, a.act_out + ((size_t)((r - a.r_lo) * a.S + s) * ntiles + tile) * tile_floats, D);
-                    __syncthreads();
+                    // the input of stage 0 is saved here; the inputs of the later stages by the transform before them
+                    if (s == 0) {
+                        tile_save<THREADS>(ysrc, a.act_out + ((size_t)(r - a.r_lo) * a.S * ntiles + tile) * tile_floats, D);
+                        if (!X0) __syncthreads();  // ysrc is Y: read before the multiply's write-back overwrites it
+                    }
                 }
                 if (!multiply_stage(ysrc)) return;
                 __syncthreads();
                 HB_MARK(HB_PH_WRITEBACK);
-                fwht_tile<NW>(Y, D, a.had_scale, warp, lane);
+                fwht_tile<NW>(Y, D, a.had_scale, warp, lane,
+                              (MODE == 1 && s + 1 < a.S)
+                                  ? a.act_out + ((size_t)((r - a.r_lo) * a.S + s + 1) * ntiles + tile) * tile_floats
+                                  : nullptr);
                 HB_MARK(HB_PH_HADAMARD);
             }
             // mode 1 may be asked for z as well (training's forward pass keeps the stage inputs for its backward)
@@ -703,11 +761,12 @@ int launch_hash_block64_mode(const HashArgs &a, int mode, int x_dtype, cudaStrea
     const bool wide = a.D % 512 == 0;
     const size_t smem_b = ((size_t)a.D * HB_MP + HB_WFLOATS + HB_CARRY * HB_MP + HB_LN_FLOATS + HF_BAR_FLOATS) * sizeof(float);
     const size_t smem_x0 = smem_b + (size_t)a.D * HB_MP * sizeof(float);
-    const bool x0 = mode == 1 && smem_x0 <= 227 * 1024;
+    const bool x0 = smem_x0 <= 227 * 1024;  // room for a second tile: the resident input (mode 1), the prefetched gradient tile (mode 2)
     const size_t smem_k = x0 ? smem_x0 : smem_b;
     void (*kern)(HashArgs) = nullptr;
     if (mode == 2) {
-        kern = wide ? hash_block64_kernel<float, 512, false, 2> : hash_block64_kernel<float, 256, false, 2>;
+        kern = wide ? (x0 ? hash_block64_kernel<float, 512, true, 2> : hash_block64_kernel<float, 512, false, 2>)
+                    : (x0 ? hash_block64_kernel<float, 256, true, 2> : hash_block64_kernel<float, 256, false, 2>);
     } else if (x_dtype == LFFN_F32) {
         kern = wide ? (x0 ? hash_block64_kernel<float, 512, true, 1> : hash_block64_kernel<float, 512, false, 1>)
                     : (x0 ? hash_block64_kernel<float, 256, true, 1> : hash_block64_kernel<float, 256, false, 1>);
