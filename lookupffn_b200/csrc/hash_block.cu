@@ -142,6 +142,7 @@ __device__ __forceinline__ void tile_load(float *dst, const HashArgs &a, long lo
                                                      a.ln_b != nullptr ? __ldg(a.ln_b + e) : 0.f)
                                           : 0.f;
         } else {
+#pragma unroll 8
             for (int e = lane; e < D; e += 32)
                 dst[e * HB_MP + mm] = (mm < mt && e < a.d_in) ? Elem<XT>::load1(xrow + e) : 0.f;
         }
