@@ -67,16 +67,25 @@ __global__ void __launch_bounds__(LNB_WARPS * 32) layernorm_bwd_kernel(const flo
     }
 }
 
-// out[i] = sum over blocks b, in order, of partial[b][i], i in [0, 2d): dgamma then dbeta
-__global__ void layernorm_bwd_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dgamma,
-                                            float *__restrict__ dbeta, int d, int blocks) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= 2 * d) return;
+// out[i] = sum over the CTAs' partial rows, i in [0, 2d): dgamma then dbeta.  32 columns x 8 groups per CTA: group g
+// adds rows g, g + 8, ... in order, then the eight group sums are added in group order (fixed order, short chains).
+__global__ void __launch_bounds__(256) layernorm_bwd_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dgamma,
+                                                                   float *__restrict__ dbeta, int d, int blocks) {
+    __shared__ float part[8][32];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + tx;
     float t = 0.f;
-#pragma unroll 8
-    for (int b = 0; b < blocks; b++) t += __ldg(partial + (size_t)b * 2 * d + i);  // loads in flight together, adds in order
-    if (i < d) dgamma[i] = t;
-    else dbeta[i - d] = t;
+    if (i < 2 * d)
+        for (int b = ty; b < blocks; b += 8) t += __ldg(partial + (size_t)b * 2 * d + i);
+    part[ty][tx] = t;
+    __syncthreads();
+    if (ty == 0 && i < 2 * d) {
+        float v = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; g++) v += part[g][tx];
+        if (i < d) dgamma[i] = v;
+        else dbeta[i - d] = v;
+    }
 }
 
 static int ln_bwd_blocks() { return 2 * num_sms(); }
@@ -104,7 +113,7 @@ extern "C" int lffn_layernorm_bwd(const float *x, const float *du, const float *
     if (smem > 48 * 1024) LFFN_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<blocks, LNB_WARPS * 32, smem, st>>>(x, du, gamma, N, eps, dx, partial);
     LFFN_CHECK_CUDA(cudaGetLastError());
-    layernorm_bwd_reduce_kernel<<<(2 * d + 255) / 256, 256, 0, st>>>(partial, dgamma, dbeta, d, blocks);
+    layernorm_bwd_reduce_kernel<<<(2 * d + 31) / 32, 256, 0, st>>>(partial, dgamma, dbeta, d, blocks);
     LFFN_CHECK_CUDA(cudaGetLastError());
     return LFFN_OK;
 }
