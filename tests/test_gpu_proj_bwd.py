@@ -49,6 +49,7 @@ CASES = [
     (300, 768, 1024, 4, 2048, 1.0 / 32, (1.0, 0.0)),    # D = 1024: the narrow tile pipeline, normalised transform
     (64, 512, 512, 2, 512, 1.0, (0.7, 0.3)),            # two stages, one rotation
     (1, 256, 256, 4, 256, 1.0, (0.7, 0.3)),             # a single token
+    (9491, 512, 512, 4, 1024, 1.0, (0.7, 0.3)),         # two or three tiles per CTA: the prefetched gradient tiles, ragged end
 ]
 
 
