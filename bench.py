@@ -528,7 +528,7 @@ def time_steps(step, steps, warmup, device, world):
 def table_sharded_record(args, rank, world, local):
     """Appended to the default line when more than one GPU runs: a short run of benchmark configuration 5 (tables
     split by T over the GPUs, every GPU sees all 262,144 tokens, partial sums combined by a reduce-scatter over
-    NVLink) with both exchanges, beside the same per-GPU shape without any exchange.  k = 8 at every N; k = 6 and
+    NVLink) with every exchange (NCCL, the two fused forms, copy engines), beside the same per-GPU shape without any exchange.  k = 8 at every N; k = 6 and
     k = 12 too at 8 GPUs.  Every rank runs it; rank 0 reports."""
     device = torch.device("cuda", local)
     ks = args.table_sharded_ks.split(",") if args.table_sharded_ks else ["c5k8"] + (["c5k12", "c5k6"] if world >= 8 else [])
