@@ -81,8 +81,9 @@ def test_random_shapes_against_oracle(seed):
         hs = float(rng.choice([1.0, 0.125, 1 / np.sqrt(D)]))
         bf16 = rng.rand() < 0.3
         NB = D // BS
-        wt = ((2.0 * rng.randint(0, 2, size=(R, S, NB, BS, BS)) - 1.0) if BS == 1
-              else rng.randn(R, S, NB, BS, BS) / np.sqrt(BS * D) * 3).astype(np.float32)
+        # diagonals: signs (the reference's use) or, one time in three, arbitrary floats (every product rounded)
+        wt = ((2.0 * rng.randint(0, 2, size=(R, S, NB, BS, BS)) - 1.0) * (rng.rand(R, S, NB, BS, BS) + 0.5 if rng.rand() < 0.33 else 1.0)
+              if BS == 1 else rng.randn(R, S, NB, BS, BS) / np.sqrt(BS * D) * 3).astype(np.float32)
         bias = (0.05 * rng.randn(T * k)).astype(np.float32) if rng.rand() < 0.7 else None
         x = rng.randn(N, d_in).astype(np.float32)
         if bf16:
