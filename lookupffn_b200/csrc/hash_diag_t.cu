@@ -83,6 +83,11 @@ __global__ void __launch_bounds__(HT_WARPS * 32, 4) hash_diag_t_kernel(HashArgs 
     float *buf = smem_t + wib * (tbuf_words(D) + HT_CARRY);
     float *carry = buf + tbuf_words(D);
     float *sbias = smem_t + HT_WARPS * (tbuf_words(D) + HT_CARRY);  // [r_hi - r_lo + 1][tbuf_words(D)] when a.bias != nullptr
+    // second per-warp buffer behind the staged bias, only for the soft-flip mode with K >= 8 (see the emission below)
+    float *stage2 = nullptr;
+    if (K >= 8 && a.weight_mode == LFFN_WEIGHT_SOFT_FLIP && (reinterpret_cast<uintptr_t>(a.idx_out) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(a.w_out) & 15u) == 0 && (((long long)a.t_count * (K + 1)) & 3) == 0)
+        stage2 = sbias + (a.bias != nullptr ? (a.r_hi - a.r_lo + 1) * tbuf_words(D) : 0) + wib * tbuf_words(D);
     const int k = K > 0 ? K : a.k;
     const long long total = (long long)a.T * k;
     if (a.bias != nullptr) {
@@ -179,6 +184,29 @@ __global__ void __launch_bounds__(HT_WARPS * 32, 4) hash_diag_t_kernel(HashArgs 
                 continue;
             }
             const long long t0 = ((long long)r * D + lane * V) / KK;  // first table of this lane in this rotation
+            if constexpr (K >= 8) {
+                // k + 1 candidates per table (soft flip): the rotation's D/K tables x (K + 1) pairs are collected in
+                // two per-warp buffers and leave as 16-byte stores of consecutive lanes, instead of 4-byte stores
+                // 36 (K + 1) bytes apart
+                constexpr int E = (D / KK) * (KK + 1);  // pairs per rotation; <= tbuf_words(D) for K >= 8
+                const long long tr0 = (long long)r * D / KK;
+                const long long o0 = n * out_pitch + (tr0 - a.t_begin) * m;
+                if (stage2 != nullptr && tr0 >= a.t_begin && tr0 + D / KK <= a.t_begin + a.t_count && (o0 & 3) == 0) {
+                    int32_t *ib = reinterpret_cast<int32_t *>(buf);
+                    float *wb = stage2;
+#pragma unroll
+                    for (int u = 0; u < TPL; u++)
+                        emit_table_k<KK>(&v[u * KK], a.bit_order, a.weight_mode, a.tau, (int32_t)((t0 + u - a.t_begin) << KK),
+                                        ib + (lane * TPL + u) * (KK + 1), wb + (lane * TPL + u) * (KK + 1));
+                    __syncwarp();
+                    for (int i = lane; i < E / 4; i += 32) {
+                        reinterpret_cast<int4 *>(a.idx_out + o0)[i] = reinterpret_cast<const int4 *>(ib)[i];
+                        reinterpret_cast<float4 *>(a.w_out + o0)[i] = reinterpret_cast<const float4 *>(wb)[i];
+                    }
+                    __syncwarp();
+                    continue;
+                }
+            }
             if (vec4) {
 #pragma unroll
                 for (int g4 = 0; g4 < TPL / 4; g4++) {
@@ -261,8 +289,10 @@ static bool try_launch_hash_t(const HashArgs &a, cudaStream_t st, int *rc) {
     if (a.D != 256 && a.D != 512 && a.D != 1024) return false;
     if (a.k < 1 || a.k > 16) return false;
     const size_t nrot = (size_t)(a.r_hi - a.r_lo + 1);
-    const size_t smem = ((size_t)HT_WARPS * (tbuf_words(a.D) + HT_CARRY) + (a.bias != nullptr ? nrot : 0) * tbuf_words(a.D)) * sizeof(float);
+    size_t smem = ((size_t)HT_WARPS * (tbuf_words(a.D) + HT_CARRY) + (a.bias != nullptr ? nrot : 0) * tbuf_words(a.D)) * sizeof(float);
     if (smem > 40 * 1024) return false;
+    if (a.weight_mode == LFFN_WEIGHT_SOFT_FLIP && (a.k == 8 || a.k == 16))  // the second staging buffer per warp
+        smem += (size_t)HT_WARPS * tbuf_words(a.D) * sizeof(float);
     switch (a.D) {
         case 256: *rc = launch_hash_t_v<8, XT>(a, smem, st); break;
         case 512: *rc = launch_hash_t_v<16, XT>(a, smem, st); break;

@@ -197,6 +197,34 @@ def test_hash_diagonal_with_general_weights(dev, D, k, mix_a):
     np.testing.assert_array_equal(t2n(idx2), idx_ref)
 
 
+@pytest.mark.parametrize("D,k", [(1024, 8), (512, 8), (256, 8), (1024, 16), (512, 16)])
+def test_hash_soft_flip_candidates_without_z(dev, D, k):
+    """k + 1 candidates per table from the transposing kernel (whole rotations leave through per-warp staging buffers
+    as 16-byte stores; partial ranges and unaligned rows take the scalar stores): codes exact, weights 1e-5."""
+    from lookupffn_b200 import ops
+
+    rng = np.random.RandomState(D + k)
+    N, d_in = 77, D - 5
+    T = (3 * D) // k            # three rotations
+    w = make_proj(rng, D, 1, 2, 3, signs=True)
+    bias = (0.05 * rng.randn(T * k)).astype(np.float32)
+    x = rng.randn(N, d_in).astype(np.float32)
+    hs = float(np.float32(1.0 / np.sqrt(D)))
+    z_ref = O.project(x, w, T * k, had_scale=hs, mix_a=1.0, mix_b=0.0, bias=bias)
+    idx_ref, w_ref = O.code_weights(z_ref, T, k, weight_mode=O.WEIGHT_SOFT_FLIP, tau=0.5)
+    desc = ops.make_hash_desc(d_in, torch.from_numpy(w).to(dev), torch.from_numpy(bias).to(dev), T, k, had_scale=hs,
+                              mix_a=1.0, mix_b=0.0, weight_mode=O.WEIGHT_SOFT_FLIP, tau=0.5)
+    xd = torch.from_numpy(x).to(dev)
+    m = k + 1
+    idx, wgt, _ = ops.hash_fwd(xd, desc)
+    np.testing.assert_array_equal(t2n(idx), idx_ref)
+    assert rel_err(t2n(wgt), w_ref) < 1e-5
+    for tb, tc in ((1, T - 2), (D // k, D // k), (4, T - 4)):  # ragged ends, exactly the middle rotation, aligned start
+        idx_s, w_s, _ = ops.hash_fwd(xd, desc, t_begin=tb, t_count=tc)
+        np.testing.assert_array_equal(t2n(idx_s), idx_ref[:, tb * m:(tb + tc) * m] - tb * (1 << k))
+        np.testing.assert_array_equal(t2n(w_s), t2n(wgt)[:, tb * m:(tb + tc) * m])
+
+
 def test_hash_bf16_input(dev):
     from lookupffn_b200 import ops
 
