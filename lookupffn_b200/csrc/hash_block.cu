@@ -448,7 +448,9 @@ constexpr int HF_BAR_FLOATS = 4 * HF_NBUF;     // a full and an empty mbarrier p
 // on 8 blocks x 16-row chunks; the chunk is 32 KB either way.
 // X0: shared memory has room for a second [D][HB_MP] array (D <= 512): the input tile is loaded once per tile and
 // kept there; the first stage of every rotation reads it directly and the mix at the end of a rotation takes u
-// from it, instead of eight passes over the tile's rows in global memory per tile.
+// from it, instead of eight passes over the tile's rows in global memory per tile.  In mode 2 the second array is the
+// other half of a double buffer: the gradient tile of the next unit is fetched into it with asynchronous copies
+// while the current unit is being worked on.
 //
 // MODE selects what the tile pipeline is used for:
 //   0  the hashing stage itself (codes, weights, optionally z)
@@ -459,7 +461,8 @@ constexpr int HF_BAR_FLOATS = 4 * HF_NBUF;     // a full and an empty mbarrier p
 //      a.act_out[s][tile] (this is the gradient at the output of stage s's multiply), g <- g W[r, s] (a.w is then
 //      the parameter in its own [o][i] order, which is input-major for this product); the result, the gradient
 //      with respect to the rotation's input, goes to a.du_out[tile]
-// Mode 2 is launched for one rotation at a time (r_lo == r_hi).
+// Mode 2 is launched for one rotation at a time (r_lo == r_hi).  In modes 1 and 2 the tiles of the later stages are
+// written out by the last pass of the transform that produces them (fwht_pass, gdst).
 template <int THREADS>
 __device__ __forceinline__ void tile_save(const float *Y, float *dst, int D) {
     for (int i = threadIdx.x; i < D * HB_M; i += THREADS) dst[i] = Y[(i >> 5) * HB_MP + (i & 31)];
