@@ -11,6 +11,12 @@
 
 #include "../../include/lookupffn.h"
 
+// Long index lists over table sets beyond L2 are consumed in slices of about this many table bytes (gather_fwd.cu,
+// gather_bwd.cu): one launch per slice re-aligns the warps along the list.
+#ifndef LFFN_GATHER_SLICE_BYTES
+#define LFFN_GATHER_SLICE_BYTES 32e6
+#endif
+
 namespace lffn {
 
 constexpr unsigned FULL = 0xffffffffu;

@@ -156,7 +156,7 @@ static int launch_bww_vpl(const int32_t *idx, const float *dy, const void *table
     int slices = 1;
     if (I >= 512) {
         const double table_bytes = (double)S * d * sizeof(TableT);
-        if (table_bytes > 256e6) slices = (int)(table_bytes / 32e6);
+        if (table_bytes > 256e6) slices = (int)(table_bytes / LFFN_GATHER_SLICE_BYTES);
         if (slices > I / 128) slices = I / 128;
         if (slices < 1) slices = 1;
     }

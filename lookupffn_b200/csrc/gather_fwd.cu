@@ -310,7 +310,7 @@ static int launch_vpl_f(const int32_t *idx, const float *w, const void *tables, 
     int slices = 1;
     if (sizeof(OutT) == 4 && seg == nullptr && I >= 512) {
         const double table_bytes = (double)S * d * sizeof(TableT);
-        if (table_bytes > 256e6) slices = (int)(table_bytes / 32e6);
+        if (table_bytes > 256e6) slices = (int)(table_bytes / LFFN_GATHER_SLICE_BYTES);
         if (slices > I / 128) slices = I / 128;
         if (slices < 1) slices = 1;
     }
