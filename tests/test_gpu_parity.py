@@ -421,7 +421,10 @@ def test_gather_bwd_tables_any_index_list(dev, N, I, S, d):
 
 @pytest.mark.parametrize("N,T,m,rows,d", [(1, 1, 1, 2, 4), (50, 6, 1, 256, 64), (300, 5, 9, 256, 768),
                                            (700, 3, 1, 64, 512), (64, 4, 7, 4096, 128), (2000, 2, 1, 16, 1024),
-                                           (5000, 2, 3, 2048, 64), (33, 3, 2, 2049, 32)])
+                                           (5000, 2, 3, 2048, 64), (33, 3, 2, 2049, 32),
+                                           # enough gradient rows that the segmented gather runs in column tiles
+                                           # (tiles of 96 + 96 + 64 vectors at d = 1024; 64 + 64 + 64 at d = 768)
+                                           (12000, 2, 1, 16, 1024), (14001, 1, 2, 64, 768)])
 def test_gather_bwd_tables_sorted_bit_exact_and_deterministic(dev, N, T, m, rows, d):
     from lookupffn_b200 import ops
 
