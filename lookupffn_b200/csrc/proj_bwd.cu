@@ -84,10 +84,12 @@ __global__ void __launch_bounds__(DW_THREADS) proj_dw_partial_kernel(const float
             const float4 y4 = *reinterpret_cast<const float4 *>(Yv + m * DW_LD);
             const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
             const float yv[4] = {y4.x, y4.y, y4.z, y4.w};
+            // two output rows per instruction (packed fused multiply-add: the same fmaf chain per element)
 #pragma unroll
-            for (int p = 0; p < 8; p++)
+            for (int p = 0; p < 8; p += 2)
 #pragma unroll
-                for (int q = 0; q < 4; q++) acc[p][q] = fmaf(gv[p], yv[q], acc[p][q]);
+                for (int q = 0; q < 4; q++)
+                    fma2(acc[p][q], acc[p + 1][q], gv[p], gv[p + 1], yv[q], yv[q], acc[p][q], acc[p + 1][q]);
         }
         if (t + 1 < t_hi) stage(b ^ 1);  // the other buffer was last read one iteration ago, before the barrier below
         __syncthreads();
