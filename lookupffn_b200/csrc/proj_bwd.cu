@@ -24,7 +24,13 @@ int launch_hash_block64_mode(const HashArgs &a, int mode, int x_dtype, cudaStrea
 
 constexpr int TILE_M = 32;       // tokens per tile of the saved activations: [D][32] floats per tile
 constexpr int DW_THREADS = 128;  // one 8 (o) x 4 (i) register tile of the 64 x 64 block per thread
-constexpr int DW_LD = 68;        // padded row length of the transposed [token][64] staging arrays
+constexpr int DW_LD = 64;        // row length of the transposed [token][64] staging arrays
+// The staging arrays are swizzled instead of padded: the 4-float chunk c of token row m sits at chunk position
+// c ^ ((m >> 2) & 7).  The transposing 4-byte stores of a warp (eight token quads x four coordinates of one chunk) then
+// fall into 32 different banks, and the 16-byte loads of the arithmetic still touch whole, differently ordered chunks
+// of a row.  (With padded rows those stores were four-way bank conflicts and the kernel was bound by shared-memory
+// bandwidth: 82 % of its peak, a quarter of the wavefronts being conflicts.)
+__device__ __forceinline__ int dw_addr(int m, int e) { return m * DW_LD + ((((e >> 2) ^ ((m >> 2) & 7)) << 2) | (e & 3)); }
 
 // grid: x = s * NB + nb, y = split.  acts_g / acts_y: [S][ntiles][D][32].
 __global__ void __launch_bounds__(DW_THREADS) proj_dw_partial_kernel(const float *__restrict__ acts_g,
@@ -62,10 +68,11 @@ __global__ void __launch_bounds__(DW_THREADS) proj_dw_partial_kernel(const float
         for (int j = 0; j < 4; j++) {
             const int f = (tid + j * DW_THREADS) * 4;  // float index in the chunk: e = f / 32, m = f % 32 .. +3
             const int e = f >> 5, m = f & 31;
-            Gs[b][(m + 0) * DW_LD + e] = rg[j].x; Gs[b][(m + 1) * DW_LD + e] = rg[j].y;
-            Gs[b][(m + 2) * DW_LD + e] = rg[j].z; Gs[b][(m + 3) * DW_LD + e] = rg[j].w;
-            Ys[b][(m + 0) * DW_LD + e] = ry[j].x; Ys[b][(m + 1) * DW_LD + e] = ry[j].y;
-            Ys[b][(m + 2) * DW_LD + e] = ry[j].z; Ys[b][(m + 3) * DW_LD + e] = ry[j].w;
+            const int a0 = dw_addr(m, e);  // m is a multiple of 4: the four rows share the swizzle
+            Gs[b][a0] = rg[j].x; Gs[b][a0 + DW_LD] = rg[j].y;
+            Gs[b][a0 + 2 * DW_LD] = rg[j].z; Gs[b][a0 + 3 * DW_LD] = rg[j].w;
+            Ys[b][a0] = ry[j].x; Ys[b][a0 + DW_LD] = ry[j].y;
+            Ys[b][a0 + 2 * DW_LD] = ry[j].z; Ys[b][a0 + 3 * DW_LD] = ry[j].w;
         }
     };
     if (t_lo < t_hi) {
@@ -76,12 +83,12 @@ __global__ void __launch_bounds__(DW_THREADS) proj_dw_partial_kernel(const float
     int b = 0;
     for (long long t = t_lo; t < t_hi; t++, b ^= 1) {
         if (t + 1 < t_hi) fetch(t + 1);  // in flight during the arithmetic below
-        const float *G = Gs[b] + 8 * to, *Yv = Ys[b] + 4 * ti;
+        const float *G = Gs[b], *Yv = Ys[b];
 #pragma unroll 8
         for (int m = 0; m < TILE_M; m++) {
-            const float4 g0 = *reinterpret_cast<const float4 *>(G + m * DW_LD);
-            const float4 g1 = *reinterpret_cast<const float4 *>(G + m * DW_LD + 4);
-            const float4 y4 = *reinterpret_cast<const float4 *>(Yv + m * DW_LD);
+            const float4 g0 = *reinterpret_cast<const float4 *>(G + dw_addr(m, 8 * to));
+            const float4 g1 = *reinterpret_cast<const float4 *>(G + dw_addr(m, 8 * to + 4));
+            const float4 y4 = *reinterpret_cast<const float4 *>(Yv + dw_addr(m, 4 * ti));
             const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
             const float yv[4] = {y4.x, y4.y, y4.z, y4.w};
             // two output rows per instruction (packed fused multiply-add: the same fmaf chain per element)
